@@ -1,0 +1,190 @@
+#!/usr/bin/env python3
+"""Generate the golden fixtures in this directory from the UNMODIFIED reference goldens.
+
+Run in a container that has the reference checkout (default /root/reference, or
+$DSV32_REFERENCE_ROOT):
+
+    python tests/golden/make_golden.py
+
+The reference's torch-CPU golden functions live in its operator test files.  Those
+files import `pypto` and `torch_npu` at module level; both are replaced here by
+permissive stand-in modules (every attribute access, call, subscript and decorator
+use succeeds), which is enough to import the files and call the pure-torch goldens.
+
+Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
+  sfa_small.npz      inputs + output of compute_attention_no_flash
+  indexer_small.npz  inputs + topk_res of lightning_indexer_compute (+ oracle scores)
+  prolog_small.npz   seed + input digests + outputs of indexer_prolog
+  kat.json           the two interpreter known-answer tests, restated as data
+
+Nothing at test time reads the reference: the tests only read these files.
+"""
+import hashlib
+import json
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("DSV32_REFERENCE_ROOT", "/root/reference")
+MODEL_DIR = os.path.join(REF, "models", "deepseek_v32_exp")
+
+
+class _Anything:
+    """Stand-in object: any attribute, call, item or decorator use succeeds."""
+
+    def __init__(self, name="stub"):
+        self.__dict__["_name"] = name
+
+    def __getattr__(self, item):
+        if item.startswith("__") and item.endswith("__"):
+            raise AttributeError(item)
+        return _Anything(f"{self._name}.{item}")
+
+    def __call__(self, *args, **kwargs):
+        if len(args) == 1 and not kwargs and callable(args[0]) and not isinstance(args[0], _Anything):
+            return args[0]  # used as a bare decorator
+        return _Anything(f"{self._name}()")
+
+    def __getitem__(self, item):
+        return _Anything(f"{self._name}[]")
+
+    def __iter__(self):
+        return iter(())
+
+    def __eq__(self, other):
+        return False
+
+    def __hash__(self):
+        return id(self)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+class _StubModule(types.ModuleType):
+    def __getattr__(self, item):
+        if item.startswith("__") and item.endswith("__"):
+            raise AttributeError(item)
+        return _Anything(f"{self.__name__}.{item}")
+
+
+def install_reference_stubs():
+    for name in ("torch_npu", "pypto", "pypto.experimental", "pypto.operation", "pypto.pypto_impl",
+                 "pypto.frontend", "pypto.platform"):
+        mod = _StubModule(name)
+        mod.__path__ = []
+        sys.modules[name] = mod
+    if MODEL_DIR not in sys.path:
+        sys.path.insert(0, MODEL_DIR)
+
+
+def bits16(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy()
+
+
+def digest(t: torch.Tensor) -> str:
+    t = t.contiguous()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        raw = t.view(torch.int16).numpy().tobytes()
+    else:
+        raw = t.numpy().tobytes()
+    return hashlib.sha256(raw).hexdigest()
+
+
+def make_sfa():
+    import deepseekv32_sparse_flash_attention_quant as ref  # noqa: reference module
+    b, nq, nkv, s1 = 3, 128, 1, 2
+    act_seq = [2600, 700, 15]
+    input_params, data, atten_out = ref.gen_gather_select_attention_golden(torch.bfloat16, (b, nq, nkv, s1), 1, act_seq)
+    q_nope, q_rope, kn, kr, kn_scales, topk_indices, block_table, _ = data
+    np.savez_compressed(
+        os.path.join(HERE, "sfa_small.npz"),
+        b=b, s1=s1, nq=nq, softmax_scale=np.float64(input_params[-1]), act_seq=np.array(act_seq, dtype=np.int32),
+        q_nope=bits16(q_nope), q_rope=bits16(q_rope), k_nope=kn.numpy(), k_rope=bits16(kr),
+        k_scales=kn_scales.numpy(), topk_indices=topk_indices.numpy(), block_table=block_table.numpy(),
+        out=bits16(atten_out))
+    print("sfa_small: out", tuple(atten_out.shape))
+
+
+def make_indexer():
+    import deepseekv32_lightning_indexer_quant as ref  # noqa: reference module
+    torch.manual_seed(11)
+    np.random.seed(11)
+    b, s1, n1, d, bs = 3, 2, 64, 128, 128
+    act_seq = [3000, 971, 2049]
+    s2 = max(act_seq)
+    block_num = sum((s + bs - 1) // bs for s in act_seq)
+    params = dict(b=b, s1=s1, n1=n1, n2=1, d=d, dtype=torch.float16, s2=s2, act_seq=act_seq, block_size=bs,
+                  block_num=block_num, max_block_num=(s2 + bs - 1) // bs, selected_count=2048)
+    m = ref.gen_data_for_compute(params, is_quant=True)
+    # The stock generator draws randn->int8 (mostly 0/+-1), which makes thousands of exact
+    # score ties.  Replace values (not shapes/layout) by full-range data so the top-k is well defined.
+    g = torch.Generator().manual_seed(12)
+    m["query"] = torch.randint(-127, 128, m["query"].shape, generator=g, dtype=torch.int8)
+    m["key"] = torch.randint(-127, 128, m["key"].shape, generator=g, dtype=torch.int8)
+    m["q_scale"] = (torch.rand(m["q_scale"].shape, generator=g) * 0.019 + 0.001).to(torch.float16)
+    m["k_scale"] = (torch.rand(m["k_scale"].shape, generator=g) * 0.019 + 0.001).to(torch.float16)
+    topk_res = ref.lightning_indexer_compute(m, params)
+    np.savez_compressed(
+        os.path.join(HERE, "indexer_small.npz"),
+        b=b, s1=s1, act_seq=np.array(act_seq, dtype=np.int32),
+        query=m["query"].reshape(b * s1, n1, d).numpy(), q_scale=bits16(m["q_scale"].reshape(b * s1, n1)),
+        key=m["key"].numpy(), k_scale=bits16(m["k_scale"].reshape(block_num, bs, 1)),
+        weights=bits16(m["weights"].reshape(b * s1, n1)), block_table=m["block_table"].numpy(),
+        topk_res=topk_res.numpy())
+    print("indexer_small: topk_res", tuple(topk_res.shape))
+
+
+def prolog_inputs(seed, b, s1, s2):
+    """Restates the call order of the reference generator
+    (deepseekv32_lightning_indexer_prolog_quant.py:105-158) so that the same seed gives the
+    same tensors without the reference being present."""
+    import deepseekv32_lightning_indexer_prolog_quant as ref  # noqa: reference module
+    torch.manual_seed(seed)
+    dims = ref.gen_dims({"b": b, "s1": s1, "s2": s2})
+    inputs = ref.gen_inputs(dims, torch.bfloat16)
+    return ref, dims, inputs
+
+
+def make_prolog():
+    seed, b, s1, s2 = 7, 2, 2, 512
+    ref, dims, inputs = prolog_inputs(seed, b, s1, s2)
+    out = ref.indexer_prolog(inputs, dims)
+    t = b * s1
+    digests = {k: digest(v) for k, v in inputs.items() if isinstance(v, torch.Tensor)}
+    np.savez_compressed(
+        os.path.join(HERE, "prolog_small.npz"),
+        seed=seed, b=b, s1=s1, s2=s2, digests=json.dumps(digests),
+        q_int8=out["query"].reshape(t, 64, 128).numpy(), q_scale=bits16(out["query_scale"].reshape(t, 64, 1)),
+        k_cache=out["idx_k_cache_out"].numpy(), k_scale_cache=bits16(out["idx_k_scale_cache_out"]),
+        weights=bits16(out["weights"].reshape(t, 64)))
+    print("prolog_small: q_int8", tuple(out["query"].shape))
+
+
+def make_kat():
+    kat = {
+        "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
+            "input": [5, 4, 5, 3, 5, 2], "k": 3, "values": [5, 5, 5], "indices": [0, 2, 4]},
+        "paged_gather": {  # test_interp_calc_matmul_sort.cpp:830-863
+            "rows": 8, "cols": 4, "row_rule": "params[r][c] = 10*r + c", "indices": [0, 2, 5, 3],
+            "page_table": [2, 0, 1], "block_size": 2, "expected_rows": [4, 0, 3, 1]},
+    }
+    with open(os.path.join(HERE, "kat.json"), "w") as f:
+        json.dump(kat, f, indent=1)
+
+
+if __name__ == "__main__":
+    if not os.path.isdir(MODEL_DIR):
+        sys.exit(f"reference checkout not found at {MODEL_DIR}")
+    install_reference_stubs()
+    make_kat()
+    make_sfa()
+    make_indexer()
+    make_prolog()

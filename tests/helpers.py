@@ -1,0 +1,170 @@
+"""Shared helpers for the test-suite: fixture loading, seeded synthetic inputs."""
+import hashlib
+import json
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def from_bits16(a, dtype):
+    return torch.from_numpy(np.ascontiguousarray(a)).view(dtype)
+
+
+def digest(t: torch.Tensor) -> str:
+    t = t.contiguous()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        raw = t.view(torch.int16).numpy().tobytes()
+    else:
+        raw = t.numpy().tobytes()
+    return hashlib.sha256(raw).hexdigest()
+
+
+def load_sfa_golden():
+    z = np.load(os.path.join(GOLDEN, "sfa_small.npz"))
+    bf = torch.bfloat16
+    return dict(
+        b=int(z["b"]), s1=int(z["s1"]), nq=int(z["nq"]), softmax_scale=float(z["softmax_scale"]),
+        act_seq=torch.from_numpy(z["act_seq"]), q_nope=from_bits16(z["q_nope"], bf), q_rope=from_bits16(z["q_rope"], bf),
+        k_nope=torch.from_numpy(z["k_nope"]), k_rope=from_bits16(z["k_rope"], bf),
+        k_scales=torch.from_numpy(z["k_scales"]), topk_indices=torch.from_numpy(z["topk_indices"]),
+        block_table=torch.from_numpy(z["block_table"]), out=from_bits16(z["out"], bf))
+
+
+def load_indexer_golden():
+    z = np.load(os.path.join(GOLDEN, "indexer_small.npz"))
+    h = torch.float16
+    return dict(
+        b=int(z["b"]), s1=int(z["s1"]), act_seq=torch.from_numpy(z["act_seq"]), query=torch.from_numpy(z["query"]),
+        q_scale=from_bits16(z["q_scale"], h), key=torch.from_numpy(z["key"]), k_scale=from_bits16(z["k_scale"], h),
+        weights=from_bits16(z["weights"], h), block_table=torch.from_numpy(z["block_table"]),
+        topk_res=torch.from_numpy(z["topk_res"]))
+
+
+def load_prolog_golden():
+    z = np.load(os.path.join(GOLDEN, "prolog_small.npz"))
+    return dict(
+        seed=int(z["seed"]), b=int(z["b"]), s1=int(z["s1"]), s2=int(z["s2"]), digests=json.loads(str(z["digests"])),
+        q_int8=torch.from_numpy(z["q_int8"]), q_scale=from_bits16(z["q_scale"], torch.float16),
+        k_cache=torch.from_numpy(z["k_cache"]), k_scale_cache=from_bits16(z["k_scale_cache"], torch.float16),
+        weights=from_bits16(z["weights"], torch.float16))
+
+
+def load_kat():
+    with open(os.path.join(GOLDEN, "kat.json")) as f:
+        return json.load(f)
+
+
+# --------------------------------------------------------------------------
+# seeded synthetic inputs
+# --------------------------------------------------------------------------
+def make_block_table(act_seq, block_size, gen, extra_blocks=0):
+    """Random page assignment; unused slots are -1.  Returns (block_num, table)."""
+    nblk = [math.ceil(int(s) / block_size) for s in act_seq]
+    total = sum(nblk) + extra_blocks
+    perm = torch.randperm(total, generator=gen).to(torch.int32)
+    width = max(max(nblk), 1)
+    table = torch.full((len(act_seq), width), -1, dtype=torch.int32)
+    pos = 0
+    for i, n in enumerate(nblk):
+        table[i, :n] = perm[pos:pos + n]
+        pos += n
+    return total, table
+
+
+def prolog_reference_inputs(seed, b, s1, s2):
+    """Same RNG call order as the reference generator
+    (deepseekv32_lightning_indexer_prolog_quant.py:105-158), so the same seed reproduces
+    the tensors whose digests are stored in prolog_small.npz."""
+    torch.manual_seed(seed)
+    bf = torch.bfloat16
+    h, qr, d, n, rd, bs = 7168, 1536, 128, 64, 64, 128
+    x = torch.empty((b, s1, h), dtype=bf).uniform_(-1, 1)
+    q_norm = torch.randint(low=-128, high=128, size=(b, s1, qr), dtype=torch.int8)
+    q_norm_scale = torch.empty((b, s1, 1), dtype=torch.float32).uniform_(-1, 1)
+    w_qb = torch.randint(low=-128, high=128, size=(qr, n * d), dtype=torch.int8)
+    w_qb_scale = torch.empty((n * d, 1), dtype=torch.float32).uniform_(-1, 1)
+    wk = torch.empty((h, d), dtype=bf).uniform_(-1, 1)
+    w_proj = torch.empty((h, n), dtype=bf).uniform_(-1, 1)
+    ln_gamma = torch.ones((d,), dtype=bf)
+    ln_beta = torch.zeros((d,), dtype=bf)
+    ang = torch.rand(b, s1, rd, dtype=torch.float32) * 2 * torch.pi
+    cos = torch.cos(ang).to(bf)
+    sin = torch.sin(ang).to(bf)
+    hq = torch.empty((d, d), dtype=bf).uniform_(-1, 1)
+    hk = torch.empty((d, d), dtype=bf).uniform_(-1, 1)
+    k_bsnd = torch.randint(low=-128, high=128, size=(b, s2, 1, d), dtype=torch.int8)
+    ks_bsnd = torch.empty((b, s2, 1, 1), dtype=torch.float16).uniform_(-1, 1)
+    nblk_each = math.ceil(s2 / bs)
+    block_num = nblk_each * b
+    perm = torch.arange(0, block_num, 1)
+    perm = perm[torch.randperm(perm.size(0))].to(torch.int32)
+    block_table = perm.reshape(b, nblk_each).clone()
+    cache_index = torch.empty((b, s1), dtype=torch.int64)
+    for i in range(b):
+        for j in range(s1):
+            pos = s2 - s1 + j
+            cache_index[i, j] = int(block_table[i, pos // bs]) * bs + pos % bs
+    k_cache = torch.zeros((block_num, bs, 1, d), dtype=torch.int8)
+    k_scale_cache = torch.zeros((block_num, bs, 1, 1), dtype=torch.float16)
+    for i in range(b):
+        for j in range(nblk_each):
+            k_cache[block_table[i, j]] = k_bsnd[i, j * bs:(j + 1) * bs]
+            k_scale_cache[block_table[i, j]] = ks_bsnd[i, j * bs:(j + 1) * bs]
+    t = b * s1
+    return {
+        "token_x": x.reshape(t, h), "q_norm": q_norm.reshape(t, qr), "q_norm_scale": q_norm_scale.reshape(t, 1),
+        "w_idx_qb": w_qb, "w_idx_qb_scale": w_qb_scale, "w_idx_k": wk, "w_idx_proj": w_proj,
+        "layer_norm_gamma": ln_gamma, "layer_norm_beta": ln_beta, "cos_idx_rope": cos.reshape(t, rd),
+        "sin_idx_rope": sin.reshape(t, rd), "hadamard_q": hq, "hadamard_k": hk, "idx_k_cache": k_cache,
+        "idx_k_scale_cache": k_scale_cache, "idx_k_cache_index": cache_index.reshape(t),
+        "idx_block_table": block_table,
+    }
+
+
+def gen_sfa_inputs(seed, act_seq, s1=1, nq=128, topk=2048, block_size=128, pad_short=True, extra_blocks=0):
+    """Seeded synthetic SFA inputs in the operator's layouts (see DESIGN: config 0 distributions)."""
+    g = torch.Generator().manual_seed(seed)
+    b = len(act_seq)
+    t = b * s1
+    bf = torch.bfloat16
+    block_num, block_table = make_block_table(act_seq, block_size, g, extra_blocks)
+    rows = block_num * block_size
+    q_nope = torch.randn((t * nq, 512), generator=g).to(bf)
+    q_rope = torch.randn((t * nq, 64), generator=g).to(bf)
+    k_nope = torch.randint(-127, 128, (rows, 512), generator=g, dtype=torch.int8)
+    k_rope = torch.randn((rows, 64), generator=g).to(bf)
+    k_scales = torch.rand((rows, 4), generator=g) * 0.019 + 0.001
+    topk_indices = torch.full((t, topk), -1, dtype=torch.int32)
+    for bi, L in enumerate(act_seq):
+        for si in range(s1):
+            eff = max(int(L) - (s1 - 1 - si), 0)
+            if eff >= topk:
+                topk_indices[bi * s1 + si] = torch.randperm(eff, generator=g)[:topk].to(torch.int32)
+            elif eff > 0:
+                topk_indices[bi * s1 + si, :eff] = torch.randperm(eff, generator=g).to(torch.int32)
+    return dict(q_nope=q_nope, q_rope=q_rope, k_nope=k_nope, k_rope=k_rope, k_scales=k_scales,
+                topk_indices=topk_indices, block_table=block_table,
+                act_seq=torch.tensor(act_seq, dtype=torch.int32), b=b, s1=s1, nq=nq,
+                softmax_scale=576 ** -0.5, topk=topk, block_size=block_size)
+
+
+def gen_indexer_inputs(seed, act_seq, s1=1, block_size=128, extra_blocks=0):
+    g = torch.Generator().manual_seed(seed)
+    b = len(act_seq)
+    t = b * s1
+    block_num, block_table = make_block_table(act_seq, block_size, g, extra_blocks)
+    query = torch.randint(-127, 128, (t, 64, 128), generator=g, dtype=torch.int8)
+    q_scale = (torch.rand((t, 64), generator=g) * 0.019 + 0.001).to(torch.float16)
+    weights = (torch.randn((t, 64), generator=g) * 0.1).to(torch.float16)
+    key = torch.randint(-127, 128, (block_num, block_size, 1, 128), generator=g, dtype=torch.int8)
+    k_scale = (torch.rand((block_num, block_size, 1), generator=g) * 0.019 + 0.001).to(torch.float16)
+    return dict(query=query, q_scale=q_scale, weights=weights, key=key, k_scale=k_scale, block_table=block_table,
+                act_seq=torch.tensor(act_seq, dtype=torch.int32), b=b, s1=s1)

@@ -1,0 +1,85 @@
+"""The CPU oracle against the fixtures produced by the unmodified reference goldens."""
+import torch
+
+import helpers
+from oracle import dsv32_oracle as orc
+
+
+def test_kat_topk_ties_lower_index_first():
+    kat = helpers.load_kat()["topk_ties"]
+    idx = orc.topk_indices_ref(torch.tensor(kat["input"], dtype=torch.float32), kat["k"])
+    assert idx.tolist() == kat["indices"]
+
+
+def test_kat_paged_gather():
+    kat = helpers.load_kat()["paged_gather"]
+    params = torch.tensor([[10 * r + c for c in range(kat["cols"])] for r in range(kat["rows"])])
+    got = orc.paged_gather(params, torch.tensor(kat["indices"]), torch.tensor(kat["page_table"]), kat["block_size"])
+    assert got.tolist() == [params[r].tolist() for r in kat["expected_rows"]]
+
+
+def test_sfa_oracle_matches_reference_golden():
+    g = helpers.load_sfa_golden()
+    out = orc.sfa_quant(g["q_nope"], g["q_rope"], g["k_nope"], g["k_rope"], g["k_scales"], g["topk_indices"],
+                        g["block_table"], g["act_seq"], g["nq"], g["softmax_scale"])
+    assert out.shape == g["out"].shape
+    # same torch ops on the same data: bit-exact on the generating machine, a bf16 ulp elsewhere
+    assert torch.allclose(out.float(), g["out"].float(), rtol=1e-2, atol=1e-3)
+    assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
+
+
+def test_indexer_oracle_matches_reference_golden():
+    g = helpers.load_indexer_golden()
+    res, scores = orc.lightning_indexer(g["query"], g["q_scale"], g["key"], g["k_scale"], g["weights"], g["act_seq"],
+                                        g["block_table"], 2048, return_scores=True)
+    assert res.shape == g["topk_res"].shape
+    s1 = g["s1"]
+    for t in range(res.shape[0]):
+        ok, ndiff, _ = orc.topk_sets_match(res[t, 0], g["topk_res"][t, 0], scores[t // s1][t % s1])
+        assert ok, (t, ndiff)
+        # pads: -1 exactly where the reference has them
+        assert ((res[t, 0] < 0) == (g["topk_res"][t, 0] < 0)).all()
+
+
+def test_indexer_dots_exact_in_fp32():
+    g = helpers.gen_indexer_inputs(5, [300], s1=2)
+    rows = orc.paged_rows(g["block_table"][0], torch.arange(300), 128)
+    keys = g["key"].reshape(-1, 128)[rows]
+    _, dots = orc.indexer_request_scores(g["query"], g["q_scale"], g["weights"], keys,
+                                         g["k_scale"].reshape(-1)[rows], return_dots=True)
+    ref = torch.matmul(g["query"].reshape(128, 128).to(torch.int32), keys.t().to(torch.int32)).reshape(2, 64, -1)
+    assert torch.equal(dots, ref)
+
+
+def test_prolog_inputs_reproduce_and_oracle_matches_reference_golden():
+    g = helpers.load_prolog_golden()
+    inp = helpers.prolog_reference_inputs(g["seed"], g["b"], g["s1"], g["s2"])
+    for name, d in g["digests"].items():
+        if name in inp:
+            assert helpers.digest(inp[name]) == d, name
+    q_i8, q_s, kc, ksc, w = orc.indexer_prolog(
+        inp["token_x"], inp["q_norm"], inp["q_norm_scale"], inp["w_idx_qb"], inp["w_idx_qb_scale"], inp["w_idx_k"],
+        inp["w_idx_proj"], inp["layer_norm_gamma"], inp["layer_norm_beta"], inp["cos_idx_rope"], inp["sin_idx_rope"],
+        inp["hadamard_q"], inp["hadamard_k"], inp["idx_k_cache"], inp["idx_k_scale_cache"], inp["idx_k_cache_index"])
+    assert (q_i8.int() - g["q_int8"].int()).abs().max() <= 1
+    assert torch.allclose(q_s.float(), g["q_scale"].float(), atol=2.5e-5, rtol=1e-3)
+    assert (kc.int() - g["k_cache"].int()).abs().max() <= 1
+    assert torch.allclose(ksc.float(), g["k_scale_cache"].float(), atol=2.5e-5, rtol=1e-3)
+    assert torch.allclose(w.float(), g["weights"].float(), atol=2.5e-5, rtol=1e-3)
+
+
+def test_merge_topk_candidates_equals_global_topk():
+    gen = torch.Generator().manual_seed(3)
+    scores = torch.randn(2, 4000, generator=gen)
+    scores[0, 100] = scores[0, 3000]  # a tie across shards
+    k, shards = 256, 4
+    cs, ci = [], []
+    for s in range(shards):
+        lo, hi = s * 1000, (s + 1) * 1000
+        part = scores[:, lo:hi]
+        idx = torch.stack([orc.topk_indices_ref(part[i], k) for i in range(2)])
+        cs.append(torch.gather(part, 1, idx))
+        ci.append((idx + lo).to(torch.int32))
+    merged = orc.merge_topk_candidates(torch.cat(cs, 1), torch.cat(ci, 1), k)
+    for i in range(2):
+        assert merged[i].tolist() == orc.topk_indices_ref(scores[i], k).tolist()
