@@ -1,0 +1,167 @@
+/*
+ * dsv32_b200 -- C ABI of the B200 (sm_100a) implementation of the DeepSeek-V3.2
+ * quantized sparse-attention decode path.
+ *
+ * Every entry point takes a struct of plain device pointers and sizes plus a CUDA
+ * stream (cudaStream_t passed as void*).  Calls only enqueue work on that stream and
+ * return immediately: 0 = enqueued, negative = rejected on the host (nothing was
+ * launched; dsv32_last_error() holds the reason for the calling thread).
+ * The caller owns every buffer, including the workspace.  All tensors are contiguous
+ * and row-major.  Paths cited below are relative to the reference project root.
+ */
+#ifndef DSV32_B200_H_
+#define DSV32_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSV32_ABI_VERSION 1
+
+/* host-side return codes */
+#define DSV32_OK 0
+#define DSV32_ERR_INVALID_ARG (-1)
+#define DSV32_ERR_WORKSPACE (-2)
+#define DSV32_ERR_CUDA (-3)
+#define DSV32_ERR_UNSUPPORTED (-4)
+
+/* device status word 0 (args.status, 4 x uint32, caller-zeroed; optional, may be NULL) */
+#define DSV32_STATUS_OK 0u
+#define DSV32_STATUS_BAD_PAGE 1u    /* a page-table entry on the valid range was < 0 or >= number of blocks */
+#define DSV32_STATUS_BAD_INDEX 2u   /* a top-k index pointed outside the request's page table              */
+#define DSV32_STATUS_TIMEOUT 3u     /* a bounded device-side wait gave up (word 1 = location id)            */
+
+/* ---------------------------------------------------------------------------------------
+ * Sparse flash attention over the int8 paged latent cache.
+ * Replaces sparse_flash_attention_quant_d / _p / _d_950
+ * (models/deepseek_v32_exp/sparse_flash_attention_quant_impl.py:655-674, 734, 572; compute
+ * body :45-286).  For token t = b_idx*s1 + i only the first
+ * K = min(max(act_seq[b_idx] - s1 + 1 + i, 0), topk) entries of topk_indices[t] are used.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* query_nope;        /* bf16 [b*s1*n_q, 512]                  */
+  const void* query_rope;        /* bf16 [b*s1*n_q, 64]                   */
+  const void* key_nope;          /* int8 [rows, 512]                      */
+  const void* key_rope;          /* bf16 [rows, 64]                       */
+  const float* k_nope_scales;    /* fp32 [rows, 4] (one per 128-dim group) */
+  const int32_t* topk_indices;   /* int32 [b*s1, topk]                    */
+  const int32_t* block_table;    /* int32 [b, max_blocks]                 */
+  const int32_t* kv_act_seqs;    /* int32 [b]                             */
+  void* attention_out;           /* bf16 [b, s1, n_q, 512]                */
+  void* workspace;               /* >= dsv32_sfa_workspace_bytes(...)     */
+  size_t workspace_bytes;
+  uint32_t* status;              /* device uint32[4] or NULL              */
+  int64_t rows;                  /* block_num * block_size                */
+  int32_t b, s1, n_q, topk, block_size, max_blocks;
+  int32_t kv_splits;             /* 0 = choose automatically              */
+  float softmax_scale;
+} Dsv32SfaArgs;
+
+size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t topk, int32_t kv_splits);
+int dsv32_sfa_quant(const Dsv32SfaArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Lightning indexer: int8 q.k scores (+ReLU, 2^-11, fp16 round, per-head weighted sum,
+ * key scale) and top-k selection.
+ * Replaces lightning_indexer_decode
+ * (models/deepseek_v32_exp/lightning_indexer_quant_impl.py:226-275; score part :114-177,
+ * top-k part :179-216).  topk_res rows hold indices by descending score, equal scores by
+ * ascending index, then -1 pads.
+ * key_begin/key_end (logical key positions) restrict the scan to a shard of the key
+ * range; pass 0 / INT32_MAX for the whole context.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const int8_t* idx_query;        /* int8 [b*s1, 64, 128]                 */
+  const void* idx_query_scale;    /* fp16 [b*s1, 64]                      */
+  const int8_t* idx_key_cache;    /* int8 [num_blocks, block_size, 1, 128] */
+  const void* idx_key_scale;      /* fp16 [num_blocks, block_size, 1]     */
+  const void* idx_weight;         /* fp16 [b*s1, 64]                      */
+  const int32_t* act_seq_key;     /* int32 [b]                            */
+  const int32_t* block_table;     /* int32 [b, max_blocks]                */
+  int32_t* topk_res;              /* int32 [b*s1, 1, selected_count] or NULL (scores only) */
+  float* topk_scores;             /* fp32 [b*s1, selected_count] or NULL: scores of topk_res (-inf pads) */
+  float* scores_out;              /* fp32 [b*s1, score_ld] or NULL: use workspace           */
+  int32_t* dots_out;              /* int32 [b*s1, 64, score_ld] or NULL (verification only) */
+  void* workspace;
+  size_t workspace_bytes;
+  uint32_t* status;
+  int64_t num_blocks;
+  int32_t b, s1, block_size, max_blocks, selected_count;
+  int32_t score_ld;               /* row stride of scores_out/dots_out in elements (>= max_blocks*block_size); 0 = that value */
+  int32_t key_begin, key_end;
+} Dsv32IndexerArgs;
+
+size_t dsv32_indexer_workspace_bytes(int32_t b, int32_t s1, int32_t max_blocks, int32_t block_size);
+int dsv32_indexer_topk(const Dsv32IndexerArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Row-wise top-k over fp32 scores (the selection stage alone).
+ * Semantics of pypto.topk as used at lightning_indexer_quant_impl.py:179-216; tie rule of
+ * framework/src/interface/interpreter/calculator/calc_torch.cpp:2481-2495.
+ * ids == NULL: entry j of a row has id j + id_base.  With ids (candidate merge), ties are
+ * broken by ascending id and entries with id < 0 are ignored.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const float* scores;            /* fp32 [rows, ld]                      */
+  const int32_t* ids;             /* int32 [rows, ld] or NULL             */
+  const int32_t* counts;          /* int32 [rows]: valid entries per row  */
+  int32_t* out_idx;               /* int32 [rows, k]                      */
+  float* out_scores;              /* fp32 [rows, k] or NULL               */
+  int32_t rows, ld, k, id_base;
+} Dsv32TopkArgs;
+
+int dsv32_topk_select(const Dsv32TopkArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Indexer prolog (quant): W8A8 q projection, k projection + LayerNorm, RoPE, 128x128
+ * "Hadamard" matmul, per-row int8 quantisation, cache scatter, head weights.
+ * Replaces lightning_indexer_prolog_quant
+ * (models/deepseek_v32_exp/lightning_indexer_prolog_quant_impl.py:325-543).
+ * Weights are plain row-major [K, N] (the reference passes an NZ-formatted view of the
+ * same logical matrices).  k_cache / k_scale_cache are updated in place at rows
+ * k_cache_index[t]; no other row is touched.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;                  /* bf16 [t, 7168]                       */
+  const int8_t* q_norm;           /* int8 [t, 1536]                       */
+  const float* q_norm_scale;      /* fp32 [t, 1]                          */
+  const int8_t* w_qb;             /* int8 [1536, 8192]                    */
+  const float* w_qb_scale;        /* fp32 [8192, 1]                       */
+  const void* wk;                 /* bf16 [7168, 128]                     */
+  const void* w_proj;             /* bf16 [7168, 64]                      */
+  const void* ln_gamma_k;         /* bf16 [128]                           */
+  const void* ln_beta_k;          /* bf16 [128]                           */
+  const void* cos_idx_rope;       /* bf16 [t, 64]                         */
+  const void* sin_idx_rope;       /* bf16 [t, 64]                         */
+  const void* hadamard_q;         /* bf16 [128, 128]                      */
+  const void* hadamard_k;         /* bf16 [128, 128]                      */
+  const int64_t* k_cache_index;   /* int64 [t]                            */
+  int8_t* q_int8;                 /* out int8 [t, 64, 128]                */
+  void* q_scale;                  /* out fp16 [t, 64, 1]                  */
+  int8_t* k_cache;                /* in/out int8 [cache_rows, 128]        */
+  void* k_scale_cache;            /* in/out fp16 [cache_rows]             */
+  void* weights;                  /* out fp16 [t, 64]                     */
+  void* workspace;
+  size_t workspace_bytes;
+  uint32_t* status;
+  int64_t cache_rows;
+  int32_t t;
+  float ln_eps;
+} Dsv32PrologArgs;
+
+size_t dsv32_prolog_workspace_bytes(int32_t t);
+int dsv32_indexer_prolog(const Dsv32PrologArgs* args, void* cuda_stream);
+
+/* library-wide */
+int dsv32_abi_version(void);
+const char* dsv32_last_error(void);
+/* Number of kernel launches enqueued by this library in this process (for launch accounting). */
+uint64_t dsv32_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSV32_B200_H_ */

@@ -1,0 +1,106 @@
+"""ctypes binding of libdsv32_b200.so (the C ABI declared in include/dsv32_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call is rejected the
+functions here raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libdsv32_b200.so")
+
+c_void_p, c_i32, c_i64, c_size_t, c_float = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t, C.c_float
+
+
+class SfaArgs(C.Structure):
+    _fields_ = [
+        ("query_nope", c_void_p), ("query_rope", c_void_p), ("key_nope", c_void_p), ("key_rope", c_void_p),
+        ("k_nope_scales", c_void_p), ("topk_indices", c_void_p), ("block_table", c_void_p), ("kv_act_seqs", c_void_p),
+        ("attention_out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("status", c_void_p),
+        ("rows", c_i64), ("b", c_i32), ("s1", c_i32), ("n_q", c_i32), ("topk", c_i32), ("block_size", c_i32),
+        ("max_blocks", c_i32), ("kv_splits", c_i32), ("softmax_scale", c_float),
+    ]
+
+
+class IndexerArgs(C.Structure):
+    _fields_ = [
+        ("idx_query", c_void_p), ("idx_query_scale", c_void_p), ("idx_key_cache", c_void_p),
+        ("idx_key_scale", c_void_p), ("idx_weight", c_void_p), ("act_seq_key", c_void_p), ("block_table", c_void_p),
+        ("topk_res", c_void_p), ("topk_scores", c_void_p), ("scores_out", c_void_p), ("dots_out", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("status", c_void_p), ("num_blocks", c_i64),
+        ("b", c_i32), ("s1", c_i32), ("block_size", c_i32), ("max_blocks", c_i32), ("selected_count", c_i32),
+        ("score_ld", c_i32), ("key_begin", c_i32), ("key_end", c_i32),
+    ]
+
+
+class TopkArgs(C.Structure):
+    _fields_ = [
+        ("scores", c_void_p), ("ids", c_void_p), ("counts", c_void_p), ("out_idx", c_void_p), ("out_scores", c_void_p),
+        ("rows", c_i32), ("ld", c_i32), ("k", c_i32), ("id_base", c_i32),
+    ]
+
+
+class PrologArgs(C.Structure):
+    _fields_ = [
+        ("x", c_void_p), ("q_norm", c_void_p), ("q_norm_scale", c_void_p), ("w_qb", c_void_p), ("w_qb_scale", c_void_p),
+        ("wk", c_void_p), ("w_proj", c_void_p), ("ln_gamma_k", c_void_p), ("ln_beta_k", c_void_p),
+        ("cos_idx_rope", c_void_p), ("sin_idx_rope", c_void_p), ("hadamard_q", c_void_p), ("hadamard_k", c_void_p),
+        ("k_cache_index", c_void_p), ("q_int8", c_void_p), ("q_scale", c_void_p), ("k_cache", c_void_p),
+        ("k_scale_cache", c_void_p), ("weights", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("status", c_void_p), ("cache_rows", c_i64), ("t", c_i32), ("ln_eps", c_float),
+    ]
+
+
+# every symbol include/dsv32_b200.h declares: name -> (restype, argtypes)
+EXPORTS = {
+    "dsv32_abi_version": (c_i32, []),
+    "dsv32_last_error": (C.c_char_p, []),
+    "dsv32_launch_count": (C.c_uint64, []),
+    "dsv32_sfa_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32, c_i32]),
+    "dsv32_sfa_quant": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
+    "dsv32_indexer_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
+    "dsv32_indexer_topk": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
+    "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
+    "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),
+    "dsv32_indexer_prolog": (c_i32, [C.POINTER(PrologArgs), c_void_p]),
+}
+
+ABI_VERSION = 1
+_lib = None
+
+
+class Dsv32Error(RuntimeError):
+    """A call into libdsv32_b200.so was rejected (host-side validation or CUDA launch error)."""
+
+
+def load():
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise Dsv32Error(
+            f"{LIB_PATH} not found: build it with `python -m pypto_b200.build` (there is no CPU fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in EXPORTS.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is missing
+        fn.restype = res
+        fn.argtypes = args
+    if lib.dsv32_abi_version() != ABI_VERSION:
+        raise Dsv32Error(f"ABI mismatch: library {lib.dsv32_abi_version()}, binding {ABI_VERSION}")
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = load().dsv32_last_error().decode("utf-8", "replace")
+        if rc == -1:
+            raise ValueError(f"{what}: {msg}")
+        raise Dsv32Error(f"{what} failed (code {rc}): {msg}")
+
+
+def launch_count() -> int:
+    return int(load().dsv32_launch_count())

@@ -1,0 +1,82 @@
+"""Host-side plumbing shared by the operator entry points: argument checks, workspace, status word."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_STATUS = {}
+STATUS_NAMES = {1: "bad page-table entry", 2: "top-k / cache index out of range", 3: "device-side wait timed out"}
+
+
+def require_cuda():
+    if not torch.cuda.is_available():
+        raise RuntimeError("pypto_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+
+
+def check_tensor(t, name, dtype, shape=None, ndim=None):
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"{name}: expected a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: expected a CUDA tensor, got device {t.device}")
+    if t.dtype != dtype:
+        raise ValueError(f"{name}: expected dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: tensor must be contiguous")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name}: expected {ndim} dims, got shape {tuple(t.shape)}")
+    if shape is not None:
+        if t.dim() != len(shape) or any(s is not None and int(d) != int(s) for d, s in zip(t.shape, shape)):
+            raise ValueError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+    return t
+
+
+def same_device(*tensors):
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device != dev:
+            raise RuntimeError(f"all tensors must live on one device: {dev} vs {t.device}")
+    return dev
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def stream_ptr(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def workspace(nbytes, device):
+    if nbytes <= 0:
+        return None
+    return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+
+def status_word(device):
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    st = _STATUS.get(key)
+    if st is None:
+        st = torch.zeros(4, dtype=torch.int32, device=device)
+        _STATUS[key] = st
+    return st
+
+
+def check_status(device=None, synchronize=True):
+    """Raise RuntimeError if a kernel of this library recorded a device-side anomaly on `device`.
+    Synchronises the device first (the status word is written by the kernels)."""
+    require_cuda()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if synchronize:
+        torch.cuda.synchronize(device)
+    st = status_word(device)
+    vals = st.tolist()
+    if vals[0] != 0:
+        st.zero_()
+        raise RuntimeError(f"dsv32 device status {vals[0]} ({STATUS_NAMES.get(vals[0], '?')}), detail {vals[1:3]}")
+
+
+lib = _lib.load
+check = _lib.check

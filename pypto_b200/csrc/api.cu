@@ -1,0 +1,263 @@
+// C ABI of libdsv32_b200.so: argument validation, workspace carving and kernel launches.
+// Declarations and the reference interfaces they replace: include/dsv32_b200.h.
+#include <atomic>
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+
+#include "kernels.cuh"
+
+namespace dsv32 {
+
+// ---- bookkeeping -----------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: launch failed: %s", what, cudaGetErrorString(e));
+    return DSV32_ERR_CUDA;
+  }
+  return DSV32_OK;
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int pick_sfa_splits(int t, int nq, int topk, int requested) {
+  const int max_splits = topk / 128 > 0 ? (topk / 128 < 16 ? topk / 128 : 16) : 1;
+  if (requested > 0) return requested < max_splits ? requested : max_splits;
+  const int ctas = t * (nq / 64);
+  if (ctas >= 148) return 1;
+  int s = (2 * 148 + ctas - 1) / ctas;
+  if (s > max_splits) s = max_splits;
+  return s < 1 ? 1 : s;
+}
+
+}  // namespace dsv32
+
+using namespace dsv32;
+
+#define REQUIRE(cond, ...)           \
+  do {                               \
+    if (!(cond)) {                   \
+      set_error(__VA_ARGS__);        \
+      return DSV32_ERR_INVALID_ARG;  \
+    }                                \
+  } while (0)
+
+extern "C" {
+
+int dsv32_abi_version(void) { return DSV32_ABI_VERSION; }
+const char* dsv32_last_error(void) { return g_err; }
+uint64_t dsv32_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+// ---- sparse flash attention ---------------------------------------------------------------------------
+size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t topk, int32_t kv_splits) {
+  if (b <= 0 || s1 <= 0 || n_q <= 0) return 0;
+  const int splits = pick_sfa_splits(b * s1, n_q, topk, kv_splits);
+  if (splits <= 1) return 0;
+  const size_t t = static_cast<size_t>(b) * s1;
+  return align_up(t * splits * n_q * kKvLora * sizeof(float), 256) + align_up(t * splits * n_q * sizeof(float), 256);
+}
+
+int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "sfa: args is NULL");
+  REQUIRE(a->b >= 0 && a->s1 >= 1, "sfa: bad b=%d s1=%d", a->b, a->s1);
+  if (a->b == 0) return DSV32_OK;
+  REQUIRE(a->n_q > 0 && a->n_q % 64 == 0, "sfa: n_q=%d must be a positive multiple of 64", a->n_q);
+  REQUIRE(a->topk >= 1, "sfa: topk=%d must be >= 1", a->topk);
+  REQUIRE(a->block_size >= 1 && a->max_blocks >= 1, "sfa: bad block_size=%d max_blocks=%d", a->block_size,
+          a->max_blocks);
+  REQUIRE(a->rows >= 0, "sfa: rows=%lld must be >= 0", static_cast<long long>(a->rows));
+  REQUIRE(a->query_nope && a->query_rope && a->key_nope && a->key_rope && a->k_nope_scales && a->topk_indices &&
+              a->block_table && a->kv_act_seqs && a->attention_out,
+          "sfa: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->key_nope) % 16 == 0 && reinterpret_cast<uintptr_t>(a->key_rope) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->k_nope_scales) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->query_nope) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->query_rope) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->attention_out) % 16 == 0,
+          "sfa: tensors must be 16-byte aligned");
+  const int t = a->b * a->s1;
+  const int splits = pick_sfa_splits(t, a->n_q, a->topk, a->kv_splits);
+  SfaParams p{};
+  p.q_nope = static_cast<const __nv_bfloat16*>(a->query_nope);
+  p.q_rope = static_cast<const __nv_bfloat16*>(a->query_rope);
+  p.k_nope = static_cast<const int8_t*>(a->key_nope);
+  p.k_rope = static_cast<const __nv_bfloat16*>(a->key_rope);
+  p.k_scales = a->k_nope_scales;
+  p.topk_idx = a->topk_indices;
+  p.block_table = a->block_table;
+  p.act_seq = a->kv_act_seqs;
+  p.out = static_cast<__nv_bfloat16*>(a->attention_out);
+  p.status = a->status;
+  p.rows = a->rows;
+  p.b = a->b; p.s1 = a->s1; p.nq = a->n_q; p.topk = a->topk; p.block_size = a->block_size;
+  p.max_blocks = a->max_blocks; p.splits = splits; p.scale = a->softmax_scale;
+  if (splits > 1) {
+    const size_t need = dsv32_sfa_workspace_bytes(a->b, a->s1, a->n_q, a->topk, splits);
+    if (a->workspace == nullptr || a->workspace_bytes < need ||
+        reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) {
+      set_error("sfa: workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
+      return DSV32_ERR_WORKSPACE;
+    }
+    const size_t o_bytes = align_up(static_cast<size_t>(t) * splits * a->n_q * kKvLora * sizeof(float), 256);
+    p.part_o = static_cast<float*>(a->workspace);
+    p.part_lse = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + o_bytes);
+  }
+  return launch_sfa_mma(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
+// ---- lightning indexer --------------------------------------------------------------------------------
+size_t dsv32_indexer_workspace_bytes(int32_t b, int32_t s1, int32_t max_blocks, int32_t block_size) {
+  if (b <= 0 || s1 <= 0 || max_blocks <= 0 || block_size <= 0) return 0;
+  return align_up(static_cast<size_t>(b) * s1 * max_blocks * block_size * sizeof(float), 256);
+}
+
+int dsv32_indexer_topk(const Dsv32IndexerArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "indexer: args is NULL");
+  REQUIRE(a->b >= 0 && a->s1 >= 1, "indexer: bad b=%d s1=%d", a->b, a->s1);
+  if (a->b == 0) return DSV32_OK;
+  REQUIRE(a->block_size == 128, "indexer: block_size=%d (only 128 is supported)", a->block_size);
+  REQUIRE(a->max_blocks >= 1 && a->num_blocks >= 0, "indexer: bad max_blocks=%d num_blocks=%lld", a->max_blocks,
+          static_cast<long long>(a->num_blocks));
+  REQUIRE(a->idx_query && a->idx_query_scale && a->idx_key_cache && a->idx_key_scale && a->idx_weight &&
+              a->act_seq_key && a->block_table,
+          "indexer: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->idx_query) % 16 == 0 && reinterpret_cast<uintptr_t>(a->idx_key_cache) % 16 == 0,
+          "indexer: idx_query / idx_key_cache must be 16-byte aligned");
+  REQUIRE(a->topk_res == nullptr || (a->selected_count >= 1 && a->selected_count <= 2048),
+          "indexer: selected_count=%d must be in [1, 2048]", a->selected_count);
+  REQUIRE(a->key_begin >= 0 && a->key_end > a->key_begin, "indexer: bad key range [%d, %d)", a->key_begin, a->key_end);
+  const int full_ld = a->max_blocks * a->block_size;
+  const int ld = a->score_ld > 0 ? a->score_ld : full_ld;
+  REQUIRE(ld >= full_ld, "indexer: score_ld=%d smaller than max_blocks*block_size=%d", ld, full_ld);
+  REQUIRE(a->dots_out == nullptr || a->scores_out != nullptr || ld == full_ld, "indexer: bad dots_out stride");
+  float* scores = a->scores_out;
+  if (scores == nullptr) {
+    const size_t need = dsv32_indexer_workspace_bytes(a->b, a->s1, a->max_blocks, a->block_size);
+    if (a->workspace == nullptr || a->workspace_bytes < need || ld != full_ld) {
+      set_error("indexer: workspace of %zu bytes required, got %zu", need, a->workspace_bytes);
+      return DSV32_ERR_WORKSPACE;
+    }
+    scores = static_cast<float*>(a->workspace);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  IndexerParams p{};
+  p.q = a->idx_query;
+  p.q_scale = static_cast<const __half*>(a->idx_query_scale);
+  p.weight = static_cast<const __half*>(a->idx_weight);
+  p.keys = a->idx_key_cache;
+  p.key_scale = static_cast<const __half*>(a->idx_key_scale);
+  p.act_seq = a->act_seq_key;
+  p.block_table = a->block_table;
+  p.scores = scores;
+  p.dots = a->dots_out;
+  p.status = a->status;
+  p.num_blocks = a->num_blocks;
+  p.b = a->b; p.s1 = a->s1; p.block_size = a->block_size; p.max_blocks = a->max_blocks; p.ld = ld;
+  p.key_begin = a->key_begin;
+  p.key_end = a->key_end;
+  // bring-up switch: DSV32_INDEXER_IMPL=mma selects the warp-MMA kernel instead of the tcgen05 one
+  static const bool use_mma = [] {
+    const char* e = getenv("DSV32_INDEXER_IMPL");
+    return e != nullptr && e[0] == 'm';
+  }();
+  int rc = use_mma ? launch_indexer_scores_mma(p, st) : launch_indexer_scores_tc(p, st);
+  if (rc != DSV32_OK || a->topk_res == nullptr) return rc;
+  TopkParams tp{};
+  tp.scores = scores;
+  tp.ids = nullptr;
+  tp.counts = nullptr;
+  tp.act_seq = a->act_seq_key;
+  tp.out_idx = a->topk_res;
+  tp.out_scores = a->topk_scores;
+  tp.s1 = a->s1;
+  tp.key_begin = a->key_begin;
+  tp.key_end = a->key_end;
+  tp.ld = ld;
+  tp.k = a->selected_count;
+  tp.id_base = 0;
+  return launch_topk(tp, a->b * a->s1, st);
+}
+
+int dsv32_topk_select(const Dsv32TopkArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "topk: args is NULL");
+  REQUIRE(a->rows >= 0 && a->ld >= 1, "topk: bad rows=%d ld=%d", a->rows, a->ld);
+  if (a->rows == 0) return DSV32_OK;
+  REQUIRE(a->k >= 1 && a->k <= 2048, "topk: k=%d must be in [1, 2048]", a->k);
+  REQUIRE(a->scores && a->counts && a->out_idx, "topk: NULL tensor pointer");
+  TopkParams tp{};
+  tp.scores = a->scores;
+  tp.ids = a->ids;
+  tp.counts = a->counts;
+  tp.act_seq = nullptr;
+  tp.out_idx = a->out_idx;
+  tp.out_scores = a->out_scores;
+  tp.s1 = 1;
+  tp.key_begin = 0;
+  tp.key_end = INT_MAX;
+  tp.ld = a->ld;
+  tp.k = a->k;
+  tp.id_base = a->id_base;
+  return launch_topk(tp, a->rows, static_cast<cudaStream_t>(cuda_stream));
+}
+
+// ---- indexer prolog -----------------------------------------------------------------------------------
+size_t dsv32_prolog_workspace_bytes(int32_t t) { return t > 0 ? align_up(prolog_workspace_bytes(t), 256) : 0; }
+
+int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "prolog: args is NULL");
+  REQUIRE(a->t >= 0, "prolog: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  REQUIRE(a->x && a->q_norm && a->q_norm_scale && a->w_qb && a->w_qb_scale && a->wk && a->w_proj && a->ln_gamma_k &&
+              a->ln_beta_k && a->cos_idx_rope && a->sin_idx_rope && a->hadamard_q && a->hadamard_k &&
+              a->k_cache_index && a->q_int8 && a->q_scale && a->k_cache && a->k_scale_cache && a->weights,
+          "prolog: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->q_norm) % 16 == 0 && reinterpret_cast<uintptr_t>(a->w_qb) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->hadamard_q) % 16 == 0 && reinterpret_cast<uintptr_t>(a->hadamard_k) % 16 == 0,
+          "prolog: q_norm / w_qb / hadamard matrices must be 16-byte aligned");
+  REQUIRE(a->cache_rows >= 1, "prolog: cache_rows=%lld must be >= 1", static_cast<long long>(a->cache_rows));
+  const size_t need = dsv32_prolog_workspace_bytes(a->t);
+  if (a->workspace == nullptr || a->workspace_bytes < need) {
+    set_error("prolog: workspace of %zu bytes required, got %zu", need, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
+  PrologParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.q_norm = a->q_norm;
+  p.q_norm_scale = a->q_norm_scale;
+  p.w_qb = a->w_qb;
+  p.w_qb_scale = a->w_qb_scale;
+  p.wk = static_cast<const __nv_bfloat16*>(a->wk);
+  p.w_proj = static_cast<const __nv_bfloat16*>(a->w_proj);
+  p.ln_gamma = static_cast<const __nv_bfloat16*>(a->ln_gamma_k);
+  p.ln_beta = static_cast<const __nv_bfloat16*>(a->ln_beta_k);
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos_idx_rope);
+  p.sin = static_cast<const __nv_bfloat16*>(a->sin_idx_rope);
+  p.had_q = static_cast<const __nv_bfloat16*>(a->hadamard_q);
+  p.had_k = static_cast<const __nv_bfloat16*>(a->hadamard_k);
+  p.cache_index = reinterpret_cast<const long long*>(a->k_cache_index);
+  p.q_int8 = a->q_int8;
+  p.q_scale = static_cast<__half*>(a->q_scale);
+  p.k_cache = a->k_cache;
+  p.k_scale_cache = static_cast<__half*>(a->k_scale_cache);
+  p.weights = static_cast<__half*>(a->weights);
+  p.partial = static_cast<float*>(a->workspace);
+  p.status = a->status;
+  p.cache_rows = a->cache_rows;
+  p.t = a->t;
+  p.eps = a->ln_eps;
+  return launch_prolog(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,86 @@
+// Kernel-side parameter blocks and launchers shared by api.cu and the kernel translation units.
+#pragma once
+#include "common.cuh"
+
+namespace dsv32 {
+
+struct TopkParams {
+  const float* scores;
+  const int32_t* ids;
+  const int32_t* counts;
+  const int32_t* act_seq;
+  int32_t* out_idx;
+  float* out_scores;
+  int s1, key_begin, key_end;
+  int ld, k, id_base;
+};
+int launch_topk(const TopkParams& p, int rows, cudaStream_t stream);
+
+struct IndexerParams {
+  const int8_t* q;
+  const __half* q_scale;
+  const __half* weight;
+  const int8_t* keys;
+  const __half* key_scale;
+  const int32_t* act_seq;
+  const int32_t* block_table;
+  float* scores;
+  int32_t* dots;
+  uint32_t* status;
+  long long num_blocks;
+  int b, s1, block_size, max_blocks, ld;
+  int key_begin, key_end;
+};
+int launch_indexer_scores_mma(const IndexerParams& p, cudaStream_t stream);
+int launch_indexer_scores_tc(const IndexerParams& p, cudaStream_t stream);
+
+struct SfaParams {
+  const __nv_bfloat16* q_nope;
+  const __nv_bfloat16* q_rope;
+  const int8_t* k_nope;
+  const __nv_bfloat16* k_rope;
+  const float* k_scales;
+  const int32_t* topk_idx;
+  const int32_t* block_table;
+  const int32_t* act_seq;
+  __nv_bfloat16* out;
+  float* part_o;
+  float* part_lse;
+  uint32_t* status;
+  long long rows;
+  int b, s1, nq, topk, block_size, max_blocks, splits;
+  float scale;
+};
+int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);
+
+struct PrologParams {
+  const __nv_bfloat16* x;
+  const int8_t* q_norm;
+  const float* q_norm_scale;
+  const int8_t* w_qb;
+  const float* w_qb_scale;
+  const __nv_bfloat16* wk;
+  const __nv_bfloat16* w_proj;
+  const __nv_bfloat16* ln_gamma;
+  const __nv_bfloat16* ln_beta;
+  const __nv_bfloat16* cos;
+  const __nv_bfloat16* sin;
+  const __nv_bfloat16* had_q;
+  const __nv_bfloat16* had_k;
+  const long long* cache_index;
+  int8_t* q_int8;
+  __half* q_scale;
+  int8_t* k_cache;
+  __half* k_scale_cache;
+  __half* weights;
+  float* partial;
+  uint32_t* status;
+  long long cache_rows;
+  int t;
+  float eps;
+};
+int launch_prolog(const PrologParams& p, cudaStream_t stream);
+size_t prolog_workspace_bytes(int t);
+
+
+}  // namespace dsv32

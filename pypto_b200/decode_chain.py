@@ -1,0 +1,82 @@
+"""One decode step of the sparse-attention chain as the reference model files define it
+(models/deepseek_v32_exp/README_en.md data flow): indexer prolog -> lightning indexer + top-k ->
+sparse flash attention, all through the operator entry points of this package.
+
+The latent cache, the index-key cache and the weights are device-resident state; the per-step
+activations may be given as pinned host tensors, in which case the step copies them to the device
+and copies the attention output back (the end-to-end path).
+"""
+from __future__ import annotations
+
+import torch
+
+from .lightning_indexer_prolog_quant_impl import (IndexerPrologQuantAttr, IndexerPrologQuantConfigs,
+                                                  lightning_indexer_prolog_quant)
+from .lightning_indexer_quant_impl import LightningIndexerConfigs, lightning_indexer_decode
+from .sparse_flash_attention_quant_impl import SaTileShapeConfig, sparse_flash_attention_quant_d
+
+STEP_INPUTS = ("x", "q_norm", "q_norm_scale", "cos", "sin", "cache_index", "q_nope", "q_rope")
+
+
+class SparseDecodeStep:
+    def __init__(self, w, nq=128, topk=2048):
+        self.w = w
+        dev = w.k_nope.device
+        t = w.t
+        self.nq, self.topk = nq, topk
+        self.q_int8 = torch.empty((t, 64, 128), dtype=torch.int8, device=dev)
+        self.q_scale = torch.empty((t, 64, 1), dtype=torch.float16, device=dev)
+        self.weights = torch.empty((t, 64), dtype=torch.float16, device=dev)
+        self.topk_res = torch.empty((t, 1, topk), dtype=torch.int32, device=dev)
+        self.out = torch.empty((w.b, w.s1, nq, 512), dtype=torch.bfloat16, device=dev)
+        self.idx_k_scale4 = w.idx_k_scale.reshape(w.idx_k_scale.shape[0], 128, 1, 1)
+        self.softmax_scale = 576 ** -0.5
+        self._cfg = (IndexerPrologQuantConfigs(), IndexerPrologQuantAttr(eps=1e-6), LightningIndexerConfigs(),
+                     SaTileShapeConfig())
+        self._dev_in = {k: getattr(w, k) for k in STEP_INPUTS}
+        self.host_in = None
+        self.host_out = None
+
+    # ---- end-to-end staging -----------------------------------------------------------------------
+    def enable_host_io(self):
+        """Keep pinned host copies of the per-step activations and a pinned output buffer."""
+        self.host_in = {k: v.cpu().pin_memory() for k, v in self._dev_in.items()}
+        self.host_out = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+        h2d = sum(v.numel() * v.element_size() for v in self.host_in.values())
+        d2h = self.host_out.numel() * self.host_out.element_size()
+        return h2d, d2h
+
+    # ---- stages -------------------------------------------------------------------------------------
+    def prolog(self):
+        w, d = self.w, self._dev_in
+        pc, pa, _, _ = self._cfg
+        lightning_indexer_prolog_quant(
+            d["x"], d["q_norm"], d["q_norm_scale"], w.w_qb, w.w_qb_scale, w.wk, w.w_proj, w.ln_gamma, w.ln_beta,
+            d["cos"], d["sin"], w.hadamard, w.hadamard, w.idx_k, self.idx_k_scale4, d["cache_index"], self.q_int8,
+            self.q_scale, w.idx_k, self.idx_k_scale4, self.weights, pc, pa)
+
+    def indexer(self):
+        w = self.w
+        lightning_indexer_decode(self.q_int8, self.q_scale.reshape(-1, 64), w.idx_k, w.idx_k_scale, self.weights,
+                                 w.act_seq, w.block_table, self.topk_res, None, self._cfg[2], self.topk)
+
+    def attention(self):
+        w, d = self.w, self._dev_in
+        sparse_flash_attention_quant_d(d["q_nope"], d["q_rope"], w.k_nope, w.k_rope, w.k_scales,
+                                       self.topk_res.reshape(-1, self.topk), w.block_table, w.act_seq, self.out,
+                                       self.nq, 1, self.softmax_scale, self.topk, 128, w.max_blocks, self._cfg[3])
+
+    def step(self):
+        """Device-resident step: prolog -> indexer + top-k -> attention on the current stream."""
+        self.prolog()
+        self.indexer()
+        self.attention()
+        return self.out
+
+    def step_from_host(self):
+        """End-to-end step: pinned host activations -> device, the three stages, output -> pinned host."""
+        for k, h in self.host_in.items():
+            self._dev_in[k].copy_(h, non_blocking=True)
+        self.step()
+        self.host_out.copy_(self.out, non_blocking=True)
+        return self.host_out

@@ -1,0 +1,118 @@
+"""Seeded synthetic decode workloads (device-resident) for the benchmark and the smoke check.
+
+Distributions: queries/activations N(0,1) bf16, latent cache int8 U{-127..127} with four fp32 scales per
+row U(0.001,0.02), rope parts N(0,1) bf16, index keys int8 U{-127..127} with fp16 scales U(0.001,0.02),
+weights N(0,0.02); pages are a random permutation of the pool; RoPE angles U(0,2pi); the 128x128
+"Hadamard" input is the Sylvester matrix / sqrt(128).  No dataset is involved.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class DecodeWorkload:
+    b: int
+    s1: int
+    ctx: list            # per-request context length (python ints)
+    block_table: torch.Tensor
+    act_seq: torch.Tensor
+    # latent KV cache
+    k_nope: torch.Tensor
+    k_rope: torch.Tensor
+    k_scales: torch.Tensor
+    # index key cache
+    idx_k: torch.Tensor
+    idx_k_scale: torch.Tensor
+    # weights of the indexer prolog
+    w_qb: torch.Tensor
+    w_qb_scale: torch.Tensor
+    wk: torch.Tensor
+    w_proj: torch.Tensor
+    ln_gamma: torch.Tensor
+    ln_beta: torch.Tensor
+    hadamard: torch.Tensor
+    # per-step activations (host or device)
+    x: torch.Tensor
+    q_norm: torch.Tensor
+    q_norm_scale: torch.Tensor
+    cos: torch.Tensor
+    sin: torch.Tensor
+    cache_index: torch.Tensor
+    q_nope: torch.Tensor
+    q_rope: torch.Tensor
+
+    @property
+    def t(self):
+        return self.b * self.s1
+
+    @property
+    def max_blocks(self):
+        return self.block_table.shape[1]
+
+
+def sylvester_hadamard(n=128, dtype=torch.bfloat16, device="cpu"):
+    h = torch.ones((1, 1))
+    while h.shape[0] < n:
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    return (h / math.sqrt(n)).to(dtype).to(device)
+
+
+def make_decode_workload(ctx, s1, seed, device, nq=128, block_size=128):
+    """ctx: list of per-request context lengths.  Everything is created on `device`."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    b = len(ctx)
+    t = b * s1
+    bf = torch.bfloat16
+    nblk = [math.ceil(c / block_size) for c in ctx]
+    blocks = sum(nblk)
+    rows = blocks * block_size
+    perm = torch.randperm(blocks, generator=g, device=dev).to(torch.int32)
+    block_table = torch.full((b, max(nblk)), -1, dtype=torch.int32, device=dev)
+    pos = 0
+    for i, n in enumerate(nblk):
+        block_table[i, :n] = perm[pos:pos + n]
+        pos += n
+    act_seq = torch.tensor(ctx, dtype=torch.int32, device=dev)
+
+    def randint8(shape):
+        return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev)
+
+    def randn(shape, std=1.0, dtype=bf):
+        return (torch.randn(shape, generator=g, device=dev) * std).to(dtype)
+
+    k_nope = randint8((rows, 512))
+    k_rope = randn((rows, 64))
+    k_scales = torch.rand((rows, 4), generator=g, device=dev) * 0.019 + 0.001
+    idx_k = randint8((blocks, block_size, 1, 128))
+    idx_k_scale = (torch.rand((blocks, block_size, 1), generator=g, device=dev) * 0.019 + 0.001).to(torch.float16)
+    wq = torch.randn((1536, 8192), generator=g, device=dev) * 0.02
+    wamax = wq.abs().amax(0, keepdim=True)
+    w_qb = torch.round(wq * (127 / wamax)).to(torch.int8)
+    w_qb_scale = (wamax / 127).reshape(8192, 1).float().contiguous()
+    wk = randn((7168, 128), 0.02)
+    w_proj = randn((7168, 64), 0.02)
+    x = randn((t, 7168))
+    qr = torch.randn((t, 1536), generator=g, device=dev)
+    amax = qr.abs().amax(-1, keepdim=True)
+    q_norm = torch.round(qr * (127 / amax)).to(torch.int8)
+    q_norm_scale = (amax / 127).float().contiguous()
+    ang = torch.rand((t, 64), generator=g, device=dev) * 2 * math.pi
+    bt_cpu = block_table.cpu()
+    ci = []
+    for bi, c in enumerate(ctx):
+        for si in range(s1):
+            p = max(c - s1 + si, 0)
+            ci.append(int(bt_cpu[bi, p // block_size]) * block_size + p % block_size)
+    cache_index = torch.tensor(ci, dtype=torch.int64, device=dev)
+    return DecodeWorkload(
+        b=b, s1=s1, ctx=list(ctx), block_table=block_table, act_seq=act_seq, k_nope=k_nope, k_rope=k_rope,
+        k_scales=k_scales, idx_k=idx_k, idx_k_scale=idx_k_scale, w_qb=w_qb, w_qb_scale=w_qb_scale, wk=wk, w_proj=w_proj,
+        ln_gamma=torch.ones(128, dtype=bf, device=dev), ln_beta=torch.zeros(128, dtype=bf, device=dev),
+        hadamard=sylvester_hadamard(128, bf, dev), x=x, q_norm=q_norm, q_norm_scale=q_norm_scale,
+        cos=torch.cos(ang).to(bf), sin=torch.sin(ang).to(bf), cache_index=cache_index,
+        q_nope=randn((t * nq, 512)), q_rope=randn((t * nq, 64)))

@@ -1,0 +1,408 @@
+"""GPU parity tests: the CUDA path (through the Python entry points -> C ABI) against the CPU oracle
+and against the committed reference-golden fixtures.  Tolerances:
+  * indexer int32 dot products: bit-exact;
+  * top-k index sets: equal, ties by lower index; entries within 1e-6 (relative) of the k-th score exempt;
+  * attention output: rtol 1e-2, atol 1e-2 (bf16); max-abs / mean-abs error are reported.  The reference's
+    own test rule (atol 1e-4, rtol 5e-3, <= 0.5 % of elements outside) cannot be met by an online softmax:
+    it rounds P to bf16 before the final normalisation, the golden after it, which flips the last bf16 bit
+    of 3-10 % of the outputs (emulating the online order with torch on the CPU gives the same fraction), and
+    one bf16 ulp is up to 0.78 % > rtol 5e-3.  That fraction is reported and bounded at 15 % as a regression
+    guard, and the mean absolute error must stay below 1 % of the mean output magnitude;
+  * prolog: int8 outputs within 1 LSB, scales / weights atol 2.5e-5 (the reference's test tolerances).
+"""
+import math
+
+import pytest
+import torch
+
+import helpers
+from oracle import dsv32_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _cuda(d):
+    return {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+
+
+# --------------------------------------------------------------------------------------------------
+# top-k
+# --------------------------------------------------------------------------------------------------
+def _run_topk(scores, counts, k, ids=None, id_base=0):
+    import pypto_b200
+    from pypto_b200.lightning_indexer_quant_impl import topk_select
+    oi, os_ = topk_select(scores.to(DEV), counts.to(DEV), k, ids=None if ids is None else ids.to(DEV), id_base=id_base)
+    pypto_b200.check_status()
+    return oi.cpu(), os_.cpu()
+
+
+def test_topk_kat_ties_lower_index_first():
+    kat = helpers.load_kat()["topk_ties"]
+    sc = torch.tensor([kat["input"]], dtype=torch.float32)
+    oi, os_ = _run_topk(sc, torch.tensor([len(kat["input"])], dtype=torch.int32), kat["k"])
+    assert oi[0].tolist() == kat["indices"]
+    assert os_[0].tolist() == [float(v) for v in kat["values"]]
+
+
+@pytest.mark.parametrize("n,k", [(70000, 2048), (5000, 2048), (2048, 2048), (100, 2048), (1, 4), (131072, 2048)])
+def test_topk_random_rows_exact_order(n, k):
+    g = torch.Generator().manual_seed(n + k)
+    rows = 3
+    sc = torch.randn(rows, n, generator=g)
+    sc[1] = torch.randint(0, 50, (n,), generator=g).float()  # heavy ties
+    sc[2] = -sc[2].abs()  # all negative
+    counts = torch.tensor([n, n, max(n - 3, 1)], dtype=torch.int32)
+    oi, os_ = _run_topk(sc, counts, k)
+    for r in range(rows):
+        c = int(counts[r])
+        ref = orc.topk_indices_ref(sc[r, :c], min(k, c))
+        assert oi[r, :ref.numel()].tolist() == ref.tolist(), (r,)
+        assert (oi[r, ref.numel():] == -1).all()
+        assert torch.equal(os_[r, :ref.numel()], sc[r, ref])
+
+
+def test_topk_explicit_ids_merge_rule():
+    g = torch.Generator().manual_seed(9)
+    n, k = 4096, 512
+    sc = torch.randint(0, 200, (2, n), generator=g).float()
+    ids = torch.stack([torch.randperm(100000, generator=g)[:n] for _ in range(2)]).to(torch.int32)
+    ids[0, 5:50] = -1  # ignored entries
+    sc_cpu = sc.clone()
+    sc_cpu[ids < 0] = float("-inf")
+    oi, _ = _run_topk(sc, torch.tensor([n, n], dtype=torch.int32), k, ids=ids)
+    ref = orc.merge_topk_candidates(sc_cpu, ids, k)
+    assert torch.equal(oi, ref)
+
+
+# --------------------------------------------------------------------------------------------------
+# lightning indexer
+# --------------------------------------------------------------------------------------------------
+def _run_indexer(d, selected=2048, want_scores=True, want_dots=False, key_begin=0, key_end=2 ** 31 - 1):
+    import pypto_b200
+    from pypto_b200.lightning_indexer_quant_impl import indexer_scores_topk
+    c = _cuda(d)
+    t = d["query"].shape[0]
+    ld = d["block_table"].shape[1] * 128
+    res = torch.zeros((t, 1, selected), dtype=torch.int32, device=DEV)
+    tsc = torch.zeros((t, selected), dtype=torch.float32, device=DEV)
+    scores = torch.full((t, ld), float("nan"), dtype=torch.float32, device=DEV) if want_scores else None
+    dots = torch.zeros((t, 64, ld), dtype=torch.int32, device=DEV) if want_dots else None
+    indexer_scores_topk(c["query"], c["q_scale"], c["key"], c["k_scale"], c["weights"], c["act_seq"], c["block_table"],
+                        res, selected, topk_scores=tsc, scores_out=scores, dots_out=dots, key_begin=key_begin,
+                        key_end=key_end)
+    pypto_b200.check_status()
+    return res.cpu(), tsc.cpu(), None if scores is None else scores.cpu(), None if dots is None else dots.cpu()
+
+
+def _check_indexer_against_oracle(d, res, scores_gpu, selected=2048):
+    ref, ref_scores = orc.lightning_indexer(d["query"], d["q_scale"], d["key"], d["k_scale"], d["weights"],
+                                            d["act_seq"], d["block_table"], selected, return_scores=True)
+    s1 = d["s1"]
+    for t in range(res.shape[0]):
+        bi, si = divmod(t, s1)
+        L = int(d["act_seq"][bi])
+        eff = L - (s1 - 1 - si)
+        sc_ref = ref_scores[bi][si]
+        if scores_gpu is not None and L > 0:
+            got = scores_gpu[t, :L]
+            assert torch.allclose(got, sc_ref[:L], rtol=2e-6, atol=1e-7), (t, (got - sc_ref[:L]).abs().max())
+        ok, ndiff, nexc = orc.topk_sets_match(res[t, 0], ref[t, 0], sc_ref if eff > 0 else sc_ref)
+        assert ok, (t, ndiff, nexc)
+        nvalid = max(min(eff, selected), 0)
+        assert (res[t, 0, :nvalid] >= 0).all() and (res[t, 0, nvalid:] == -1).all()
+
+
+def test_indexer_reference_golden_fixture():
+    g = helpers.load_indexer_golden()
+    res, _, scores, dots = _run_indexer(g, want_dots=True)
+    # bit-exact int32 dot products
+    for bi in range(g["b"]):
+        L = int(g["act_seq"][bi])
+        rows = orc.paged_rows(g["block_table"][bi], torch.arange(L), 128)
+        keys = g["key"].reshape(-1, 128)[rows].to(torch.int32)
+        for si in range(g["s1"]):
+            t = bi * g["s1"] + si
+            ref = g["query"][t].to(torch.int32) @ keys.t()
+            assert torch.equal(dots[t, :, :L], ref)
+    _check_indexer_against_oracle(g, res, scores)
+    # and directly against the reference's own golden output
+    _, ref_scores = orc.lightning_indexer(g["query"], g["q_scale"], g["key"], g["k_scale"], g["weights"],
+                                          g["act_seq"], g["block_table"], 2048, return_scores=True)
+    for t in range(res.shape[0]):
+        ok, ndiff, _ = orc.topk_sets_match(res[t, 0], g["topk_res"][t, 0], ref_scores[t // g["s1"]][t % g["s1"]])
+        assert ok, (t, ndiff)
+
+
+@pytest.mark.parametrize("act_seq,s1", [([4101, 971, 2048, 129], 1), ([3000, 127, 2049], 2), ([1, 2, 5000], 2),
+                                        ([700, 2500], 4), ([16511], 3)])
+def test_indexer_ragged_vs_oracle(act_seq, s1):
+    d = helpers.gen_indexer_inputs(100 + len(act_seq) + s1, act_seq, s1=s1, extra_blocks=3)
+    res, tsc, scores, _ = _run_indexer(d)
+    _check_indexer_against_oracle(d, res, scores)
+    # rows are sorted by descending score and the reported scores are the scores of the reported keys
+    for t in range(res.shape[0]):
+        n = int((res[t, 0] >= 0).sum())
+        if n:
+            assert (tsc[t, :n - 1] >= tsc[t, 1:n]).all()
+            assert torch.equal(tsc[t, :n], scores[t, res[t, 0, :n].long()])
+
+
+def test_indexer_64k_context_properties_and_sampled_oracle():
+    d = helpers.gen_indexer_inputs(7, [65536, 65536, 40000], s1=2)
+    res, tsc, scores, _ = _run_indexer(d)
+    _check_indexer_against_oracle(d, res, scores)
+    for t in range(res.shape[0]):
+        row = res[t, 0]
+        assert row.min() >= 0 and row.unique().numel() == 2048
+        assert (tsc[t, :-1] >= tsc[t, 1:]).all()
+        eff = int(d["act_seq"][t // 2]) - (1 - t % 2)
+        assert row.max() < eff
+        # every unselected score is <= the smallest selected one
+        mask = torch.ones(eff, dtype=torch.bool)
+        mask[row.long()] = False
+        assert scores[t, :eff][mask].max() <= tsc[t, -1]
+
+
+def test_indexer_key_range_shards_merge_to_global_topk():
+    import pypto_b200
+    from pypto_b200.lightning_indexer_quant_impl import topk_select
+    d = helpers.gen_indexer_inputs(21, [6000], s1=2)
+    full, _, _, _ = _run_indexer(d)
+    shards, k = 3, 2048
+    cs, ci = [], []
+    for s in range(shards):
+        res, tsc, _, _ = _run_indexer(d, want_scores=False, key_begin=s * 2048, key_end=(s + 1) * 2048)
+        cs.append(tsc)
+        ci.append(res[:, 0])
+    cand_s, cand_i = torch.cat(cs, 1), torch.cat(ci, 1).to(torch.int32)
+    counts = torch.full((cand_s.shape[0],), cand_s.shape[1], dtype=torch.int32)
+    oi, _ = topk_select(cand_s.to(DEV), counts.to(DEV), k, ids=cand_i.to(DEV))
+    pypto_b200.check_status()
+    assert torch.equal(oi.cpu(), full[:, 0])
+    assert torch.equal(orc.merge_topk_candidates(cand_s, cand_i, k), full[:, 0])
+
+
+def test_indexer_bad_page_table_sets_status_not_fault():
+    import pypto_b200
+    d = helpers.gen_indexer_inputs(3, [600], s1=1)
+    d["block_table"][0, 1] = -1
+    with pytest.raises(RuntimeError, match="status"):
+        _run_indexer(d, want_scores=False)
+    pypto_b200.check_status()  # cleared
+
+
+# --------------------------------------------------------------------------------------------------
+# sparse flash attention
+# --------------------------------------------------------------------------------------------------
+def _run_sfa(d, kv_splits=0, entry="d"):
+    import pypto_b200
+    from pypto_b200 import sparse_flash_attention_quant_impl as sfa
+    c = _cuda(d)
+    out = torch.full((d["b"], d["s1"], d["nq"], 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cfg = sfa.SaTileShapeConfig()
+    if kv_splits:
+        sfa._sfa(c["q_nope"], c["q_rope"], c["k_nope"], c["k_rope"], c["k_scales"], c["topk_indices"],
+                 c["block_table"], c["act_seq"], out, d["nq"], 1, d["softmax_scale"], d.get("topk", 2048), 128,
+                 d["block_table"].shape[1], cfg, kv_splits=kv_splits)
+    else:
+        fn = {"d": sfa.sparse_flash_attention_quant_d, "p": sfa.sparse_flash_attention_quant_p,
+              "d950": sfa.sparse_flash_attention_quant_d_950}[entry]
+        fn(c["q_nope"], c["q_rope"], c["k_nope"], c["k_rope"], c["k_scales"], c["topk_indices"], c["block_table"],
+           c["act_seq"], out, d["nq"], 1, d["softmax_scale"], d.get("topk", 2048), 128, d["block_table"].shape[1], cfg)
+    pypto_b200.check_status()
+    return out.cpu()
+
+
+def _sfa_oracle(d, tokens=None):
+    return orc.sfa_quant(d["q_nope"], d["q_rope"], d["k_nope"], d["k_rope"], d["k_scales"], d["topk_indices"],
+                         d["block_table"], d["act_seq"], d["nq"], d["softmax_scale"], d.get("topk", 2048), 128,
+                         tokens=tokens)
+
+
+def _assert_attention_close(out, ref):
+    o, r = out.float(), ref.float()
+    assert not torch.isnan(o).any()
+    err = (o - r).abs()
+    assert torch.allclose(o, r, rtol=1e-2, atol=1e-2), f"max-abs {err.max():.4g} mean-abs {err.mean():.4g}"
+    strict = orc.reference_compare_count(out, ref, 1e-4, 5e-3)
+    assert strict <= 0.15 * out.numel(), f"{strict} of {out.numel()} outside the reference's own last-bit rule"
+    assert err.mean() <= 1e-2 * r.abs().mean() + 1e-6, f"mean-abs {err.mean():.4g} vs mean |ref| {r.abs().mean():.4g}"
+    return float(err.max()), float(err.mean())
+
+
+def test_sfa_reference_golden_fixture():
+    g = helpers.load_sfa_golden()
+    out = _run_sfa(g)
+    _assert_attention_close(out, g["out"])
+    _assert_attention_close(out, _sfa_oracle(g))
+
+
+@pytest.mark.parametrize("entry", ["d", "p", "d950"])
+def test_sfa_config0_seeded_vs_oracle(entry):
+    g = torch.Generator().manual_seed(1000)
+    act = torch.randint(2048, 8193, (4,), generator=g).tolist()
+    d = helpers.gen_sfa_inputs(1000, act, s1=1)
+    _assert_attention_close(_run_sfa(d, entry=entry), _sfa_oracle(d))
+
+
+@pytest.mark.parametrize("act_seq,s1", [([15, 666, 2048, 2049], 1), ([1, 33, 5000], 2), ([2047, 100], 4),
+                                        ([0, 300], 1)])
+def test_sfa_ragged_edges_vs_oracle(act_seq, s1):
+    d = helpers.gen_sfa_inputs(77 + s1, act_seq, s1=s1, extra_blocks=2)
+    _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
+
+
+def test_sfa_negative_index_inside_prefix_is_skipped():
+    d = helpers.gen_sfa_inputs(5, [3000], s1=1)
+    d["topk_indices"][0, 10:200] = -1
+    _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+def test_sfa_kv_split_invariance(splits):
+    d = helpers.gen_sfa_inputs(11, [5000, 700], s1=2)
+    ref = _sfa_oracle(d)
+    _assert_attention_close(_run_sfa(d, kv_splits=splits), ref)
+
+
+def test_sfa_full_size_properties_batch64_ctx64k():
+    # BASELINE shapes (batch 64, 64K context, s1=2): the oracle is checked on sampled tokens, the rest
+    # through order-independence (softmax attention does not depend on the order of the selected keys).
+    b, s1, ctx = 64, 2, 65536
+    g = torch.Generator(device=DEV).manual_seed(2)
+    blocks = b * ctx // 128
+    rows = blocks * 128
+    k_nope = torch.randint(-127, 128, (rows, 512), generator=g, dtype=torch.int8, device=DEV)
+    k_rope = torch.randn((rows, 64), generator=g, device=DEV).to(torch.bfloat16)
+    k_scales = torch.rand((rows, 4), generator=g, device=DEV) * 0.019 + 0.001
+    q_nope = torch.randn((b * s1 * 128, 512), generator=g, device=DEV).to(torch.bfloat16)
+    q_rope = torch.randn((b * s1 * 128, 64), generator=g, device=DEV).to(torch.bfloat16)
+    block_table = torch.randperm(blocks, generator=g, device=DEV).to(torch.int32).reshape(b, ctx // 128)
+    act = torch.full((b,), ctx, dtype=torch.int32, device=DEV)
+    idx = torch.stack([torch.randperm(ctx - 1, generator=g, device=DEV)[:2048] for _ in range(b * s1)]).to(torch.int32)
+    from pypto_b200.sparse_flash_attention_quant_impl import sparse_flash_attention_quant_d as sfa_d
+    import pypto_b200
+    scale = 576 ** -0.5
+    out1 = torch.empty((b, s1, 128, 512), dtype=torch.bfloat16, device=DEV)
+    out2 = torch.empty_like(out1)
+    sfa_d(q_nope, q_rope, k_nope, k_rope, k_scales, idx, block_table, act, out1, 128, 1, scale, 2048, 128, ctx // 128)
+    idx2 = idx.flip(1).contiguous()
+    sfa_d(q_nope, q_rope, k_nope, k_rope, k_scales, idx2, block_table, act, out2, 128, 1, scale, 2048, 128, ctx // 128)
+    pypto_b200.check_status()
+    assert not torch.isnan(out1.float()).any()
+    assert torch.allclose(out1.float(), out2.float(), rtol=1e-2, atol=1e-2)
+    # sampled oracle: gather the few rows the sampled tokens touch into a compact CPU cache
+    for tok in (0, 77, 127):
+        bi = tok // s1
+        ids = idx[tok].long()
+        phys = block_table[bi][ids // 128].long() * 128 + ids % 128
+        sub = dict(q_nope=q_nope[tok * 128:(tok + 1) * 128].cpu(), q_rope=q_rope[tok * 128:(tok + 1) * 128].cpu(),
+                   k_nope=k_nope[phys].cpu(), k_rope=k_rope[phys].cpu(), k_scales=k_scales[phys].cpu(),
+                   topk_indices=torch.arange(2048, dtype=torch.int32).reshape(1, -1),
+                   block_table=torch.arange(16, dtype=torch.int32).reshape(1, -1),
+                   act_seq=torch.tensor([2048], dtype=torch.int32), b=1, s1=1, nq=128, softmax_scale=scale)
+        ref = _sfa_oracle(sub)
+        _assert_attention_close(out1[bi, tok % s1].cpu().reshape(1, 1, 128, 512), ref)
+
+
+def test_sfa_rejects_bad_arguments():
+    from pypto_b200.sparse_flash_attention_quant_impl import sparse_flash_attention_quant_d as sfa_d
+    d = _cuda(helpers.gen_sfa_inputs(1, [300], s1=1))
+    out = torch.empty((1, 1, 128, 512), dtype=torch.bfloat16, device=DEV)
+    args = [d["q_nope"], d["q_rope"], d["k_nope"], d["k_rope"], d["k_scales"], d["topk_indices"], d["block_table"],
+            d["act_seq"], out, 128, 1, d["softmax_scale"], 2048, 128, d["block_table"].shape[1], None]
+    bad = list(args)
+    bad[0] = d["q_nope"].float()
+    with pytest.raises(ValueError):
+        sfa_d(*bad)
+    bad = list(args)
+    bad[2] = d["k_nope"].t()
+    with pytest.raises(ValueError):
+        sfa_d(*bad)
+    bad = list(args)
+    bad[5] = d["topk_indices"].cpu()
+    with pytest.raises(RuntimeError):
+        sfa_d(*bad)
+
+
+# --------------------------------------------------------------------------------------------------
+# indexer prolog
+# --------------------------------------------------------------------------------------------------
+def _run_prolog(inp, eps=1e-6):
+    import pypto_b200
+    from pypto_b200 import lightning_indexer_prolog_quant_impl as pl
+    c = _cuda(inp)
+    t = inp["token_x"].shape[0]
+    q_int8 = torch.zeros((t, 64, 128), dtype=torch.int8, device=DEV)
+    q_scale = torch.zeros((t, 64, 1), dtype=torch.float16, device=DEV)
+    weights = torch.zeros((t, 64), dtype=torch.float16, device=DEV)
+    kc, ksc = c["idx_k_cache"].clone(), c["idx_k_scale_cache"].clone()
+    pl.lightning_indexer_prolog_quant(
+        c["token_x"], c["q_norm"], c["q_norm_scale"], c["w_idx_qb"], c["w_idx_qb_scale"], c["w_idx_k"],
+        c["w_idx_proj"], c["layer_norm_gamma"], c["layer_norm_beta"], c["cos_idx_rope"], c["sin_idx_rope"],
+        c["hadamard_q"], c["hadamard_k"], kc, ksc, c["idx_k_cache_index"], q_int8, q_scale, kc, ksc, weights,
+        pl.IndexerPrologQuantConfigs(), pl.IndexerPrologQuantAttr(eps=eps))
+    pypto_b200.check_status()
+    return q_int8.cpu(), q_scale.cpu(), kc.cpu(), ksc.cpu(), weights.cpu()
+
+
+def _assert_prolog_close(got, ref, cache_index):
+    q_i8, q_s, kc, ksc, w = got
+    rq_i8, rq_s, rkc, rksc, rw = ref
+    assert (q_i8.int() - rq_i8.reshape(q_i8.shape).int()).abs().max() <= 1
+    assert (q_i8 != rq_i8.reshape(q_i8.shape)).float().mean() < 0.02
+    assert torch.allclose(q_s.float().reshape(-1), rq_s.float().reshape(-1), atol=2.5e-5, rtol=2e-3)
+    assert (kc.int() - rkc.int()).abs().max() <= 1
+    assert torch.allclose(ksc.float(), rksc.float(), atol=2.5e-5, rtol=2e-3)
+    assert torch.allclose(w.float(), rw.float().reshape(w.shape), atol=2.5e-5, rtol=4e-3)
+    # untouched cache rows are bit-identical
+    mask = torch.ones(kc.reshape(-1, 128).shape[0], dtype=torch.bool)
+    mask[cache_index] = False
+    assert torch.equal(kc.reshape(-1, 128)[mask], rkc.reshape(-1, 128)[mask])
+
+
+def test_prolog_reference_golden_fixture():
+    g = helpers.load_prolog_golden()
+    inp = helpers.prolog_reference_inputs(g["seed"], g["b"], g["s1"], g["s2"])
+    got = _run_prolog(inp)
+    _assert_prolog_close(got, (g["q_int8"], g["q_scale"], g["k_cache"], g["k_scale_cache"], g["weights"]),
+                         inp["idx_k_cache_index"])
+
+
+@pytest.mark.parametrize("t", [1, 16, 37])
+def test_prolog_config1_distributions_vs_oracle(t):
+    g = torch.Generator().manual_seed(1001 + t)
+    bf = torch.bfloat16
+    x = torch.randn((t, 7168), generator=g).to(bf)
+    qr = torch.randn((t, 1536), generator=g)
+    amax = qr.abs().amax(-1, keepdim=True)
+    q_norm = torch.round(qr * (127 / amax)).to(torch.int8)
+    q_norm_scale = (amax / 127).float()
+    wq = torch.randn((1536, 8192), generator=g) * 0.02
+    wamax = wq.abs().amax(0, keepdim=True)
+    w_qb = torch.round(wq * (127 / wamax)).to(torch.int8)
+    w_qb_scale = (wamax / 127).reshape(8192, 1).float()
+    wk = (torch.randn((7168, 128), generator=g) * 0.02).to(bf)
+    w_proj = (torch.randn((7168, 64), generator=g) * 0.02).to(bf)
+    ang = torch.rand((t, 64), generator=g) * 2 * math.pi
+    had = torch.ones((1, 1))
+    while had.shape[0] < 128:
+        had = torch.cat([torch.cat([had, had], 1), torch.cat([had, -had], 1)], 0)
+    had = (had / math.sqrt(128)).to(bf)
+    nblk = 8
+    inp = {
+        "token_x": x, "q_norm": q_norm, "q_norm_scale": q_norm_scale, "w_idx_qb": w_qb, "w_idx_qb_scale": w_qb_scale,
+        "w_idx_k": wk, "w_idx_proj": w_proj, "layer_norm_gamma": (1 + 0.1 * torch.randn(128, generator=g)).to(bf),
+        "layer_norm_beta": (0.1 * torch.randn(128, generator=g)).to(bf), "cos_idx_rope": torch.cos(ang).to(bf),
+        "sin_idx_rope": torch.sin(ang).to(bf), "hadamard_q": had, "hadamard_k": had,
+        "idx_k_cache": torch.randint(-127, 128, (nblk, 128, 1, 128), generator=g, dtype=torch.int8),
+        "idx_k_scale_cache": (torch.rand((nblk, 128, 1, 1), generator=g) * 0.02).to(torch.float16),
+        "idx_k_cache_index": torch.randperm(nblk * 128, generator=g)[:t].to(torch.int64),
+    }
+    ref = orc.indexer_prolog(inp["token_x"], inp["q_norm"], inp["q_norm_scale"], inp["w_idx_qb"], inp["w_idx_qb_scale"],
+                             inp["w_idx_k"], inp["w_idx_proj"], inp["layer_norm_gamma"], inp["layer_norm_beta"],
+                             inp["cos_idx_rope"], inp["sin_idx_rope"], inp["hadamard_q"], inp["hadamard_k"],
+                             inp["idx_k_cache"], inp["idx_k_scale_cache"], inp["idx_k_cache_index"])
+    _assert_prolog_close(_run_prolog(inp), ref, inp["idx_k_cache_index"])
