@@ -114,7 +114,13 @@ int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
     p.part_o = static_cast<float*>(a->workspace);
     p.part_lse = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + o_bytes);
   }
-  return launch_sfa_mma(p, static_cast<cudaStream_t>(cuda_stream));
+  // bring-up switch: DSV32_SFA_IMPL=mma selects the warp-MMA kernel instead of the tcgen05 one
+  static const bool use_mma = [] {
+    const char* e = getenv("DSV32_SFA_IMPL");
+    return e != nullptr && e[0] == 'm';
+  }();
+  if (use_mma || a->n_q != 128) return launch_sfa_mma(p, static_cast<cudaStream_t>(cuda_stream));
+  return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
 // ---- lightning indexer --------------------------------------------------------------------------------

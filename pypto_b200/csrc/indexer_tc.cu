@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
     const int key_in_blk = quarter * 32 + lane;
     for (int i = 0; i < nblk; ++i) {
       const int a = i & 1;
-      if (!mbar_wait(&tfull_bar[a], (i >> 1) & 1, p.status, 5)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[a], (i >> 1) & 1, p.status, 5))) break;
       tc_fence_after();
       const int pos = (blk_begin + i) * bs + key_in_blk;
       const bool in_range = pos < hi && pos >= p.key_begin;
@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }

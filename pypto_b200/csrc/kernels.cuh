@@ -52,6 +52,8 @@ struct SfaParams {
   float scale;
 };
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);
+int launch_sfa_tc(const SfaParams& p, cudaStream_t stream);
+int launch_sfa_combine(const SfaParams& p, cudaStream_t stream);
 
 struct PrologParams {
   const __nv_bfloat16* x;

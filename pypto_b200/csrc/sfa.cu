@@ -336,22 +336,21 @@ __global__ void __launch_bounds__(128) sfa_combine_kernel(const float* part_o, c
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream) {
   const int t = p.b * p.s1;
   if (t <= 0) return DSV32_OK;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(sfa_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSfaSmemBytes);
-    attr_set = true;
-  }
+  cudaFuncSetAttribute(sfa_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSfaSmemBytes);
   dim3 grid(p.nq / kSfaHeads, t, p.splits);
   sfa_mma_kernel<<<grid, kSfaThreads, kSfaSmemBytes, stream>>>(p);
   count_launch();
   int rc = check_launch("sfa_mma_kernel");
   if (rc != DSV32_OK) return rc;
-  if (p.splits > 1) {
-    sfa_combine_kernel<<<t * p.nq, 128, 0, stream>>>(p.part_o, p.part_lse, p.out, p.splits, p.nq);
-    count_launch();
-    rc = check_launch("sfa_combine_kernel");
-  }
+  if (p.splits > 1) rc = launch_sfa_combine(p, stream);
   return rc;
+}
+
+int launch_sfa_combine(const SfaParams& p, cudaStream_t stream) {
+  const int t = p.b * p.s1;
+  sfa_combine_kernel<<<t * p.nq, 128, 0, stream>>>(p.part_o, p.part_lse, p.out, p.splits, p.nq);
+  count_launch();
+  return check_launch("sfa_combine_kernel");
 }
 
 }  // namespace dsv32

@@ -1,0 +1,438 @@
+// Sparse flash attention over the int8 paged latent KV cache on tcgen05 tensor cores (sm_100a).
+// Follows models/deepseek_v32_exp/sparse_flash_attention_quant_impl.py:121-286 (golden:
+// deepseekv32_sparse_flash_attention_quant.py:174-259).
+//
+// One CTA = (token, half of the 512 value dims, key split); M = all 128 query heads.
+// Tensor memory (512 columns x 128 lanes, lane = head):
+//   [  0,256)  O accumulator for this CTA's 256 value dims (fp32)
+//   [256,320)  S buffer 0   (64 keys, fp32) -- after the softmax its first 32 columns hold P (bf16 pairs)
+//   [320,384)  S buffer 1
+//   [384,512)  Q dims 0..255 as bf16 pairs (A operand read straight from tensor memory)
+// Shared memory: Q dims 256..575 (five 128x64 bf16 chunks, 128-byte swizzle, loaded by TMA) and two K
+// stages of 64 gathered keys x 576 dims (nine 64x64 bf16 chunks, 128-byte swizzle).  A stage is read
+// K-major by S = Q K^T and MN-major (as V) by O += P V, so the dequantised rows are written once.
+// Warps: 0 = MMA issuer / tensor-memory owner, 1..4 = softmax + O rescale + epilogue (one head per thread,
+// so row max / row sum need no shuffles), 5..12 = gather + dequantise producers.
+// The running maximum is only raised when a tile exceeds it by more than 2^8 (warp-uniform decision), so
+// the read-modify-write of O in tensor memory is rare; P stays below 2^8 in between.
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace dsv32 {
+
+constexpr int kStThreads = 416;          // 13 warps
+constexpr int kStTile = 64;              // keys per tile
+constexpr int kStChunkBytes = kStTile * 128;       // one 64-dim chunk of a K stage (8 KB)
+constexpr int kStStageBytes = 9 * kStChunkBytes;   // 73,728
+constexpr int kStQChunkBytes = 128 * 128;          // one 64-dim chunk of Q (16 KB)
+constexpr int kStQsBytes = 5 * kStQChunkBytes;     // dims 256..575
+constexpr int kStOffQ = 2 * kStStageBytes;
+constexpr int kStOffValid = kStOffQ + kStQsBytes;  // int[2][64]
+constexpr int kStOffBars = kStOffValid + 2 * kStTile * 4;
+constexpr int kStNumBars = 2 + 2 + 2 + 2 + 1;      // full[2], s_full[2], p_ready[2], pv_done[2], q_ready
+constexpr int kStOffTmem = kStOffBars + kStNumBars * 8;
+constexpr size_t kStSmemBytes = kStOffTmem + 16 + 1024;
+
+constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct StPrefetch {
+  int4 nope[4];
+  int4 rope;
+  float4 sc;
+  bool valid;
+};
+
+__device__ __forceinline__ void st_dequant16(const int4& raw, float sc, uint4& lo, uint4& hi) {
+  const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float f0 = static_cast<float>(static_cast<int8_t>(w[i] & 0xff)) * sc;
+    const float f1 = static_cast<float>(static_cast<int8_t>((w[i] >> 8) & 0xff)) * sc;
+    const float f2 = static_cast<float>(static_cast<int8_t>((w[i] >> 16) & 0xff)) * sc;
+    const float f3 = static_cast<float>(static_cast<int8_t>((w[i] >> 24) & 0xff)) * sc;
+    o[2 * i] = pack_bf16x2(f0, f1);
+    o[2 * i + 1] = pack_bf16x2(f2, f3);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+__global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
+                                                               const __grid_constant__ CUtensorMap qr_map,
+                                                               SfaParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* k_s = smem;
+  unsigned char* q_s = smem + kStOffQ;
+  int* valid_s = reinterpret_cast<int*>(smem + kStOffValid);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStOffBars);
+  uint64_t* full_bar = bars;         // [2] producers -> MMA            (8 warp arrivals)
+  uint64_t* sfull_bar = bars + 2;    // [2] S complete -> softmax       (tcgen05.commit)
+  uint64_t* pready_bar = bars + 4;   // [2] P stored -> MMA             (128 thread arrivals)
+  uint64_t* pvdone_bar = bars + 6;   // [2] PV complete -> producers / MMA / softmax (tcgen05.commit)
+  uint64_t* q_bar = bars + 8;        //     Q in place -> MMA           (TMA tx + 128 thread arrivals)
+  uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + kStOffTmem);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int half = blockIdx.x;  // which 256 value dims
+  const int tok = blockIdx.y;
+  const int split = blockIdx.z;
+  const int bi = tok / p.s1, si = tok % p.s1;
+  const int cnt = min(max(p.act_seq[bi] - p.s1 + 1 + si, 0), p.topk);
+  const int per = (((cnt + p.splits - 1) / p.splits) + kStTile - 1) / kStTile * kStTile;
+  const int k_lo = split * per;
+  const int k_hi = min(cnt, k_lo + per);
+  const int ntiles = (k_hi > k_lo) ? (k_hi - k_lo + kStTile - 1) / kStTile : 0;
+
+  if (ntiles == 0) {  // nothing to attend to: zero row block (uniform for the CTA)
+    for (int i = tid; i < 128 * 64; i += kStThreads) {
+      const int h = i >> 6, c = i & 63;  // 64 chunks of 4 dims
+      if (p.splits == 1) {
+        *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(tok) * p.nq + h) * kKvLora + half * 256 + c * 4) =
+            make_uint2(0u, 0u);
+      } else {
+        const size_t prow = (static_cast<size_t>(tok) * p.splits + split) * p.nq + h;
+        *reinterpret_cast<float4*>(p.part_o + prow * kKvLora + half * 256 + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (half == 0 && c == 0) p.part_lse[prow] = -INFINITY;
+      }
+    }
+    return;
+  }
+
+  // ---- setup -------------------------------------------------------------------------------------------
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&qn_map);
+      tma_prefetch_desc(&qr_map);
+      mbar_init(&full_bar[0], 8);
+      mbar_init(&full_bar[1], 8);
+      mbar_init(&sfull_bar[0], 1);
+      mbar_init(&sfull_bar[1], 1);
+      mbar_init(&pready_bar[0], 128);
+      mbar_init(&pready_bar[1], 128);
+      mbar_init(&pvdone_bar[0], 1);
+      mbar_init(&pvdone_bar[1], 1);
+      mbar_init(q_bar, 129);
+      mbar_fence_init();
+    }
+    __syncwarp();
+    tmem_alloc(tmem_ptr_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_s;
+
+  if (warp == 0) {
+    // ================================ MMA issuer ==========================================================
+    if (lane == 0) {
+      // Q dims 256..575 -> shared memory (TMA, 128-byte swizzle): nope chunks 4..7 and the rope chunk
+      mbar_arrive_expect_tx(q_bar, kStQsBytes);
+      for (int c = 0; c < 4; ++c)
+        tma_load_2d(q_s + c * kStQChunkBytes, &qn_map, (4 + c) * 128, tok * p.nq, q_bar);
+      tma_load_2d(q_s + 4 * kStQChunkBytes, &qr_map, 0, tok * p.nq, q_bar);
+
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, kStTile, false, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 256, false, true);
+      bool ok = mbar_wait(q_bar, 0, p.status, 10);
+
+      auto issue_s = [&](int i) -> bool {
+        const int s = i & 1;
+        if (!mbar_wait(&full_bar[s], (i >> 1) & 1, p.status, 11)) return false;
+        tc_fence_after();
+        const uint32_t stage = smem_u32(k_s + s * kStStageBytes);
+        const uint32_t d = tmem_base + kColS + s * kStTile;
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks)  // Q dims 0..255 from tensor memory
+          umma_f16_ts(d, tmem_base + kColQ + ks * 8,
+                      umma_smem_desc_sw128(stage + (ks >> 2) * kStChunkBytes + (ks & 3) * 32, 16, 1024), idesc_s,
+                      ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 16; ks < 36; ++ks)  // Q dims 256..575 from shared memory
+          umma_f16_ss(d, umma_smem_desc_sw128(smem_u32(q_s) + ((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32, 16, 1024),
+                      umma_smem_desc_sw128(stage + (ks >> 2) * kStChunkBytes + (ks & 3) * 32, 16, 1024), idesc_s, 1u);
+        umma_commit(&sfull_bar[s]);
+        return true;
+      };
+      auto issue_pv = [&](int i) -> bool {
+        const int s = i & 1;
+        if (!mbar_wait(&pready_bar[s], (i >> 1) & 1, p.status, 12)) return false;
+        tc_fence_after();
+        const uint32_t stage = smem_u32(k_s + s * kStStageBytes);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
+          umma_f16_ts(tmem_base + kColO, tmem_base + kColS + s * kStTile + kk * 8,
+                      umma_smem_desc_sw128(stage + (4 * half) * kStChunkBytes + kk * 2048, kStChunkBytes, 1024),
+                      idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&pvdone_bar[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int i = 0; ok && i < ntiles; ++i) {
+        if (i + 1 < ntiles) ok = issue_s(i + 1);
+        if (ok) ok = issue_pv(i);
+      }
+    }
+  } else if (warp <= 4) {
+    // ================================ softmax / epilogue ==================================================
+    const int quarter = warp & 3;
+    const int head = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    // Q dims 0..255 of this head -> tensor memory as bf16 pairs
+    {
+      const uint4* qrow = reinterpret_cast<const uint4*>(p.q_nope + (static_cast<size_t>(tok) * p.nq + head) * kKvLora);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 v = __ldg(qrow + c * 8 + j);
+          r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+        }
+        tmem_st_32x32b_x32(tmem_base + lane_addr + kColQ + c * 32, r);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(q_bar);
+    }
+    const float sc2 = p.scale * 1.4426950408889634f;  // softmax scale in log2 units
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int i = 0; ok && i < ntiles; ++i) {
+      const int s = i & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], (i >> 1) & 1, p.status, 20))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem_base + lane_addr + kColS + s * kStTile;
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(s_addr, r0);
+      tmem_ld_32x32b_x32(s_addr + 32, r1);
+      tmem_ld_wait();
+      const int* vm = valid_s + s * kStTile;
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float t0 = vm[j] ? __uint_as_float(r0[j]) * sc2 : -INFINITY;
+        const float t1 = vm[32 + j] ? __uint_as_float(r1[j]) * sc2 : -INFINITY;
+        r0[j] = __float_as_uint(t0);
+        r1[j] = __float_as_uint(t1);
+        m_tile = fmaxf(m_tile, fmaxf(t0, t1));
+      }
+      const bool need = m_tile > m_run + kRescaleThreshold;  // also true on the first non-empty tile (m_run = -inf)
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_new = need ? m_tile : m_run;
+        const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);  // m_run = -inf -> 0
+        l_run *= alpha;
+        m_run = m_new;
+        if (i > 0) {  // O holds data: scale this head's row (the previous PV must have finished)
+          if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[(i - 1) & 1], ((i - 1) >> 1) & 1, p.status, 21))) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + kColO + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_32x32b_x32(tmem_base + lane_addr + kColO + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      float lsum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = exp2f(__uint_as_float(r0[j]) - m_use), p1 = exp2f(__uint_as_float(r0[j + 1]) - m_use);
+        lsum += p0 + p1;
+        pk[j >> 1] = pack_bf16x2(p0, p1);
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = exp2f(__uint_as_float(r1[j]) - m_use), p1 = exp2f(__uint_as_float(r1[j + 1]) - m_use);
+        lsum += p0 + p1;
+        pk[16 + (j >> 1)] = pack_bf16x2(p0, p1);
+      }
+      l_run += lsum;
+      tmem_st_32x32b_x32(s_addr, pk);  // P (64 keys as 32 bf16 pairs) over the first half of its S buffer
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&pready_bar[s]);
+    }
+    // ---- epilogue: O / l -> bf16 (or fp32 partial + log-sum-exp for a key split) -----------------------------
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pvdone_bar[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, p.status, 22));
+    if (ok) {
+      tc_fence_after();
+      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      if (p.splits == 1) {
+        __nv_bfloat16* orow = p.out + (static_cast<size_t>(tok) * p.nq + head) * kKvLora + half * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + kColO + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + j) = v;
+          }
+        }
+      } else {
+        const size_t prow = (static_cast<size_t>(tok) * p.splits + split) * p.nq + head;
+        float* orow = p.part_o + prow * kKvLora + half * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + kColO + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(orow + c * 32 + j) =
+                make_float4(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv,
+                            __uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+        }
+        if (half == 0)
+          p.part_lse[prow] = (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  } else {
+    // ================================ gather + dequantise producers ========================================
+    const int ptid = tid - 160;            // 0..255
+    const int pwarp_lane0 = (lane == 0);
+    const int gkey = ptid >> 3, gpart = ptid & 7;  // two passes of 32 keys; 16-byte chunks gpart + 8*j
+    const int32_t* idx_row = p.topk_idx + static_cast<size_t>(tok) * p.topk;
+    const int32_t* bt = p.block_table + static_cast<size_t>(bi) * p.max_blocks;
+
+    auto prefetch = [&](int tile, int pass, StPrefetch& pf) {
+      const int j = k_lo + tile * kStTile + pass * 32 + gkey;
+      pf.valid = false;
+      if (j < k_hi) {
+        const int idx = idx_row[j];
+        if (idx >= 0) {
+          const int lb = idx / p.block_size;
+          long long row = -1;
+          if (lb < p.max_blocks) {
+            const int pb = bt[lb];
+            row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
+            if (pb < 0 || row >= p.rows) {
+              report_status(p.status, DSV32_STATUS_BAD_PAGE, bi, lb);
+              row = -1;
+            }
+          } else {
+            report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, j);
+          }
+          if (row >= 0) {
+            pf.valid = true;
+            const int4* src = reinterpret_cast<const int4*>(p.k_nope + row * kKvLora);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) pf.nope[q] = __ldg(src + gpart + 8 * q);
+            pf.rope = __ldg(reinterpret_cast<const int4*>(p.k_rope + row * kRopeDim) + gpart);
+            pf.sc = __ldg(reinterpret_cast<const float4*>(p.k_scales + row * 4));
+          }
+        }
+      }
+    };
+    auto commit = [&](int tile, int pass, const StPrefetch& pf) {
+      const int s = tile & 1;
+      const int r = pass * 32 + gkey;  // row (key) inside the tile
+      unsigned char* stage = k_s + s * kStStageBytes;
+      const float sc[4] = {pf.sc.x, pf.sc.y, pf.sc.z, pf.sc.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (pf.valid) st_dequant16(pf.nope[q], sc[q], lo, hi);
+        const int ci = gpart + 8 * q;   // 16-dim group 0..31
+        const int chunk = ci >> 2;      // 64-dim chunk 0..7
+        const int u0 = (ci & 3) * 2;    // first of two 16-byte units inside the 128-byte line
+        unsigned char* line = stage + chunk * kStChunkBytes + r * 128;
+        *reinterpret_cast<uint4*>(line + ((u0 ^ (r & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(line + (((u0 + 1) ^ (r & 7)) << 4)) = hi;
+      }
+      {
+        unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
+        const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
+        *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
+      }
+      if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
+    };
+
+    StPrefetch pf0, pf1;
+    prefetch(0, 0, pf0);
+    prefetch(0, 1, pf1);
+    for (int i = 0; i < ntiles; ++i) {
+      const int s = i & 1;
+      // the stage is free once the PV MMA of tile i-2 has completed (passes at once for i < 2)
+      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], ((i >> 1) & 1) ^ 1, p.status, 30))) break;
+      commit(i, 0, pf0);
+      commit(i, 1, pf1);
+      if (i + 1 < ntiles) {
+        prefetch(i + 1, 0, pf0);
+        prefetch(i + 1, 1, pf1);
+      }
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
+      __syncwarp();
+      if (pwarp_lane0) mbar_arrive(&full_bar[s]);
+    }
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
+  const int t = p.b * p.s1;
+  if (t <= 0) return DSV32_OK;
+  if (p.nq != 128) {
+    set_error("sfa: the tcgen05 kernel needs n_q == 128 (got %d)", p.nq);
+    return DSV32_ERR_UNSUPPORTED;
+  }
+  CUtensorMap qn_map, qr_map;
+  int rc = make_tensor_map_2d_u8(&qn_map, p.q_nope, static_cast<uint64_t>(t) * p.nq, kKvLora * 2, 128, 128);
+  if (rc != DSV32_OK) return rc;
+  rc = make_tensor_map_2d_u8(&qr_map, p.q_rope, static_cast<uint64_t>(t) * p.nq, kRopeDim * 2, 128, 128);
+  if (rc != DSV32_OK) return rc;
+  cudaFuncSetAttribute(sfa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  dim3 grid(2, t, p.splits);
+  sfa_tc_kernel<<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
+  count_launch();
+  rc = check_launch("sfa_tc_kernel");
+  if (rc == DSV32_OK && p.splits > 1) rc = launch_sfa_combine(p, stream);
+  return rc;
+}
+
+}  // namespace dsv32
