@@ -33,6 +33,13 @@ int check_launch(const char* what) {
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 static int pick_sfa_splits(int t, int nq, int topk, int requested) {
+  if (requested <= 0) {  // DSV32_SFA_KV_SPLITS overrides the automatic choice (profiling knob)
+    static const int env_splits = [] {
+      const char* e = getenv("DSV32_SFA_KV_SPLITS");
+      return e != nullptr ? atoi(e) : 0;
+    }();
+    requested = env_splits;
+  }
   const int max_splits = topk / 128 > 0 ? (topk / 128 < 16 ? topk / 128 : 16) : 1;
   if (requested > 0) return requested < max_splits ? requested : max_splits;
   const int ctas = t * (nq / 64);

@@ -146,8 +146,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
     // ---- epilogue: 4 warps, TMEM lane quarter = warp % 4 ---------------------------------------------------
     const int quarter = warp & 3;
     const int key_in_blk = quarter * 32 + lane;
+    // the key scale of a block is fetched one block ahead so that its latency is not exposed
+    __half ks_next = p.key_scale[static_cast<size_t>(phys_s[0]) * bs + key_in_blk];
     for (int i = 0; i < nblk; ++i) {
       const int a = i & 1;
+      const float ks = __half2float(ks_next);
+      if (i + 1 < nblk) ks_next = p.key_scale[static_cast<size_t>(phys_s[i + 1]) * bs + key_in_blk];
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[a], (i >> 1) & 1, p.status, 5))) break;
       tc_fence_after();
       const int pos = (blk_begin + i) * bs + key_in_blk;
@@ -185,7 +189,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       tc_fence_before();
       mbar_arrive(&tempty_bar[a]);
       if (in_range) {
-        const float ks = __half2float(p.key_scale[static_cast<size_t>(phys_s[i]) * bs + key_in_blk]);
 #pragma unroll
         for (int t = 0; t < TOK; ++t)
           if (t < ntok) p.scores[(row0 + t) * static_cast<size_t>(p.ld) + pos] = acc[t] * ks;

@@ -58,6 +58,12 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       : "memory");
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct StPrefetch {
   int4 nope[4];
   int4 rope;
@@ -66,14 +72,16 @@ struct StPrefetch {
 };
 
 __device__ __forceinline__ void st_dequant16(const int4& raw, float sc, uint4& lo, uint4& hi) {
+  // float(int8) without the conversion pipe: (2^23 + (x ^ 0x80)) as a float, minus (2^23 + 128), is exactly x
   const int w[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t o[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float f0 = static_cast<float>(static_cast<int8_t>(w[i] & 0xff)) * sc;
-    const float f1 = static_cast<float>(static_cast<int8_t>((w[i] >> 8) & 0xff)) * sc;
-    const float f2 = static_cast<float>(static_cast<int8_t>((w[i] >> 16) & 0xff)) * sc;
-    const float f3 = static_cast<float>(static_cast<int8_t>((w[i] >> 24) & 0xff)) * sc;
+    const uint32_t u = static_cast<uint32_t>(w[i]) ^ 0x80808080u;
+    const float f0 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.0f) * sc;
+    const float f1 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.0f) * sc;
+    const float f2 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.0f) * sc;
+    const float f3 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f) * sc;
     o[2 * i] = pack_bf16x2(f0, f1);
     o[2 * i + 1] = pack_bf16x2(f2, f3);
   }
@@ -268,13 +276,13 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       uint32_t pk[32];
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float p0 = exp2f(__uint_as_float(r0[j]) - m_use), p1 = exp2f(__uint_as_float(r0[j + 1]) - m_use);
+        const float p0 = fast_exp2(__uint_as_float(r0[j]) - m_use), p1 = fast_exp2(__uint_as_float(r0[j + 1]) - m_use);
         lsum += p0 + p1;
         pk[j >> 1] = pack_bf16x2(p0, p1);
       }
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float p0 = exp2f(__uint_as_float(r1[j]) - m_use), p1 = exp2f(__uint_as_float(r1[j + 1]) - m_use);
+        const float p0 = fast_exp2(__uint_as_float(r1[j]) - m_use), p1 = fast_exp2(__uint_as_float(r1[j + 1]) - m_use);
         lsum += p0 + p1;
         pk[16 + (j >> 1)] = pack_bf16x2(p0, p1);
       }
@@ -332,33 +340,35 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     const int32_t* idx_row = p.topk_idx + static_cast<size_t>(tok) * p.topk;
     const int32_t* bt = p.block_table + static_cast<size_t>(bi) * p.max_blocks;
 
-    auto prefetch = [&](int tile, int pass, StPrefetch& pf) {
+    // Address resolution is software-pipelined so that no iteration waits on a chain of dependent loads:
+    // index of tile i+3 -> page-table entry of tile i+2 -> row data of tile i+1 -> store of tile i.
+    auto load_idx = [&](int tile, int pass) -> int {
       const int j = k_lo + tile * kStTile + pass * 32 + gkey;
-      pf.valid = false;
-      if (j < k_hi) {
-        const int idx = idx_row[j];
-        if (idx >= 0) {
-          const int lb = idx / p.block_size;
-          long long row = -1;
-          if (lb < p.max_blocks) {
-            const int pb = bt[lb];
-            row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
-            if (pb < 0 || row >= p.rows) {
-              report_status(p.status, DSV32_STATUS_BAD_PAGE, bi, lb);
-              row = -1;
-            }
-          } else {
-            report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, j);
-          }
-          if (row >= 0) {
-            pf.valid = true;
-            const int4* src = reinterpret_cast<const int4*>(p.k_nope + row * kKvLora);
+      return (tile < ntiles && j < k_hi) ? __ldg(idx_row + j) : -1;
+    };
+    auto resolve = [&](int idx, int tile, int pass) -> long long {
+      if (idx < 0) return -1;
+      const int lb = idx / p.block_size;
+      if (lb >= p.max_blocks) {
+        report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, k_lo + tile * kStTile + pass * 32 + gkey);
+        return -1;
+      }
+      const int pb = __ldg(bt + lb);
+      const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
+      if (pb < 0 || row >= p.rows) {
+        report_status(p.status, DSV32_STATUS_BAD_PAGE, bi, lb);
+        return -1;
+      }
+      return row;
+    };
+    auto issue_loads = [&](long long row, StPrefetch& pf) {
+      pf.valid = row >= 0;
+      if (pf.valid) {
+        const int4* src = reinterpret_cast<const int4*>(p.k_nope + row * kKvLora);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) pf.nope[q] = __ldg(src + gpart + 8 * q);
-            pf.rope = __ldg(reinterpret_cast<const int4*>(p.k_rope + row * kRopeDim) + gpart);
-            pf.sc = __ldg(reinterpret_cast<const float4*>(p.k_scales + row * 4));
-          }
-        }
+        for (int q = 0; q < 4; ++q) pf.nope[q] = __ldg(src + gpart + 8 * q);
+        pf.rope = __ldg(reinterpret_cast<const int4*>(p.k_rope + row * kRopeDim) + gpart);
+        pf.sc = __ldg(reinterpret_cast<const float4*>(p.k_scales + row * 4));
       }
     };
     auto commit = [&](int tile, int pass, const StPrefetch& pf) {
@@ -386,8 +396,10 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     };
 
     StPrefetch pf0, pf1;
-    prefetch(0, 0, pf0);
-    prefetch(0, 1, pf1);
+    issue_loads(resolve(load_idx(0, 0), 0, 0), pf0);
+    issue_loads(resolve(load_idx(0, 1), 0, 1), pf1);
+    long long row_n0 = resolve(load_idx(1, 0), 1, 0), row_n1 = resolve(load_idx(1, 1), 1, 1);
+    int idx_nn0 = load_idx(2, 0), idx_nn1 = load_idx(2, 1);
     for (int i = 0; i < ntiles; ++i) {
       const int s = i & 1;
       // the stage is free once the PV MMA of tile i-2 has completed (passes at once for i < 2)
@@ -395,8 +407,12 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       commit(i, 0, pf0);
       commit(i, 1, pf1);
       if (i + 1 < ntiles) {
-        prefetch(i + 1, 0, pf0);
-        prefetch(i + 1, 1, pf1);
+        issue_loads(row_n0, pf0);
+        issue_loads(row_n1, pf1);
+        row_n0 = resolve(idx_nn0, i + 2, 0);
+        row_n1 = resolve(idx_nn1, i + 2, 1);
+        idx_nn0 = load_idx(i + 3, 0);
+        idx_nn1 = load_idx(i + 3, 1);
       }
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
       __syncwarp();
