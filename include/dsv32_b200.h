@@ -98,6 +98,25 @@ size_t dsv32_indexer_workspace_bytes(int32_t b, int32_t s1, int32_t max_blocks, 
 int dsv32_indexer_topk(const Dsv32IndexerArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The same operator for callers that must not allocate device memory (no counterpart in the
+ * reference, whose launcher always allocates its workspace through a callback).  The fp32
+ * score rows -- the operator's only scratch -- are kept in a fixed array inside the library
+ * image, so neither the caller nor the library calls cudaMalloc / cudaFree or any allocating
+ * routine; inputs and outputs are still the caller's.  args.workspace and args.scores_out are
+ * ignored.
+ *   - Limit: b * s1 * max_blocks * block_size <= DSV32_NOALLOC_INDEXER_MAX_SCORES (8 MiB of
+ *     scores); larger problems are rejected with DSV32_ERR_WORKSPACE and a message.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any
+ *     stream capture begins.
+ *   - All calls on a device share the one array, which keeps the previous call's contents
+ *     (nothing in it needs clearing: every score that is read is written first).  Two calls
+ *     that overlap on the GPU (different streams) race on it -- serialise them.
+ * ------------------------------------------------------------------------------------- */
+#define DSV32_NOALLOC_INDEXER_MAX_SCORES 2097152ull
+int dsv32_indexer_topk_noalloc(const Dsv32IndexerArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * Row-wise top-k over fp32 scores (the selection stage alone).
  * Semantics of pypto.topk as used at lightning_indexer_quant_impl.py:179-216; tie rule of
  * framework/src/interface/interpreter/calculator/calc_torch.cpp:2481-2495.

@@ -62,6 +62,7 @@ EXPORTS = {
     "dsv32_sfa_quant": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
     "dsv32_indexer_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
     "dsv32_indexer_topk": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
+    "dsv32_indexer_topk_noalloc": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_indexer_prolog": (c_i32, [C.POINTER(PrologArgs), c_void_p]),
