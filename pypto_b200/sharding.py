@@ -1,0 +1,106 @@
+"""Multi-GPU partitioning of the decode path (one process per GPU, torch.distributed for the plumbing).
+
+* Decode batches shard by request with no collective: `split_even` / `lpt_assign` decide which rank owns
+  which request (each rank keeps its requests' cache pages in its own pool).
+* A single long request shards the index-key RANGE: every rank scores all query tokens against its block
+  range, emits a local top-k with scores, the candidates are all-gathered and every rank re-selects the
+  global top-k (exact: the global top-k is a subset of the union of the local top-ks; ties go to the lower
+  global index).  The reference indexer is single-device (lightning_indexer_quant_impl.py:31-32), so this
+  has no reference counterpart; its result equals the unsharded operator's.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+INT32_MAX = 2 ** 31 - 1
+
+
+def split_even(n_requests: int, world: int) -> List[List[int]]:
+    """Contiguous, as-even-as-possible split of request ids over ranks."""
+    base, rem = divmod(n_requests, world)
+    out, pos = [], 0
+    for r in range(world):
+        n = base + (1 if r < rem else 0)
+        out.append(list(range(pos, pos + n)))
+        pos += n
+    return out
+
+
+def request_cost(ctx_len: int, s1: int = 1, topk: int = 2048) -> float:
+    """Relative cost of one request per decode step: the indexer streams 130 B per key, the attention
+    gathers 656 B for each of min(ctx, topk) keys per query token."""
+    return 130.0 * ctx_len + 656.0 * min(ctx_len, topk) * s1
+
+
+def lpt_assign(costs: Sequence[float], world: int) -> List[List[int]]:
+    """Longest-processing-time-first bin packing of requests onto ranks (ragged production batches)."""
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    loads = [0.0] * world
+    bins: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (loads[j], j))
+        bins[r].append(i)
+        loads[r] += costs[i]
+    for b in bins:
+        b.sort()
+    return bins
+
+
+def key_range_for_rank(max_ctx: int, rank: int, world: int, block_size: int = 128):
+    """Block-aligned logical key range [begin, end) of `rank`; the last rank takes the remainder."""
+    nblk = math.ceil(max_ctx / block_size)
+    per = math.ceil(nblk / world)
+    begin = min(rank * per, nblk) * block_size
+    end = min((rank + 1) * per, nblk) * block_size
+    return begin, (INT32_MAX if rank == world - 1 else end)
+
+
+def _cuda_local_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key, block_table,
+                     selected_count, key_begin, key_end):
+    from .lightning_indexer_quant_impl import indexer_scores_topk
+    t = idx_query.shape[0]
+    res = torch.empty((t, 1, selected_count), dtype=torch.int32, device=idx_query.device)
+    sc = torch.empty((t, selected_count), dtype=torch.float32, device=idx_query.device)
+    indexer_scores_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
+                        block_table, res, selected_count, topk_scores=sc, key_begin=key_begin, key_end=key_end)
+    return res.reshape(t, selected_count), sc
+
+
+def _cuda_merge(cand_scores, cand_ids, k):
+    from .lightning_indexer_quant_impl import topk_select
+    counts = torch.full((cand_scores.shape[0],), cand_scores.shape[1], dtype=torch.int32, device=cand_scores.device)
+    out_idx, _ = topk_select(cand_scores.contiguous(), counts, k, ids=cand_ids.contiguous())
+    return out_idx
+
+
+def sharded_indexer_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
+                         block_table, selected_count: int = 2048, group=None,
+                         local_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None):
+    """Key-range-sharded lightning indexer.  Every rank passes the same query-side tensors and a cache that
+    holds (at least) its own block range; returns topk indices [t, selected_count] int32 (global logical key
+    positions, -1 pads), identical on every rank.
+
+    `local_fn` / `merge_fn` default to the CUDA kernels; the CPU (gloo) tests of the host logic inject
+    stand-ins with the same signatures.
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    local_fn = local_fn or _cuda_local_topk
+    merge_fn = merge_fn or _cuda_merge
+    max_ctx = block_table.shape[1] * 128
+    begin, end = key_range_for_rank(max_ctx, rank, world)
+    idx, sc = local_fn(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key, block_table,
+                       selected_count, begin, end)
+    if world == 1:
+        return idx
+    # one all-gather of (score, index) candidates: selected_count * 8 bytes per token and rank
+    packed = torch.stack([sc.view(torch.int32), idx.to(torch.int32)], dim=0).contiguous()
+    gathered = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(gathered, packed, group=group)
+    cand_sc = torch.cat([g[0].view(torch.float32) for g in gathered], dim=1)
+    cand_id = torch.cat([g[1] for g in gathered], dim=1)
+    return merge_fn(cand_sc, cand_id, selected_count)

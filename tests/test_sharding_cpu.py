@@ -1,0 +1,107 @@
+"""Host-side multi-rank logic on CPU ranks (gloo, world_size 2): request partitioning, the key-range
+sharded indexer with candidate all-gather + merge, and what the healthy rank sees when a peer dies before
+the collective.  The CUDA kernels are replaced by the CPU oracle here; the same flow runs on GPUs in
+tests/test_gpu_parity.py::test_indexer_key_range_shards_merge_to_global_topk."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import helpers
+from oracle import dsv32_oracle as orc
+from pypto_b200 import sharding
+
+
+def test_split_even_and_key_ranges():
+    assert sharding.split_even(10, 4) == [[0, 1, 2], [3, 4, 5], [6, 7], [8, 9]]
+    assert sum(len(x) for x in sharding.split_even(64, 8)) == 64
+    ranges = [sharding.key_range_for_rank(131072, r, 8) for r in range(8)]
+    assert ranges[0] == (0, 16384) and ranges[7][0] == 7 * 16384 and ranges[7][1] == sharding.INT32_MAX
+    # ragged: 1000 keys = 8 blocks over 3 ranks -> 3/3/2 blocks
+    assert [sharding.key_range_for_rank(1000, r, 3)[0] for r in range(3)] == [0, 384, 768]
+
+
+def test_lpt_balances_ragged_batches():
+    g = torch.Generator().manual_seed(4)
+    ctx = torch.exp(torch.rand(256, generator=g) * (torch.log(torch.tensor(131072.0)) - torch.log(torch.tensor(1024.0)))
+                    + torch.log(torch.tensor(1024.0))).long().tolist()
+    costs = [sharding.request_cost(c, 2) for c in ctx]
+    bins = sharding.lpt_assign(costs, 8)
+    assert sorted(i for b in bins for i in b) == list(range(256))
+    loads = [sum(costs[i] for i in b) for b in bins]
+    assert max(loads) / (sum(loads) / 8) < 1.05
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_local(q, qs, kc, ks, w, act, bt, k, begin, end):
+    t, b = q.shape[0], act.shape[0]
+    s1 = t // b
+    scores = orc.indexer_scores(q, qs, kc, ks, w, act, bt, key_offset=begin, key_limit=end)
+    idx = torch.full((t, k), -1, dtype=torch.int32)
+    sc = torch.full((t, k), float("-inf"))
+    for bi in range(b):
+        for si in range(s1):
+            eff = int(act[bi]) - (s1 - 1 - si)
+            n = max(min(eff, end) - begin, 0)
+            if n <= 0:
+                continue
+            row = scores[bi][si, :n]
+            sel = orc.topk_indices_ref(row, min(k, n))
+            idx[bi * s1 + si, :sel.numel()] = (sel + begin).to(torch.int32)
+            sc[bi * s1 + si, :sel.numel()] = row[sel]
+    return idx, sc
+
+
+def _worker(rank, world, port, mode, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    try:
+        d = helpers.gen_indexer_inputs(21, [6000], s1=2)
+        if mode == "die" and rank == 1:
+            raise RuntimeError("rank 1 fails before the collective")
+        out = sharding.sharded_indexer_topk(d["query"], d["q_scale"], d["key"], d["k_scale"], d["weights"], d["act_seq"],
+                                            d["block_table"], 2048, local_fn=_oracle_local,
+                                            merge_fn=orc.merge_topk_candidates)
+        ref = orc.lightning_indexer(d["query"], d["q_scale"], d["key"], d["k_scale"], d["weights"], d["act_seq"],
+                                    d["block_table"], 2048)
+        ret[rank] = "ok" if torch.equal(out, ref[:, 0]) else "mismatch"
+    except Exception as e:  # noqa: BLE001
+        ret[rank] = f"error: {type(e).__name__}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def _run(mode):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert not p.is_alive()
+    return dict(ret)
+
+
+def test_key_range_sharded_indexer_equals_unsharded_world2():
+    assert _run("ok") == {0: "ok", 1: "ok"}
+
+
+def test_rank_failure_surfaces_as_error_on_the_healthy_rank():
+    ret = _run("die")
+    assert ret[1].startswith("error: RuntimeError")
+    assert ret[0].startswith("error")  # the collective ends with an error (peer gone / timeout), it does not hang
