@@ -5,7 +5,7 @@
 //
 // Keys are the M dimension: a 128-key cache block is one 16 KB TMA tile (128-byte swizzle) and one
 // M=128 MMA tile, and every epilogue thread owns one key with all its (token, head) columns, so the head
-// reduction is a sequential fp32 sum in registers (h = 0..63), with no shuffles.
+// reduction is an fp32 sum in registers (four interleaved partial sums, fixed order), with no shuffles.
 // Follows models/deepseek_v32_exp/lightning_indexer_quant_impl.py:114-177 (golden:
 // deepseekv32_lightning_indexer_quant.py:209-242).
 //
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* k_s = smem + TcSmemLayout::keys;
   unsigned char* q_s = smem + TcSmemLayout::q;
-  float* ws_s = reinterpret_cast<float*>(smem + TcSmemLayout::ws);
+  uint32_t* ws_s = reinterpret_cast<uint32_t*>(smem + TcSmemLayout::ws);  // fp16 pairs
   int* phys_s = reinterpret_cast<int*>(smem + TcSmemLayout::phys);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmemLayout::bars);
   uint64_t* full_bar = bars;                       // [kTcStages]
@@ -99,11 +99,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
     tmem_alloc(tmem_ptr_s, kTmemCols);
     tmem_relinquish();
   } else {
-    for (int i = tid - 64; i < N; i += 128) {
-      float w = 0.f;
-      if (i < ntok * 64) w = __half2float(__hmul(p.q_scale[row0 * 64 + i], p.weight[row0 * 64 + i]));
-      ws_s[i] = w;
-    }
+    __half* ws_h = reinterpret_cast<__half*>(ws_s);  // ws = fp16(q_scale * weight), one per (token, head)
+    for (int i = tid - 64; i < N; i += 128)
+      ws_h[i] = (i < ntok * 64) ? __hmul(p.q_scale[row0 * 64 + i], p.weight[row0 * 64 + i]) : __float2half(0.f);
   }
   tc_fence_before();
   __syncthreads();
@@ -156,9 +154,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       tc_fence_after();
       const int pos = (blk_begin + i) * bs + key_in_blk;
       const bool in_range = pos < hi && pos >= p.key_begin;
-      float acc[TOK];
+      // four partial sums per token break the dependent-FMA chain; they are added in a fixed order
+      float acc[TOK][4];
 #pragma unroll
-      for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
+      for (int t = 0; t < TOK; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * N;
 #pragma unroll
       for (int c = 0; c < N / 32; ++c) {
@@ -173,16 +172,25 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
             p.dots[((row0 + t) * 64 + h0 + j) * static_cast<size_t>(p.ld) + pos] = static_cast<int32_t>(r[j]);
         }
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
+        for (int j = 0; j < 32; j += 4) {
           // dot * 2^-11 exactly: (2^23 + 2^22 + dot) as a float, then one FMA
           const float f0 = fmaf(__int_as_float(static_cast<int>(r[j]) + 0x4B400000), 1.f / 2048.f, -6144.f);
           const float f1 = fmaf(__int_as_float(static_cast<int>(r[j + 1]) + 0x4B400000), 1.f / 2048.f, -6144.f);
-          uint32_t pk;  // fp16 round-to-nearest-even with ReLU, two at a time
-          asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(pk) : "f"(f1), "f"(f0));
-          const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&pk));
-          const float2 w = *reinterpret_cast<const float2*>(&ws_s[t * 64 + h0 + j]);
-          acc[t] = fmaf(w.x, rr.x, acc[t]);
-          acc[t] = fmaf(w.y, rr.y, acc[t]);
+          const float f2 = fmaf(__int_as_float(static_cast<int>(r[j + 2]) + 0x4B400000), 1.f / 2048.f, -6144.f);
+          const float f3 = fmaf(__int_as_float(static_cast<int>(r[j + 3]) + 0x4B400000), 1.f / 2048.f, -6144.f);
+          uint32_t pk0, pk1;  // fp16 round-to-nearest-even with ReLU, two at a time
+          asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(pk0) : "f"(f1), "f"(f0));
+          asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(pk1) : "f"(f3), "f"(f2));
+          const uint2 w = *reinterpret_cast<const uint2*>(&ws_s[(t * 64 + h0 + j) >> 1]);  // four fp16 weights
+          // acc(fp32) += r(fp16) * ws(fp16): the product of two fp16 values is exact in fp32
+          asm("{\n\t.reg .b16 rl, rh, wl, wh;\n\t"
+              "mov.b32 {rl, rh}, %2;\n\tmov.b32 {wl, wh}, %3;\n\t"
+              "fma.rn.f32.f16 %0, rl, wl, %0;\n\tfma.rn.f32.f16 %1, rh, wh, %1;\n\t}"
+              : "+f"(acc[t][0]), "+f"(acc[t][1]) : "r"(pk0), "r"(w.x));
+          asm("{\n\t.reg .b16 rl, rh, wl, wh;\n\t"
+              "mov.b32 {rl, rh}, %2;\n\tmov.b32 {wl, wh}, %3;\n\t"
+              "fma.rn.f32.f16 %0, rl, wl, %0;\n\tfma.rn.f32.f16 %1, rh, wh, %1;\n\t}"
+              : "+f"(acc[t][2]), "+f"(acc[t][3]) : "r"(pk1), "r"(w.y));
         }
       }
       // all tcgen05.ld of this accumulator are complete: hand it back to the MMA warp
@@ -191,7 +199,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       if (in_range) {
 #pragma unroll
         for (int t = 0; t < TOK; ++t)
-          if (t < ntok) p.scores[(row0 + t) * static_cast<size_t>(p.ld) + pos] = acc[t] * ks;
+          if (t < ntok)
+            p.scores[(row0 + t) * static_cast<size_t>(p.ld) + pos] = ((acc[t][0] + acc[t][1]) + (acc[t][2] + acc[t][3])) * ks;
       }
     }
   }

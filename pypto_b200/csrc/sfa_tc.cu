@@ -240,16 +240,20 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       tmem_ld_32x32b_x32(s_addr, r0);
       tmem_ld_32x32b_x32(s_addr + 32, r1);
       tmem_ld_wait();
+      // Masking is only needed when the tile holds an invalid key (tail of the list, or a -1 entry).
       const int* vm = valid_s + s * kStTile;
-      float m_tile = -INFINITY;
+      const bool all_valid = __all_sync(0xffffffffu, (vm[lane] & vm[32 + lane]) != 0);
+      if (!all_valid) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float t0 = vm[j] ? __uint_as_float(r0[j]) * sc2 : -INFINITY;
-        const float t1 = vm[32 + j] ? __uint_as_float(r1[j]) * sc2 : -INFINITY;
-        r0[j] = __float_as_uint(t0);
-        r1[j] = __float_as_uint(t1);
-        m_tile = fmaxf(m_tile, fmaxf(t0, t1));
+        for (int j = 0; j < 32; ++j) {
+          if (!vm[j]) r0[j] = 0xff800000u;       // -inf
+          if (!vm[32 + j]) r1[j] = 0xff800000u;
+        }
       }
+      float m_raw = -INFINITY;  // row maximum of the raw scores (the softmax scale is positive)
+#pragma unroll
+      for (int j = 0; j < 32; ++j) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
+      const float m_tile = m_raw * sc2;
       const bool need = m_tile > m_run + kRescaleThreshold;  // also true on the first non-empty tile (m_run = -inf)
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = need ? m_tile : m_run;
@@ -271,21 +275,21 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
           tmem_st_wait();
         }
       }
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      float lsum = 0.f;
+      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+      float lsum0 = 0.f, lsum1 = 0.f;
       uint32_t pk[32];
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const float p0 = fast_exp2(__uint_as_float(r0[j]) - m_use), p1 = fast_exp2(__uint_as_float(r0[j + 1]) - m_use);
-        lsum += p0 + p1;
+      for (int j = 0; j < 32; j += 2) {  // p = 2^(s*scale*log2e - m): one FMA + one ex2 per key
+        const float p0 = fast_exp2(fmaf(__uint_as_float(r0[j]), sc2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(r0[j + 1]), sc2, neg_m));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(r1[j]), sc2, neg_m));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(r1[j + 1]), sc2, neg_m));
+        lsum0 += p0 + p1;
+        lsum1 += p2 + p3;
         pk[j >> 1] = pack_bf16x2(p0, p1);
+        pk[16 + (j >> 1)] = pack_bf16x2(p2, p3);
       }
-#pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const float p0 = fast_exp2(__uint_as_float(r1[j]) - m_use), p1 = fast_exp2(__uint_as_float(r1[j + 1]) - m_use);
-        lsum += p0 + p1;
-        pk[16 + (j >> 1)] = pack_bf16x2(p0, p1);
-      }
+      const float lsum = lsum0 + lsum1;
       l_run += lsum;
       tmem_st_32x32b_x32(s_addr, pk);  // P (64 keys as 32 bf16 pairs) over the first half of its S buffer
       tmem_st_wait();
@@ -341,25 +345,34 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     const int32_t* bt = p.block_table + static_cast<size_t>(bi) * p.max_blocks;
 
     // Address resolution is software-pipelined so that no iteration waits on a chain of dependent loads:
-    // index of tile i+3 -> page-table entry of tile i+2 -> row data of tile i+1 -> store of tile i.
+    //   top-k index of tile i+4 -> page-table entry of tile i+3 -> row number + L2 prefetch of tile i+2
+    //   -> row data of tile i+1 into registers -> dequantise + store tile i.
+    // A value loaded in one iteration is first touched in the next one.
     auto load_idx = [&](int tile, int pass) -> int {
       const int j = k_lo + tile * kStTile + pass * 32 + gkey;
       return (tile < ntiles && j < k_hi) ? __ldg(idx_row + j) : -1;
     };
-    auto resolve = [&](int idx, int tile, int pass) -> long long {
+    auto load_page = [&](int idx) -> int {  // page-table entry of a (possibly invalid) index; -1 = none
       if (idx < 0) return -1;
       const int lb = idx / p.block_size;
-      if (lb >= p.max_blocks) {
-        report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, k_lo + tile * kStTile + pass * 32 + gkey);
-        return -1;
-      }
-      const int pb = __ldg(bt + lb);
+      return (lb < p.max_blocks) ? __ldg(bt + lb) : -2;
+    };
+    auto make_row = [&](int idx, int pb) -> long long {
+      if (idx < 0) return -1;
       const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
       if (pb < 0 || row >= p.rows) {
-        report_status(p.status, DSV32_STATUS_BAD_PAGE, bi, lb);
+        report_status(p.status, pb == -2 ? DSV32_STATUS_BAD_INDEX : DSV32_STATUS_BAD_PAGE, tok, idx);
         return -1;
       }
       return row;
+    };
+    auto l2_prefetch = [&](long long row) {  // the 656 bytes of a row: lanes 0..3 nope lines, 4 rope, 5 scales
+      if (row < 0) return;
+      const void* a = nullptr;
+      if (gpart < 4) a = p.k_nope + row * kKvLora + gpart * 128;
+      else if (gpart == 4) a = p.k_rope + row * kRopeDim;
+      else if (gpart == 5) a = p.k_scales + row * 4;
+      if (a != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
     };
     auto issue_loads = [&](long long row, StPrefetch& pf) {
       pf.valid = row >= 0;
@@ -396,27 +409,42 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     };
 
     StPrefetch pf0, pf1;
-    issue_loads(resolve(load_idx(0, 0), 0, 0), pf0);
-    issue_loads(resolve(load_idx(0, 1), 0, 1), pf1);
-    long long row_n0 = resolve(load_idx(1, 0), 1, 0), row_n1 = resolve(load_idx(1, 1), 1, 1);
-    int idx_nn0 = load_idx(2, 0), idx_nn1 = load_idx(2, 1);
+    {
+      const int i0 = load_idx(0, 0), i1 = load_idx(0, 1);
+      issue_loads(make_row(i0, load_page(i0)), pf0);
+      issue_loads(make_row(i1, load_page(i1)), pf1);
+    }
+    int idx_b0 = load_idx(1, 0), idx_b1 = load_idx(1, 1);
+    long long row_n0 = make_row(idx_b0, load_page(idx_b0)), row_n1 = make_row(idx_b1, load_page(idx_b1));  // tile 1
+    l2_prefetch(row_n0);
+    l2_prefetch(row_n1);
+    idx_b0 = load_idx(2, 0);
+    idx_b1 = load_idx(2, 1);
+    int pb_b0 = load_page(idx_b0), pb_b1 = load_page(idx_b1);   // tile 2
+    int idx_c0 = load_idx(3, 0), idx_c1 = load_idx(3, 1);       // tile 3
     for (int i = 0; i < ntiles; ++i) {
       const int s = i & 1;
       // the stage is free once the PV MMA of tile i-2 has completed (passes at once for i < 2)
       if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], ((i >> 1) & 1) ^ 1, p.status, 30))) break;
       commit(i, 0, pf0);
       commit(i, 1, pf1);
-      if (i + 1 < ntiles) {
-        issue_loads(row_n0, pf0);
-        issue_loads(row_n1, pf1);
-        row_n0 = resolve(idx_nn0, i + 2, 0);
-        row_n1 = resolve(idx_nn1, i + 2, 1);
-        idx_nn0 = load_idx(i + 3, 0);
-        idx_nn1 = load_idx(i + 3, 1);
-      }
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
       __syncwarp();
       if (pwarp_lane0) mbar_arrive(&full_bar[s]);
+      if (i + 1 < ntiles) {
+        issue_loads(row_n0, pf0);                 // tile i+1
+        issue_loads(row_n1, pf1);
+        row_n0 = make_row(idx_b0, pb_b0);         // tile i+2
+        row_n1 = make_row(idx_b1, pb_b1);
+        l2_prefetch(row_n0);
+        l2_prefetch(row_n1);
+        idx_b0 = idx_c0;                          // tile i+3
+        idx_b1 = idx_c1;
+        pb_b0 = load_page(idx_b0);
+        pb_b1 = load_page(idx_b1);
+        idx_c0 = load_idx(i + 4, 0);              // tile i+4
+        idx_c1 = load_idx(i + 4, 1);
+      }
     }
   }
 
