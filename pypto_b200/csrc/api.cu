@@ -237,8 +237,10 @@ int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {
               a->k_cache_index && a->q_int8 && a->q_scale && a->k_cache && a->k_scale_cache && a->weights,
           "prolog: NULL tensor pointer");
   REQUIRE(reinterpret_cast<uintptr_t>(a->q_norm) % 16 == 0 && reinterpret_cast<uintptr_t>(a->w_qb) % 16 == 0 &&
-              reinterpret_cast<uintptr_t>(a->hadamard_q) % 16 == 0 && reinterpret_cast<uintptr_t>(a->hadamard_k) % 16 == 0,
-          "prolog: q_norm / w_qb / hadamard matrices must be 16-byte aligned");
+              reinterpret_cast<uintptr_t>(a->hadamard_q) % 16 == 0 && reinterpret_cast<uintptr_t>(a->hadamard_k) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->x) % 16 == 0 && reinterpret_cast<uintptr_t>(a->wk) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->w_proj) % 16 == 0,
+          "prolog: x / q_norm / weights / hadamard matrices must be 16-byte aligned");
   REQUIRE(a->cache_rows >= 1, "prolog: cache_rows=%lld must be >= 1", static_cast<long long>(a->cache_rows));
   const size_t need = dsv32_prolog_workspace_bytes(a->t);
   if (a->workspace == nullptr || a->workspace_bytes < need) {
@@ -270,7 +272,13 @@ int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {
   p.cache_rows = a->cache_rows;
   p.t = a->t;
   p.eps = a->ln_eps;
-  return launch_prolog(p, static_cast<cudaStream_t>(cuda_stream));
+  // bring-up switch: DSV32_PROLOG_IMPL=simt selects the CUDA-core kernels instead of the tcgen05 ones
+  static const bool use_simt = [] {
+    const char* e = getenv("DSV32_PROLOG_IMPL");
+    return e != nullptr && e[0] == 's';
+  }();
+  if (use_simt) return launch_prolog(p, static_cast<cudaStream_t>(cuda_stream));
+  return launch_prolog_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
 }  // extern "C"

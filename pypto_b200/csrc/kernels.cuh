@@ -82,6 +82,7 @@ struct PrologParams {
   float eps;
 };
 int launch_prolog(const PrologParams& p, cudaStream_t stream);
+int launch_prolog_tc(const PrologParams& p, cudaStream_t stream);
 size_t prolog_workspace_bytes(int t);
 
 

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kKwCols) prolog_kw_partial_kernel(PrologParams
 // ---------------------------------------------------------------------------------------------------
 // Kernel 3: finish K and W paths.  grid = t tokens; 192 threads (128 for K, 64 for W)
 // ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kKwCols) prolog_kw_finish_kernel(PrologParams p) {
+__global__ void __launch_bounds__(kKwCols) prolog_kw_finish_kernel(PrologParams p, int nsplits) {
   __shared__ float v_s[128], r_s[128];
   __shared__ float red_s[4], red2_s[4];
   __shared__ __align__(16) __nv_bfloat16 had_s[128][128];
@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(kKwCols) prolog_kw_finish_kernel(PrologParams 
   for (int c = tid; c < 128 * 16; c += kKwCols)
     *reinterpret_cast<int4*>(&had_s[c / 16][(c % 16) * 8]) = *reinterpret_cast<const int4*>(p.had_k + c * 8);
   float sum = 0.f;
-  for (int kc = 0; kc < kKSplits; ++kc) sum += p.partial[(static_cast<size_t>(kc) * p.t + tok) * kKwCols + tid];
+  for (int kc = 0; kc < nsplits; ++kc) sum += p.partial[(static_cast<size_t>(kc) * p.t + tok) * kKwCols + tid];
 
   if (tid >= 128) {  // W path (no barriers below are skipped: the K path barriers are executed by all threads)
     const float w = __bfloat162float(__float2bfloat16_rn(sum));
@@ -221,6 +221,12 @@ __global__ void __launch_bounds__(kKwCols) prolog_kw_finish_kernel(PrologParams 
   }
 }
 
+int launch_prolog_finish(const PrologParams& p, int splits, cudaStream_t stream) {
+  prolog_kw_finish_kernel<<<p.t, kKwCols, 0, stream>>>(p, splits);
+  count_launch();
+  return check_launch("prolog_kw_finish_kernel");
+}
+
 int launch_prolog(const PrologParams& p, cudaStream_t stream) {
   if (p.t <= 0) return DSV32_OK;
   const int chunks = (p.t + kTokChunk - 1) / kTokChunk;
@@ -232,9 +238,7 @@ int launch_prolog(const PrologParams& p, cudaStream_t stream) {
   count_launch();
   rc = check_launch("prolog_kw_partial_kernel");
   if (rc != DSV32_OK) return rc;
-  prolog_kw_finish_kernel<<<p.t, kKwCols, 0, stream>>>(p);
-  count_launch();
-  return check_launch("prolog_kw_finish_kernel");
+  return launch_prolog_finish(p, kKSplits, stream);
 }
 
 size_t prolog_workspace_bytes(int t) { return static_cast<size_t>(kKSplits) * t * kKwCols * sizeof(float); }
