@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libdsv32_b200.so")
+LIB_PATH = os.environ.get("DSV32_B200_LIB", os.path.join(HERE, "libdsv32_b200.so"))
 
 c_void_p, c_i32, c_i64, c_size_t, c_float = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t, C.c_float
 

@@ -34,6 +34,19 @@ constexpr int kStOffTmem = kStOffBars + kStNumBars * 8;
 constexpr size_t kStSmemBytes = kStOffTmem + 16 + 1024;
 
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;
+
+// Optional pipeline trace (profiling builds only, -DDSV32_SFA_TRACE): SM clock at eight points per tile
+// for the first four CTAs.  Not compiled into the product library.
+#ifdef DSV32_SFA_TRACE
+__device__ unsigned long long g_sfa_trace[4][40][8];
+#define ST_TRACE(tile, slot)                                                                        \
+  do {                                                                                              \
+    const int cta_ = blockIdx.x + 2 * blockIdx.y;                                                   \
+    if (cta_ < 4 && (tile) < 40) g_sfa_trace[cta_][tile][slot] = clock64();                         \
+  } while (0)
+#else
+#define ST_TRACE(tile, slot) do { } while (0)
+#endif
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -147,41 +160,66 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 256, false, true);
       bool ok = mbar_wait(q_bar, 0, p.status, 10);
 
-      auto issue_s = [&](int i) -> bool {
+      // Descriptors are assembled from precomputed 32-bit halves: per MMA only the start-address field moves.
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+      auto desc = [](uint32_t lo) -> uint64_t {
+        uint64_t d;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+        return d;
+      };
+      const uint32_t q_lo = ((smem_u32(q_s) >> 4) & 0x3FFFu) | (1u << 16);
+      uint32_t stage_lo[2], v_lo[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const uint32_t a = smem_u32(k_s + s * kStStageBytes);
+        stage_lo[s] = ((a >> 4) & 0x3FFFu) | (1u << 16);                                              // K-major (S)
+        v_lo[s] = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);  // MN-major (V)
+      }
+
+      auto issue_s = [&](int i) {
         const int s = i & 1;
-        if (!mbar_wait(&full_bar[s], (i >> 1) & 1, p.status, 11)) return false;
+        ST_TRACE(i, 2);
         tc_fence_after();
-        const uint32_t stage = smem_u32(k_s + s * kStStageBytes);
         const uint32_t d = tmem_base + kColS + s * kStTile;
+        const uint32_t klo = stage_lo[s];
 #pragma unroll
         for (int ks = 0; ks < 16; ++ks)  // Q dims 0..255 from tensor memory
-          umma_f16_ts(d, tmem_base + kColQ + ks * 8,
-                      umma_smem_desc_sw128(stage + (ks >> 2) * kStChunkBytes + (ks & 3) * 32, 16, 1024), idesc_s,
-                      ks > 0 ? 1u : 0u);
+          umma_f16_ts(d, tmem_base + kColQ + ks * 8, desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)),
+                      idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
         for (int ks = 16; ks < 36; ++ks)  // Q dims 256..575 from shared memory
-          umma_f16_ss(d, umma_smem_desc_sw128(smem_u32(q_s) + ((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32, 16, 1024),
-                      umma_smem_desc_sw128(stage + (ks >> 2) * kStChunkBytes + (ks & 3) * 32, 16, 1024), idesc_s, 1u);
+          umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
+                      desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
         umma_commit(&sfull_bar[s]);
-        return true;
+        ST_TRACE(i, 3);
       };
-      auto issue_pv = [&](int i) -> bool {
+      auto issue_pv = [&](int i) {
         const int s = i & 1;
-        if (!mbar_wait(&pready_bar[s], (i >> 1) & 1, p.status, 12)) return false;
+        ST_TRACE(i, 4);
         tc_fence_after();
-        const uint32_t stage = smem_u32(k_s + s * kStStageBytes);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
-          umma_f16_ts(tmem_base + kColO, tmem_base + kColS + s * kStTile + kk * 8,
-                      umma_smem_desc_sw128(stage + (4 * half) * kStChunkBytes + kk * 2048, kStChunkBytes, 1024),
+          umma_f16_ts(tmem_base + kColO, tmem_base + kColS + s * kStTile + kk * 8, desc(v_lo[s] + ((kk * 2048) >> 4)),
                       idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&pvdone_bar[s]);
-        return true;
+        ST_TRACE(i, 5);
       };
-      if (ok) ok = issue_s(0);
-      for (int i = 0; ok && i < ntiles; ++i) {
-        if (i + 1 < ntiles) ok = issue_s(i + 1);
-        if (ok) ok = issue_pv(i);
+      // Issue whichever is ready, PV first: finishing PV(i) frees K stage i for the producers, so the
+      // dequantisation of tile i+2 overlaps the S MMAs of tile i+1.  (S(i) never overtakes PV(i-2): the
+      // stage it reads is only refilled after that PV has completed.)
+      int next_s = 0, next_pv = 0;
+      long long t_idle = clock64();
+      while (ok && next_pv < ntiles) {
+        if (next_pv < next_s && mbar_try_wait(&pready_bar[next_pv & 1], (next_pv >> 1) & 1)) {
+          issue_pv(next_pv++);
+          t_idle = clock64();
+        } else if (next_s < ntiles && next_s < next_pv + 2 && mbar_try_wait(&full_bar[next_s & 1], (next_s >> 1) & 1)) {
+          issue_s(next_s++);
+          t_idle = clock64();
+        } else if (clock64() - t_idle > kWaitBudgetCycles) {
+          report_status(p.status, DSV32_STATUS_TIMEOUT, 11, blockIdx.y);
+          ok = false;
+        }
       }
     }
   } else if (warp <= 4) {
@@ -212,6 +250,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     for (int i = 0; ok && i < ntiles; ++i) {
       const int s = i & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], (i >> 1) & 1, p.status, 20))) { ok = false; break; }
+      if (tid == 32) ST_TRACE(i, 6);
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + kColS + s * kStTile;
       uint32_t r0[32], r1[32];
@@ -273,6 +312,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pready_bar[s]);
+      if (tid == 32) ST_TRACE(i, 7);
     }
     // ---- epilogue: O / l -> bf16 (or fp32 partial + log-sum-exp for a key split) -----------------------------
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pvdone_bar[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, p.status, 22));
@@ -382,8 +422,8 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
         const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
         *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
+        if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
       }
-      if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
     };
 
     StPrefetch pf0, pf1;
@@ -404,11 +444,13 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       const int s = i & 1;
       // the stage is free once the PV MMA of tile i-2 has completed (passes at once for i < 2)
       if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], ((i >> 1) & 1) ^ 1, p.status, 30))) break;
+      if (ptid == 0) ST_TRACE(i, 0);
       commit(i, 0, pf0);
       commit(i, 1, pf1);
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
       __syncwarp();
       if (pwarp_lane0) mbar_arrive(&full_bar[s]);
+      if (ptid == 0) ST_TRACE(i, 1);
       if (i + 1 < ntiles) {
         issue_loads(row_n0, pf0);                 // tile i+1
         issue_loads(row_n1, pf1);
@@ -458,3 +500,9 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
 }
 
 }  // namespace dsv32
+
+#ifdef DSV32_SFA_TRACE
+extern "C" int dsv32_debug_sfa_trace(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, dsv32::g_sfa_trace, sizeof(dsv32::g_sfa_trace));
+}
+#endif

@@ -1,10 +1,13 @@
 // Row-wise top-k by block-wide radix select (one CTA per row), followed by a bitonic sort of the
 // selected entries so that rows come out by descending score, equal scores by ascending id.
 //
-// Selection key: 64-bit composite  (sortable(score) << 32) | (0xFFFFFFFF - id).  Digits of 12/12/8 bits
-// are resolved from the top; a pass only histograms entries that match the prefix found so far, and the
-// loop stops as soon as the bucket holding the k-th entry is wholly selected (for distinct scores that is
-// after the three score digits).  Semantics: pypto.topk as used at
+// Selection key: 64-bit composite  (sortable(score) << 32) | (0xFFFFFFFF - id).
+// Fast path (position ids): two scans of the row.  Scan 1 histograms the top 12 key bits; scan 2 sends
+// every entry above the bucket that holds the k-th entry straight to the output list and collects the
+// bucket itself into a shared-memory candidate list, on which the remaining digits (12/8 score bits, then
+// 12/12/8 id bits, early exit) are resolved without touching global memory again.
+// General path (explicit ids, or a candidate list that does not fit): the same digit loop over the row
+// in global memory.  Semantics: pypto.topk as used at
 // models/deepseek_v32_exp/lightning_indexer_quant_impl.py:179-216 with the tie rule of
 // framework/src/interface/interpreter/calculator/calc_torch.cpp:2481-2495.
 #include "kernels.cuh"
@@ -14,7 +17,8 @@ namespace dsv32 {
 constexpr int kTopkThreads = 1024;
 constexpr int kTopkMaxK = 2048;
 constexpr int kHistBins = 4096;
-
+constexpr int kCandCap = 4096;
+constexpr size_t kTopkSmemBytes = kHistBins * 4 + kTopkMaxK * 8 + kCandCap * 8;
 
 __device__ __forceinline__ int row_count(const TopkParams& p, int row, int& col0) {
   if (p.counts != nullptr) {
@@ -56,11 +60,79 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* w
   return wex + inc - v;
 }
 
+struct SelectState {
+  uint64_t prefix, mask;  // an entry is selected iff (key & mask) >= prefix
+  uint32_t k_rem;         // entries still to be taken from the bucket (key & mask) == prefix
+  bool done;
+};
+
+// After a histogram of the current digit has been built over the entries with (key & mask) == prefix:
+// find the bin that holds the k_rem-th entry from the top and narrow the state.  `total` = histogram sum.
+__device__ __forceinline__ void narrow(SelectState& st, const uint32_t* hist, uint32_t* warp_tot, uint32_t* s_tmp,
+                                       int shift, uint32_t dmask, uint32_t& total) {
+  const int tid = threadIdx.x;
+  uint32_t h[4], tsum = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {  // bins are visited from the top: thread t owns descending slots [4t, 4t+4)
+    h[q] = hist[kHistBins - 1 - (4 * tid + q)];
+    tsum += h[q];
+  }
+  uint32_t above = block_exclusive_scan(tsum, warp_tot, total);
+  if (total <= st.k_rem && st.mask == 0) {  // fewer valid entries than k: everything valid is selected
+    st.k_rem = total;
+    st.done = true;
+    return;
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    if (above < st.k_rem && above + h[q] >= st.k_rem) {
+      s_tmp[0] = static_cast<uint32_t>(kHistBins - 1 - (4 * tid + q));
+      s_tmp[1] = above;
+      s_tmp[2] = h[q];
+    }
+    above += h[q];
+  }
+  __syncthreads();
+  st.prefix |= static_cast<uint64_t>(s_tmp[0]) << shift;
+  st.mask |= static_cast<uint64_t>(dmask) << shift;
+  const uint32_t need = st.k_rem - s_tmp[1];
+  st.done = (s_tmp[2] == need);  // the whole bucket is selected
+  st.k_rem = need;
+  __syncthreads();
+}
+
+__constant__ int kShifts[6] = {52, 40, 32, 20, 8, 0};
+__constant__ int kDigitBits[6] = {12, 12, 8, 12, 12, 8};
+
+// Digit loop over an arbitrary entry source: get(j, key) returns false for entries to skip.
+template <class Get>
+__device__ __forceinline__ void radix_passes(SelectState& st, int first_pass, int n, Get get, uint32_t* hist,
+                                             uint32_t* warp_tot, uint32_t* s_tmp) {
+  const int tid = threadIdx.x;
+  for (int pass = first_pass; pass < 6 && !st.done; ++pass) {
+    for (int i = tid; i < kHistBins; i += kTopkThreads) hist[i] = 0;
+    __syncthreads();
+    const int shift = kShifts[pass];
+    const uint32_t dmask = (1u << kDigitBits[pass]) - 1u;
+    for (int j = tid; j < n; j += kTopkThreads) {
+      uint64_t c;
+      if (!get(j, c)) continue;
+      if ((c & st.mask) == st.prefix) atomicAdd(&hist[static_cast<uint32_t>(c >> shift) & dmask], 1u);
+    }
+    __syncthreads();
+    uint32_t total;
+    narrow(st, hist, warp_tot, s_tmp, shift, dmask, total);
+  }
+}
+
 __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p) {
-  __shared__ uint32_t hist[kHistBins];
-  __shared__ uint64_t sel[kTopkMaxK];
+  extern __shared__ __align__(16) unsigned char topk_smem[];
+  uint32_t* hist = reinterpret_cast<uint32_t*>(topk_smem);
+  uint64_t* sel = reinterpret_cast<uint64_t*>(topk_smem + kHistBins * 4);
+  uint64_t* cand = sel + kTopkMaxK;
   __shared__ uint32_t warp_tot[32];
-  __shared__ uint32_t s_bin, s_above, s_bucket, s_nsel;
+  __shared__ uint32_t s_tmp[4];
+  __shared__ uint32_t s_nsel, s_ncand;
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -72,84 +144,85 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   int32_t* orow = p.out_idx + static_cast<size_t>(row) * p.k;
   float* osrow = p.out_scores ? p.out_scores + static_cast<size_t>(row) * p.k : nullptr;
 
-  uint64_t prefix = 0, mask = 0;
-  uint32_t k_rem = static_cast<uint32_t>(min(p.k, n));
-
-  if (n > 0) {
-    const int shifts[6] = {52, 40, 32, 20, 8, 0};
-    const int nbits[6] = {12, 12, 8, 12, 12, 8};
-    for (int pass = 0; pass < 6; ++pass) {
-      for (int i = tid; i < kHistBins; i += kTopkThreads) hist[i] = 0;
-      __syncthreads();
-      const int shift = shifts[pass];
-      const uint32_t dmask = (1u << nbits[pass]) - 1u;
-#pragma unroll 4
-      for (int j = tid; j < n; j += kTopkThreads) {
-        const float s = srow[j];
-        uint32_t id = idb + j;
-        if (irow) {
-          const int32_t v = irow[j];
-          if (v < 0) continue;
-          id = static_cast<uint32_t>(v);
-        }
-        const uint64_t c = composite_key(s, id);
-        if ((c & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(c >> shift) & dmask], 1u);
-      }
-      __syncthreads();
-      // bins are visited from the top: thread t owns descending-order slots [4t, 4t+4)
-      uint32_t h[4], tsum = 0;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        h[q] = hist[kHistBins - 1 - (4 * tid + q)];
-        tsum += h[q];
-      }
-      uint32_t total;
-      uint32_t above = block_exclusive_scan(tsum, warp_tot, total);
-      if (pass == 0 && total <= k_rem) {
-        // fewer valid entries than k: everything valid is selected (mask stays 0)
-        k_rem = total;
-        break;
-      }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        if (above < k_rem && above + h[q] >= k_rem) {
-          s_bin = static_cast<uint32_t>(kHistBins - 1 - (4 * tid + q));
-          s_above = above;
-          s_bucket = h[q];
-        }
-        above += h[q];
-      }
-      __syncthreads();
-      // note: bins above the digit range are empty, so s_bin always lies inside it
-      prefix |= static_cast<uint64_t>(s_bin) << shift;
-      mask |= static_cast<uint64_t>(dmask) << shift;
-      const uint32_t need = k_rem - s_above;  // entries still to take from the selected bucket
-      const bool done = (s_bucket == need);
-      __syncthreads();
-      if (done) break;
-      // entries strictly above the bucket are already decided; keep counting inside the bucket only
-      // (the final emission re-derives membership from prefix/mask, so k_rem is not needed after this)
-      k_rem = need + 0u;
-      // k_rem now counts within the bucket; "above" for later passes is relative to the bucket because
-      // only bucket members are histogrammed.
-    }
+  if (tid == 0) {
+    s_nsel = 0;
+    s_ncand = 0;
   }
+  SelectState st{0, 0, static_cast<uint32_t>(min(p.k, n)), false};
+  auto from_global = [&](int j, uint64_t& c) -> bool {
+    uint32_t id = idb + j;
+    if (irow) {
+      const int32_t v = irow[j];
+      if (v < 0) return false;
+      id = static_cast<uint32_t>(v);
+    }
+    c = composite_key(srow[j], id);
+    return true;
+  };
 
-  // ---- emission: every valid entry whose masked key is >= prefix ------------------------------
-  if (tid == 0) s_nsel = 0;
-  __syncthreads();
-  if (n > 0) {
-#pragma unroll 4
-    for (int j = tid; j < n; j += kTopkThreads) {
-      const float s = srow[j];
-      uint32_t id = idb + j;
-      if (irow) {
-        const int32_t v = irow[j];
-        if (v < 0) continue;
-        id = static_cast<uint32_t>(v);
+  bool emitted = false;
+  if (n > 0 && irow == nullptr) {
+    // ---- fast path: scan 1 = histogram of the top 12 key bits (vectorised when the row is 16-byte aligned) ----
+    for (int i = tid; i < kHistBins; i += kTopkThreads) hist[i] = 0;
+    __syncthreads();
+    const bool vec = (reinterpret_cast<uintptr_t>(srow) & 15) == 0;
+    const int n4 = vec ? (n >> 2) : 0;
+    const float4* srow4 = reinterpret_cast<const float4*>(srow);
+    for (int j = tid; j < n4; j += kTopkThreads) {
+      const float4 v = srow4[j];
+      atomicAdd(&hist[float_to_key(v.x) >> 20], 1u);
+      atomicAdd(&hist[float_to_key(v.y) >> 20], 1u);
+      atomicAdd(&hist[float_to_key(v.z) >> 20], 1u);
+      atomicAdd(&hist[float_to_key(v.w) >> 20], 1u);
+    }
+    for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) atomicAdd(&hist[float_to_key(srow[j]) >> 20], 1u);
+    __syncthreads();
+    uint32_t total;
+    narrow(st, hist, warp_tot, s_tmp, 52, 0xFFFu, total);
+    if (!st.done && s_tmp[2] <= static_cast<uint32_t>(kCandCap)) {
+      // ---- scan 2: winners go to the output list, the threshold bucket to the candidate list ---------------
+      const uint32_t bin = static_cast<uint32_t>(st.prefix >> 52);
+      auto place = [&](float s, int j) {
+        const uint32_t k32 = float_to_key(s);
+        const uint32_t b = k32 >> 20;
+        if (b < bin) return;
+        const uint64_t c = (static_cast<uint64_t>(k32) << 32) | static_cast<uint64_t>(0xFFFFFFFFu - (idb + j));
+        if (b > bin) sel[atomicAdd(&s_nsel, 1u)] = c;
+        else cand[atomicAdd(&s_ncand, 1u)] = c;
+      };
+      for (int j = tid; j < n4; j += kTopkThreads) {
+        const float4 v = srow4[j];
+        place(v.x, 4 * j);
+        place(v.y, 4 * j + 1);
+        place(v.z, 4 * j + 2);
+        place(v.w, 4 * j + 3);
       }
-      const uint64_t c = composite_key(s, id);
-      if ((c & mask) >= prefix) {
+      for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) place(srow[j], j);
+      __syncthreads();
+      const int ncand = static_cast<int>(s_ncand);
+      auto from_cand = [&](int j, uint64_t& c) -> bool {
+        c = cand[j];
+        return true;
+      };
+      radix_passes(st, 1, ncand, from_cand, hist, warp_tot, s_tmp);
+      for (int j = tid; j < ncand; j += kTopkThreads) {
+        const uint64_t c = cand[j];
+        if ((c & st.mask) >= st.prefix) sel[atomicAdd(&s_nsel, 1u)] = c;
+      }
+      emitted = true;
+    } else if (!st.done) {
+      radix_passes(st, 1, n, from_global, hist, warp_tot, s_tmp);  // bucket too large for the candidate list
+    }
+  } else if (n > 0) {
+    radix_passes(st, 0, n, from_global, hist, warp_tot, s_tmp);
+  }
+  __syncthreads();
+  if (n > 0 && !emitted) {
+    // ---- emission: every valid entry whose masked key is >= prefix ---------------------------------------------
+    for (int j = tid; j < n; j += kTopkThreads) {
+      uint64_t c;
+      if (!from_global(j, c)) continue;
+      if ((c & st.mask) >= st.prefix) {
         const uint32_t slot = atomicAdd(&s_nsel, 1u);
         if (slot < kTopkMaxK) sel[slot] = c;
       }
@@ -161,7 +234,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   while (npad < nsel) npad <<= 1;
   for (int i = tid; i < npad; i += kTopkThreads)
     if (i >= nsel) sel[i] = 0ull;
-  // ---- bitonic sort, descending --------------------------------------------------------------
+  // ---- bitonic sort, descending ------------------------------------------------------------------------------
   for (int size = 2; size <= npad; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
       __syncthreads();
@@ -192,7 +265,8 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
 
 int launch_topk(const TopkParams& p, int rows, cudaStream_t stream) {
   if (rows <= 0) return DSV32_OK;
-  topk_select_kernel<<<rows, kTopkThreads, 0, stream>>>(p);
+  cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTopkSmemBytes);
+  topk_select_kernel<<<rows, kTopkThreads, kTopkSmemBytes, stream>>>(p);
   count_launch();
   return check_launch("topk_select_kernel");
 }
