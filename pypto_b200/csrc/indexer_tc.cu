@@ -9,8 +9,9 @@
 // Follows models/deepseek_v32_exp/lightning_indexer_quant_impl.py:114-177 (golden:
 // deepseekv32_lightning_indexer_quant.py:209-242).
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + tensor-memory owner,
-// warps 2..5 = epilogue (one TMEM lane quarter each).  Key blocks go through a 4-stage shared-memory ring;
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer + tensor-memory owner, then the epilogue warps
+// (one TMEM lane quarter each; with two or more tokens per CTA there are eight of them and the two warps of
+// a quarter split the tokens, which doubles the warps available to hide latency).  Key blocks go through a 4-stage shared-memory ring;
 // the accumulator is double-buffered in tensor memory so the epilogue of block i overlaps the MMA of i+1.
 #include <mutex>
 
@@ -19,7 +20,6 @@
 
 namespace dsv32 {
 
-constexpr int kTcThreads = 192;
 constexpr int kTcStages = 4;
 constexpr int kTcBlocksPerCta = 32;
 constexpr int kKeyTileBytes = 128 * 128;
@@ -38,10 +38,19 @@ struct TcSmemLayout {
 constexpr size_t kTcSmemBytes = TcSmemLayout::total + 1024;  // slack for manual 1024-byte alignment
 
 template <int TOK>
-__global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap key_map,
+struct TcShape {
+  static constexpr int kEpilogueWarps = TOK >= 2 ? 8 : 4;
+  static constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+  static constexpr int kTokPerWarp = TOK / (kEpilogueWarps / 4);  // tokens handled by one epilogue warp
+};
+
+template <int TOK>
+__global__ void __launch_bounds__(TcShape<TOK>::kThreads, 2) indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap key_map,
                                                                       const __grid_constant__ CUtensorMap q_map,
                                                                       IndexerParams p) {
   constexpr int N = 64 * TOK;
+  constexpr int kEpThreads = 32 * TcShape<TOK>::kEpilogueWarps;
+  constexpr int TPW = TcShape<TOK>::kTokPerWarp;
   constexpr uint32_t kTmemCols = 2 * N < 32 ? 32 : 2 * N;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -90,8 +99,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       }
       mbar_init(&tfull_bar[0], 1);
       mbar_init(&tfull_bar[1], 1);
-      mbar_init(&tempty_bar[0], 128);
-      mbar_init(&tempty_bar[1], 128);
+      mbar_init(&tempty_bar[0], kEpThreads);
+      mbar_init(&tempty_bar[1], kEpThreads);
       mbar_init(q_bar, 1);
       mbar_fence_init();
     }
@@ -100,7 +109,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
     tmem_relinquish();
   } else {
     __half* ws_h = reinterpret_cast<__half*>(ws_s);  // ws = fp16(q_scale * weight), one per (token, head)
-    for (int i = tid - 64; i < N; i += 128)
+    for (int i = tid - 64; i < N; i += kEpThreads)
       ws_h[i] = (i < ntok * 64) ? __hmul(p.q_scale[row0 * 64 + i], p.weight[row0 * 64 + i]) : __float2half(0.f);
   }
   tc_fence_before();
@@ -141,8 +150,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       }
     }
   } else {
-    // ---- epilogue: 4 warps, TMEM lane quarter = warp % 4 ---------------------------------------------------
+    // ---- epilogue: TMEM lane quarter = warp % 4; warp group (warp - 2) / 4 owns tokens [tg*TPW, tg*TPW + TPW) ----
     const int quarter = warp & 3;
+    const int tg = (warp - 2) >> 2;
     const int key_in_blk = quarter * 32 + lane;
     // the key scale of a block is fetched one block ahead so that its latency is not exposed
     __half ks_next = p.key_scale[static_cast<size_t>(phys_s[0]) * bs + key_in_blk];
@@ -155,17 +165,18 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       const int pos = (blk_begin + i) * bs + key_in_blk;
       const bool in_range = pos < hi && pos >= p.key_begin;
       // four partial sums per token break the dependent-FMA chain; they are added in a fixed order
-      float acc[TOK][4];
+      float acc[TPW][4];
 #pragma unroll
-      for (int t = 0; t < TOK; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * N;
+      for (int t = 0; t < TPW; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * N + tg * TPW * 64;
 #pragma unroll
-      for (int c = 0; c < N / 32; ++c) {
+      for (int c = 0; c < TPW * 2; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
-        const int t = (c * 32) / 64;
-        const int h0 = (c * 32) % 64;
+        const int tl = c >> 1;               // token within this warp's group
+        const int t = tg * TPW + tl;         // token within the CTA
+        const int h0 = (c & 1) * 32;
         if (p.dots != nullptr && in_range && t < ntok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -186,11 +197,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
           asm("{\n\t.reg .b16 rl, rh, wl, wh;\n\t"
               "mov.b32 {rl, rh}, %2;\n\tmov.b32 {wl, wh}, %3;\n\t"
               "fma.rn.f32.f16 %0, rl, wl, %0;\n\tfma.rn.f32.f16 %1, rh, wh, %1;\n\t}"
-              : "+f"(acc[t][0]), "+f"(acc[t][1]) : "r"(pk0), "r"(w.x));
+              : "+f"(acc[tl][0]), "+f"(acc[tl][1]) : "r"(pk0), "r"(w.x));
           asm("{\n\t.reg .b16 rl, rh, wl, wh;\n\t"
               "mov.b32 {rl, rh}, %2;\n\tmov.b32 {wl, wh}, %3;\n\t"
               "fma.rn.f32.f16 %0, rl, wl, %0;\n\tfma.rn.f32.f16 %1, rh, wh, %1;\n\t}"
-              : "+f"(acc[t][2]), "+f"(acc[t][3]) : "r"(pk1), "r"(w.y));
+              : "+f"(acc[tl][2]), "+f"(acc[tl][3]) : "r"(pk1), "r"(w.y));
         }
       }
       // all tcgen05.ld of this accumulator are complete: hand it back to the MMA warp
@@ -198,9 +209,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) indexer_scores_tc_kernel(const 
       mbar_arrive(&tempty_bar[a]);
       if (in_range) {
 #pragma unroll
-        for (int t = 0; t < TOK; ++t)
-          if (t < ntok)
-            p.scores[(row0 + t) * static_cast<size_t>(p.ld) + pos] = ((acc[t][0] + acc[t][1]) + (acc[t][2] + acc[t][3])) * ks;
+        for (int tl = 0; tl < TPW; ++tl)
+          if (tg * TPW + tl < ntok)
+            p.scores[(row0 + tg * TPW + tl) * static_cast<size_t>(p.ld) + pos] =
+                ((acc[tl][0] + acc[tl][1]) + (acc[tl][2] + acc[tl][3])) * ks;
       }
     }
   }
@@ -262,7 +274,7 @@ static int launch_tc(const IndexerParams& p, const CUtensorMap& key_map, dim3 gr
   int rc = make_tensor_map_2d_u8(&q_map, p.q, q_rows, 128, 64 * TOK, 128);
   if (rc != DSV32_OK) return rc;
   cudaFuncSetAttribute(indexer_scores_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
-  indexer_scores_tc_kernel<TOK><<<grid, kTcThreads, kTcSmemBytes, stream>>>(key_map, q_map, p);
+  indexer_scores_tc_kernel<TOK><<<grid, TcShape<TOK>::kThreads, kTcSmemBytes, stream>>>(key_map, q_map, p);
   count_launch();
   return check_launch("indexer_scores_tc_kernel");
 }

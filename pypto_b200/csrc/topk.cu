@@ -168,12 +168,27 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
     const bool vec = (reinterpret_cast<uintptr_t>(srow) & 15) == 0;
     const int n4 = vec ? (n >> 2) : 0;
     const float4* srow4 = reinterpret_cast<const float4*>(srow);
-    for (int j = tid; j < n4; j += kTopkThreads) {
-      const float4 v = srow4[j];
-      atomicAdd(&hist[float_to_key(v.x) >> 20], 1u);
-      atomicAdd(&hist[float_to_key(v.y) >> 20], 1u);
-      atomicAdd(&hist[float_to_key(v.z) >> 20], 1u);
-      atomicAdd(&hist[float_to_key(v.w) >> 20], 1u);
+    {
+      int j = tid;
+      for (; j + 3 * kTopkThreads < n4; j += 4 * kTopkThreads) {  // four independent loads in flight per thread
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = srow4[j + u * kTopkThreads];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          atomicAdd(&hist[float_to_key(v[u].x) >> 20], 1u);
+          atomicAdd(&hist[float_to_key(v[u].y) >> 20], 1u);
+          atomicAdd(&hist[float_to_key(v[u].z) >> 20], 1u);
+          atomicAdd(&hist[float_to_key(v[u].w) >> 20], 1u);
+        }
+      }
+      for (; j < n4; j += kTopkThreads) {
+        const float4 v = srow4[j];
+        atomicAdd(&hist[float_to_key(v.x) >> 20], 1u);
+        atomicAdd(&hist[float_to_key(v.y) >> 20], 1u);
+        atomicAdd(&hist[float_to_key(v.z) >> 20], 1u);
+        atomicAdd(&hist[float_to_key(v.w) >> 20], 1u);
+      }
     }
     for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) atomicAdd(&hist[float_to_key(srow[j]) >> 20], 1u);
     __syncthreads();
@@ -190,12 +205,28 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
         if (b > bin) sel[atomicAdd(&s_nsel, 1u)] = c;
         else cand[atomicAdd(&s_ncand, 1u)] = c;
       };
-      for (int j = tid; j < n4; j += kTopkThreads) {
-        const float4 v = srow4[j];
-        place(v.x, 4 * j);
-        place(v.y, 4 * j + 1);
-        place(v.z, 4 * j + 2);
-        place(v.w, 4 * j + 3);
+      {
+        int j = tid;
+        for (; j + 3 * kTopkThreads < n4; j += 4 * kTopkThreads) {
+          float4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = srow4[j + u * kTopkThreads];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = 4 * (j + u * kTopkThreads);
+            place(v[u].x, e);
+            place(v[u].y, e + 1);
+            place(v[u].z, e + 2);
+            place(v[u].w, e + 3);
+          }
+        }
+        for (; j < n4; j += kTopkThreads) {
+          const float4 v = srow4[j];
+          place(v.x, 4 * j);
+          place(v.y, 4 * j + 1);
+          place(v.z, 4 * j + 2);
+          place(v.w, 4 * j + 3);
+        }
       }
       for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) place(srow[j], j);
       __syncthreads();
