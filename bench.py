@@ -53,6 +53,13 @@ def indexer_bytes_per_request(ctx, s1):
     return ctx * 130 + ((ctx + 127) // 128) * 4 + s1 * (8192 + 128 + 128) + s1 * 8192
 
 
+# DRAM traffic per unit from the ncu capture summarised in profiles/tcgen05_kernels_b16_ctx64k.md
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch / units of that launch); it grows in proportion
+# to the units, so a full launch is units x this figure.
+NCU_SFA_TRAFFIC_PER_TOKEN = (51.919872e6 + 0.655360e6) / 32
+NCU_INDEXER_TRAFFIC_PER_REQUEST = (136.647680e6 + 6.585344e6) / 16
+
+
 def prolog_bytes_per_call(t):
     return 15433728 + t * (14336 + 1536 + 4 + 256 + 8) + t * (8192 + 128 + 130 + 128)
 
@@ -273,14 +280,18 @@ def run_ours(args, rank, world, local_rank):
                     "achieved_gbs": sfa_bytes / t_sfa / 1e9, "hbm_frac": sfa_bytes / t_sfa / 1e9 / peaks["hbm_gbs"]},
         }
         if t_sfa >= t_index:
-            roofline = {"kernel": "sfa_mma_kernel", "bound": "tensor", "achieved": sfa_flops / t_sfa / 1e12,
+            roofline = {"kernel": "sfa_tc_kernel", "bound": "tensor", "achieved": sfa_flops / t_sfa / 1e12,
                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                        "frac": sfa_flops / t_sfa / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,
+                        "frac": sfa_flops / t_sfa / 1e12 / peaks["bf16_tflops_sustained"],
+                        "traffic": NCU_SFA_TRAFFIC_PER_TOKEN * tokens_per_rank if args.ctx == 65536 else None,
+                        "algorithmic_bytes": sfa_bytes,
                         "peak_source": peaks["source"] + " (sustained bf16)"}
         else:
-            roofline = {"kernel": "indexer scores + top-k stage", "bound": "hbm", "achieved": idx_bytes / t_index / 1e9,
-                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": idx_bytes / t_index / 1e9 / peaks["hbm_gbs"],
-                        "traffic": None, "peak_source": peaks["source"]}
+            roofline = {"kernel": "indexer_scores_tc_kernel + topk_select_kernel", "bound": "hbm",
+                        "achieved": idx_bytes / t_index / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": idx_bytes / t_index / 1e9 / peaks["hbm_gbs"],
+                        "traffic": NCU_INDEXER_TRAFFIC_PER_REQUEST * per_rank if args.ctx == 65536 else None,
+                        "algorithmic_bytes": idx_bytes, "peak_source": peaks["source"]}
         # CPU baseline on a bounded sample of the same workload (rank 0, N=1 only)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
@@ -292,7 +303,7 @@ def run_ours(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "warmup_steps_run": n_warm,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "stages": stage_info,
             "cpu_baseline": cpu,
