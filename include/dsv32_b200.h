@@ -174,6 +174,43 @@ typedef struct {
 size_t dsv32_prolog_workspace_bytes(int32_t t);
 int dsv32_indexer_prolog(const Dsv32PrologArgs* args, void* cuda_stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Fused element-wise stages of the MLA prolog (quant), the MLA half of
+ * mla_indexer_prolog_quant_d / _p
+ * (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:112-211,486-528; helpers
+ * mla_prolog_quant_impl.py:96-361).  The plain projections between the stages are library
+ * GEMMs issued by the host layer (pypto_b200/mla_indexer_prolog_quant_impl.py).
+ *   stage 0: q_a -> RMSNorm(gamma_cq) -> bf16 -> per-token int8 -> q_norm, q_norm_scale
+ *   stage 1: q_b int32 -> * q_norm_scale * w_qb_scale -> bf16; nope -> q_nope_tmp [128][t][128],
+ *            rope -> de-interleave + RoPE -> q_rope [t,128,64]
+ *   stage 2: kv_a -> RMSNorm(gamma_ckv) -> 4 x 128-dim int8 groups + fp32 scales -> kv_cache /
+ *            k_scale_cache at rows cache_index; last 64 dims -> de-interleave + RoPE -> kr_cache
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q_a;                /* stage 0: bf16 [t, 1536]                         */
+  const void* gamma_cq;           /* bf16 [1536]                                     */
+  int8_t* q_norm;                 /* stage 0 out: int8 [t, 1536]                     */
+  float* q_norm_scale;            /* stage 0 out / stage 1 in: fp32 [t]              */
+  const int32_t* q_b;             /* stage 1: int32 [t, q_b_ld], first 24576 columns */
+  const float* w_qb_scale;        /* fp32 [24576]                                    */
+  void* q_nope_tmp;               /* stage 1 out: bf16 [128, t, 128]                 */
+  void* q_rope;                   /* stage 1 out: bf16 [t, 128, 64]                  */
+  const void* kv_a;               /* stage 2: bf16 [t, 576]                          */
+  const void* gamma_ckv;          /* bf16 [512]                                      */
+  const void* cos;                /* bf16 [t, 64]                                    */
+  const void* sin;                /* bf16 [t, 64]                                    */
+  const int64_t* cache_index;     /* int64 [t]                                       */
+  int8_t* kv_cache;               /* in/out int8 [cache_rows, 512]                   */
+  void* kr_cache;                 /* in/out bf16 [cache_rows, 64]                    */
+  float* k_scale_cache;           /* in/out fp32 [cache_rows, 4]                     */
+  uint32_t* status;
+  int64_t cache_rows;
+  int32_t t, q_b_ld;
+  float eps_cq, eps_ckv;
+} Dsv32MlaStageArgs;
+
+int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* args, int32_t stage, void* cuda_stream);
+
 /* library-wide */
 int dsv32_abi_version(void);
 const char* dsv32_last_error(void);

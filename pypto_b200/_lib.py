@@ -53,6 +53,16 @@ class PrologArgs(C.Structure):
     ]
 
 
+class MlaStageArgs(C.Structure):
+    _fields_ = [
+        ("q_a", c_void_p), ("gamma_cq", c_void_p), ("q_norm", c_void_p), ("q_norm_scale", c_void_p), ("q_b", c_void_p),
+        ("w_qb_scale", c_void_p), ("q_nope_tmp", c_void_p), ("q_rope", c_void_p), ("kv_a", c_void_p),
+        ("gamma_ckv", c_void_p), ("cos", c_void_p), ("sin", c_void_p), ("cache_index", c_void_p), ("kv_cache", c_void_p),
+        ("kr_cache", c_void_p), ("k_scale_cache", c_void_p), ("status", c_void_p), ("cache_rows", c_i64), ("t", c_i32),
+        ("q_b_ld", c_i32), ("eps_cq", c_float), ("eps_ckv", c_float),
+    ]
+
+
 # every symbol include/dsv32_b200.h declares: name -> (restype, argtypes)
 EXPORTS = {
     "dsv32_abi_version": (c_i32, []),
@@ -66,6 +76,7 @@ EXPORTS = {
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_indexer_prolog": (c_i32, [C.POINTER(PrologArgs), c_void_p]),
+    "dsv32_mla_prolog_stage": (c_i32, [C.POINTER(MlaStageArgs), c_i32, c_void_p]),
 }
 
 ABI_VERSION = 1

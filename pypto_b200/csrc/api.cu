@@ -281,4 +281,45 @@ int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {
   return launch_prolog_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
+// ---- MLA prolog stages ----------------------------------------------------------------------------------
+int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* a, int32_t stage, void* cuda_stream) {
+  REQUIRE(a != nullptr, "mla: args is NULL");
+  REQUIRE(stage >= 0 && stage <= 2, "mla: stage=%d must be 0, 1 or 2", stage);
+  REQUIRE(a->t >= 0, "mla: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  if (stage == 0) REQUIRE(a->q_a && a->gamma_cq && a->q_norm && a->q_norm_scale, "mla stage 0: NULL tensor pointer");
+  if (stage == 1)
+    REQUIRE(a->q_b && a->q_norm_scale && a->w_qb_scale && a->q_nope_tmp && a->q_rope && a->cos && a->sin &&
+                a->q_b_ld >= 24576,
+            "mla stage 1: NULL tensor pointer or q_b_ld=%d < 24576", a->q_b_ld);
+  if (stage == 2)
+    REQUIRE(a->kv_a && a->gamma_ckv && a->cos && a->sin && a->cache_index && a->kv_cache && a->kr_cache &&
+                a->k_scale_cache && a->cache_rows >= 1,
+            "mla stage 2: NULL tensor pointer or empty cache");
+  MlaStageParams p{};
+  p.q_a = static_cast<const __nv_bfloat16*>(a->q_a);
+  p.gamma_cq = static_cast<const __nv_bfloat16*>(a->gamma_cq);
+  p.q_norm = a->q_norm;
+  p.q_norm_scale = a->q_norm_scale;
+  p.q_b = a->q_b;
+  p.w_qb_scale = a->w_qb_scale;
+  p.q_nope_tmp = static_cast<__nv_bfloat16*>(a->q_nope_tmp);
+  p.q_rope = static_cast<__nv_bfloat16*>(a->q_rope);
+  p.kv_a = static_cast<const __nv_bfloat16*>(a->kv_a);
+  p.gamma_ckv = static_cast<const __nv_bfloat16*>(a->gamma_ckv);
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos);
+  p.sin = static_cast<const __nv_bfloat16*>(a->sin);
+  p.cache_index = reinterpret_cast<const long long*>(a->cache_index);
+  p.kv_cache = a->kv_cache;
+  p.kr_cache = static_cast<__nv_bfloat16*>(a->kr_cache);
+  p.k_scale_cache = a->k_scale_cache;
+  p.status = a->status;
+  p.cache_rows = a->cache_rows;
+  p.t = a->t;
+  p.q_b_ld = a->q_b_ld;
+  p.eps_cq = a->eps_cq;
+  p.eps_ckv = a->eps_ckv;
+  return launch_mla_stage(p, stage, static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

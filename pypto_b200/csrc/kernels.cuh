@@ -86,4 +86,28 @@ int launch_prolog_tc(const PrologParams& p, cudaStream_t stream);
 size_t prolog_workspace_bytes(int t);
 
 
+struct MlaStageParams {
+  const __nv_bfloat16* q_a;
+  const __nv_bfloat16* gamma_cq;
+  int8_t* q_norm;
+  float* q_norm_scale;
+  const int32_t* q_b;
+  const float* w_qb_scale;
+  __nv_bfloat16* q_nope_tmp;
+  __nv_bfloat16* q_rope;
+  const __nv_bfloat16* kv_a;
+  const __nv_bfloat16* gamma_ckv;
+  const __nv_bfloat16* cos;
+  const __nv_bfloat16* sin;
+  const long long* cache_index;
+  int8_t* kv_cache;
+  __nv_bfloat16* kr_cache;
+  float* k_scale_cache;
+  uint32_t* status;
+  long long cache_rows;
+  int t, q_b_ld;
+  float eps_cq, eps_ckv;
+};
+int launch_mla_stage(const MlaStageParams& p, int stage, cudaStream_t stream);
+
 }  // namespace dsv32

@@ -15,6 +15,7 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
   sfa_small.npz      inputs + output of compute_attention_no_flash
   indexer_small.npz  inputs + topk_res of lightning_indexer_compute (+ oracle scores)
   prolog_small.npz   seed + input digests + outputs of indexer_prolog
+  mla_small.npz      seed + input digests + outputs of mla_prolog_quant_v32_compute
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -168,6 +169,36 @@ def make_prolog():
     print("prolog_small: q_int8", tuple(out["query"].shape))
 
 
+def make_mla():
+    import deepseekv32_mla_indexer_prolog_quant as ref  # noqa: reference module
+    seed, b, s1, s2 = 6, 2, 2, 256
+    torch.manual_seed(seed)
+    params = dict(n1=128, n2=1, h=7168, num_heads=128, idx_n_heads=64, q_lora_rank=1536, qk_nope_head_dim=128,
+                  idx_head_dim=128, qk_rope_head_dim=64, rope_head_dim=64, kv_lora_rank=512, block_size=128,
+                  dtype=torch.bfloat16, b=b, s=s1, t=b * s1, s1=s1, s2=s2,
+                  actual_seq=torch.tensor([s2] * b, dtype=torch.int32).unsqueeze(-1))
+    (x, w_dq, w_uqqr, _, scale_data, w_dkvkr, w_uk, gamma_cq, gamma_ckv, cos, sin, cache_index, kv_cache, kr_cache,
+     ks_cache, _, _) = ref.gen_mla_prolog_quant_v32_inputs(params, (torch.bfloat16, torch.bfloat16),
+                                                          params["actual_seq"], (False, True), False, False, 128,
+                                                          "PA_BSND")
+    inputs = dict(dtype=torch.bfloat16, is_quant_a=False, is_quant_b=True, has_smooth=False, cache_mode="PA_BSND",
+                  gamma_cq=gamma_cq, gamma_ckv=gamma_ckv, x=x, w_dq=w_dq, w_uqqr=w_uqqr, w_uk=w_uk, w_dkvkr=w_dkvkr,
+                  cos=cos, sin=sin, kv_cache=kv_cache, kr_cache=kr_cache, kv_quant_scale_cache=ks_cache,
+                  cache_index=cache_index, w_qb_scale=scale_data["w_uqqr"])
+    q_nope, q_rope, q_norm, q_norm_scale, kv_out, kr_out, ks_out = ref.mla_prolog_quant_v32_compute(inputs)
+    t = b * s1
+    named = dict(x=x, w_dq=w_dq, w_uqqr=w_uqqr, w_qb_scale=scale_data["w_uqqr"], w_uk=w_uk, w_dkvkr=w_dkvkr,
+                 gamma_cq=gamma_cq, gamma_ckv=gamma_ckv, cos=cos, sin=sin, cache_index=cache_index, kv_cache=kv_cache,
+                 kr_cache=kr_cache, ks_cache=ks_cache)
+    digests = {k: digest(v) for k, v in named.items()}
+    np.savez_compressed(
+        os.path.join(HERE, "mla_small.npz"), seed=seed, b=b, s1=s1, s2=s2, digests=json.dumps(digests),
+        q_nope=bits16(q_nope.reshape(t, 128, 512)), q_rope=bits16(q_rope.reshape(t, 128, 64)),
+        q_norm=q_norm.reshape(t, 1536).numpy(), q_norm_scale=q_norm_scale.reshape(t, 1).numpy(),
+        kv_cache=kv_out.numpy(), kr_cache=bits16(kr_out), ks_cache=ks_out.numpy())
+    print("mla_small: q_nope", tuple(q_nope.shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -188,3 +219,4 @@ if __name__ == "__main__":
     make_sfa()
     make_indexer()
     make_prolog()
+    make_mla()

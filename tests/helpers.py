@@ -168,3 +168,66 @@ def gen_indexer_inputs(seed, act_seq, s1=1, block_size=128, extra_blocks=0):
     k_scale = (torch.rand((block_num, block_size, 1), generator=g) * 0.019 + 0.001).to(torch.float16)
     return dict(query=query, q_scale=q_scale, weights=weights, key=key, k_scale=k_scale, block_table=block_table,
                 act_seq=torch.tensor(act_seq, dtype=torch.int32), b=b, s1=s1)
+
+
+def load_mla_golden():
+    z = np.load(os.path.join(GOLDEN, "mla_small.npz"))
+    bf = torch.bfloat16
+    return dict(
+        seed=int(z["seed"]), b=int(z["b"]), s1=int(z["s1"]), s2=int(z["s2"]), digests=json.loads(str(z["digests"])),
+        q_nope=from_bits16(z["q_nope"], bf), q_rope=from_bits16(z["q_rope"], bf), q_norm=torch.from_numpy(z["q_norm"]),
+        q_norm_scale=torch.from_numpy(z["q_norm_scale"]), kv_cache=torch.from_numpy(z["kv_cache"]),
+        kr_cache=from_bits16(z["kr_cache"], bf), ks_cache=torch.from_numpy(z["ks_cache"]))
+
+
+def _per_row_quant(t, dim):
+    """quant() of the MLA golden (deepseekv32_mla_indexer_prolog_quant.py:35-53) along `dim`."""
+    f = t.to(torch.float32)
+    amax = torch.max(torch.abs(f), dim=dim, keepdim=True)[0]
+    s = 127 / amax
+    q = torch.trunc(torch.round(f * s).to(torch.int32).to(torch.float16)).to(torch.int8)
+    return q, 1 / s
+
+
+def mla_reference_inputs(seed, b, s1, s2):
+    """Same RNG call order as the reference generator (deepseekv32_mla_indexer_prolog_quant.py:161-333,
+    is_quant = (False, True), no smoothing), so the same seed reproduces the tensors whose digests are stored
+    in mla_small.npz."""
+    torch.manual_seed(seed)
+    bf = torch.bfloat16
+    h, qr, n, nope, rope, lora, bs = 7168, 1536, 128, 128, 64, 512, 128
+    nblk_each = math.ceil(s2 / bs)
+    block_num = nblk_each * b
+    perm = torch.arange(0, block_num, 1)
+    perm = perm[torch.randperm(perm.size(0))].to(torch.int32)
+    block_table = perm.reshape(b, nblk_each).clone()
+    cache_index = torch.empty((b, s1), dtype=torch.int64)
+    for i in range(b):
+        for j in range(s1):
+            pos = s2 - s1 + j
+            cache_index[i, j] = int(block_table[i, pos // bs]) * bs + pos % bs
+    x = torch.empty([b, s1, h]).uniform_(-1, 1).to(bf)
+    w_dq = torch.empty([h, qr]).uniform_(-0.1, 0.1).to(bf)
+    w_uqqr = torch.empty([qr, n * (nope + rope)]).uniform_(-0.1, 0.1).to(bf)
+    w_dkvkr = torch.empty([h, lora + rope]).uniform_(-0.1, 0.1).to(bf)
+    w_uqqr, w_qb_scale = _per_row_quant(w_uqqr, -2)
+    w_uk = torch.empty([n, nope, lora]).uniform_(-0.1, 0.1).to(bf)
+    gamma_cq = torch.empty([qr]).uniform_(-1, 1).to(bf)
+    gamma_ckv = torch.empty([lora]).uniform_(-1, 1).to(bf)
+    cos = torch.empty([b, s1, rope]).uniform_(-0.1, 0.1).to(bf)
+    sin = torch.empty([b, s1, rope]).uniform_(-0.1, 0.1).to(bf)
+    k_bsnd = torch.empty([b, s2, 1, lora + rope]).uniform_(-1, 1).to(bf)
+    k_pad = torch.zeros((b, nblk_each * bs, 1, lora + rope)).to(bf)
+    k_pad[:, :s2] = k_bsnd
+    k_cache = torch.zeros([block_num, bs, 1, lora + rope]).to(bf)
+    for i in range(b):
+        for j in range(nblk_each):
+            k_cache[block_table[i, j]] = k_pad[i, j * bs:(j + 1) * bs]
+    kv_cache = k_cache[:, :, :, :lora]
+    kr_cache = k_cache[:, :, :, lora:].contiguous()
+    kv_q, kv_s = _per_row_quant(kv_cache.reshape(-1, 4, lora // 4), -1)
+    t = b * s1
+    return dict(x=x.reshape(t, h), w_dq=w_dq, w_uqqr=w_uqqr, w_qb_scale=w_qb_scale, w_uk=w_uk, w_dkvkr=w_dkvkr,
+                gamma_cq=gamma_cq, gamma_ckv=gamma_ckv, cos=cos.reshape(t, rope), sin=sin.reshape(t, rope),
+                cache_index=cache_index.reshape(t), kv_cache=kv_q.reshape(block_num, bs, 1, lora), kr_cache=kr_cache,
+                ks_cache=kv_s.reshape(block_num, bs, 1, 4), block_table=block_table)

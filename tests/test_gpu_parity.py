@@ -406,3 +406,151 @@ def test_prolog_config1_distributions_vs_oracle(t):
                              inp["cos_idx_rope"], inp["sin_idx_rope"], inp["hadamard_q"], inp["hadamard_k"],
                              inp["idx_k_cache"], inp["idx_k_scale_cache"], inp["idx_k_cache_index"])
     _assert_prolog_close(_run_prolog(inp), ref, inp["idx_k_cache_index"])
+
+
+# --------------------------------------------------------------------------------------------------
+# fused MLA prolog + indexer prolog
+# --------------------------------------------------------------------------------------------------
+def _run_mla(inp, ip):
+    """Runs the stand-alone MLA entry (for q_norm) and the fused entry on copies of the same caches."""
+    import pypto_b200
+    from pypto_b200 import mla_indexer_prolog_quant_impl as mla
+    from pypto_b200 import mla_prolog_quant_impl as mlp
+    from pypto_b200 import lightning_indexer_prolog_quant_impl as pl
+    c, ci = _cuda(inp), _cuda(ip)
+    t = inp["x"].shape[0]
+    bf = torch.bfloat16
+    scale = c["w_qb_scale"].reshape(-1, 1).contiguous()
+    # stand-alone MLA prolog: exposes q_norm / q_norm_scale
+    q_norm = torch.zeros((t, 1536), dtype=torch.int8, device=DEV)
+    q_norm_scale = torch.zeros((t, 1), dtype=torch.float32, device=DEV)
+    q_nope0 = torch.zeros((t, 128, 512), dtype=bf, device=DEV)
+    q_rope0 = torch.zeros((t, 128, 64), dtype=bf, device=DEV)
+    kv0, kr0, ks0 = c["kv_cache"].clone(), c["kr_cache"].clone(), c["ks_cache"].clone()
+    mlp.mla_prolog_quant_d(c["x"], c["w_dq"], c["w_uqqr"], scale, c["w_uk"], c["w_dkvkr"], c["gamma_cq"], c["gamma_ckv"],
+                           c["cos"], c["sin"], c["cache_index"], kv0, kr0, ks0, q_norm, q_norm_scale, q_nope0, q_rope0,
+                           kv0, kr0, ks0, 1e-6, 1e-6, "PA_BSND", mlp.MlaTileConfig(), mlp.RopeTileShapeConfig())
+    # fused entry
+    q_nope = torch.zeros((t, 128, 512), dtype=bf, device=DEV)
+    q_rope = torch.zeros((t, 128, 64), dtype=bf, device=DEV)
+    kv, kr, ks = c["kv_cache"].clone(), c["kr_cache"].clone(), c["ks_cache"].clone()
+    q_int8 = torch.zeros((t, 64, 128), dtype=torch.int8, device=DEV)
+    q_scale = torch.zeros((t, 64, 1), dtype=torch.float16, device=DEV)
+    weights = torch.zeros((t, 64), dtype=torch.float16, device=DEV)
+    ikc, iksc = ci["idx_k_cache"].clone(), ci["idx_k_scale_cache"].clone()
+    mla.mla_indexer_prolog_quant_d(
+        c["x"], c["w_dq"], c["w_uqqr"], scale, c["w_uk"], c["w_dkvkr"], c["gamma_cq"],
+        c["gamma_ckv"], c["cos"], c["sin"], c["cache_index"], kv, kr, ks, ci["w_idx_qb"], ci["w_idx_qb_scale"],
+        ci["w_idx_k"], ci["w_idx_proj"], ci["layer_norm_gamma"], ci["layer_norm_beta"], ci["hadamard_q"],
+        ci["hadamard_k"], ikc, iksc, q_nope, q_rope, kv, kr, ks, q_int8, q_scale, ikc, iksc, weights,
+        1e-6, 1e-6, "PA_BSND", mla.MlaTileConfig(), pl.IndexerPrologQuantAttr(eps=1e-6), pl.IndexerPrologQuantConfigs(),
+        mla.RopeTileShapeConfig())
+    pypto_b200.check_status()
+    # both entries run the same kernels on the same inputs: identical results
+    for a, b in ((q_nope0, q_nope), (q_rope0, q_rope), (kv0, kv), (kr0, kr), (ks0, ks)):
+        assert torch.equal(a, b)
+    return dict(q_nope=q_nope.cpu(), q_rope=q_rope.cpu(), kv=kv.cpu(), kr=kr.cpu(), ks=ks.cpu(), q_int8=q_int8.cpu(),
+                q_scale=q_scale.cpu(), weights=weights.cpu(), ikc=ikc.cpu(), iksc=iksc.cpu(), q_norm=q_norm.cpu(),
+                q_norm_scale=q_norm_scale.cpu())
+
+
+def _indexer_side_inputs(seed, t, nblk):
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    return {
+        "w_idx_qb": torch.randint(-128, 128, (1536, 8192), generator=g, dtype=torch.int8),
+        "w_idx_qb_scale": (torch.rand((8192, 1), generator=g) * 2e-3 + 1e-4),
+        "w_idx_k": (torch.randn((7168, 128), generator=g) * 0.02).to(bf),
+        "w_idx_proj": (torch.randn((7168, 64), generator=g) * 0.02).to(bf),
+        "layer_norm_gamma": torch.ones(128, dtype=bf), "layer_norm_beta": torch.zeros(128, dtype=bf),
+        "hadamard_q": (torch.rand((128, 128), generator=g) * 2 - 1).to(bf),
+        "hadamard_k": (torch.rand((128, 128), generator=g) * 2 - 1).to(bf),
+        "idx_k_cache": torch.randint(-127, 128, (nblk, 128, 1, 128), generator=g, dtype=torch.int8),
+        "idx_k_scale_cache": (torch.rand((nblk, 128, 1, 1), generator=g) * 0.02).to(torch.float16),
+    }
+
+
+def _check_mla(out, ref, ip, inp, ratio=0.005, scale_ratio=0.005):
+    q_nope, q_rope, q_norm, q_norm_scale, kv, kr, ks = ref
+    bad = []
+
+    def points(name, got, want, atol, rtol, allowed):
+        n = orc.reference_compare_count(got, want, atol, rtol)
+        if n > allowed:
+            bad.append(f"{name}: {n} of {want.numel()} elements outside atol={atol} rtol={rtol} (allowed {allowed:.1f})")
+
+    def lsb(name, got, want, steps):
+        d = int((got.int() - want.int()).abs().max())
+        if d > steps:
+            bad.append(f"{name}: max int8 difference {d} > {steps}")
+
+    # the reference's own tolerances for the fused operator (deepseekv32_mla_indexer_prolog_quant.py:808-828);
+    # `ratio` is its allowance of error points (0.5 % there)
+    points("q_nope", out["q_nope"], q_nope, 0.005, 0.0078125, ratio * q_nope.numel())
+    points("q_rope", out["q_rope"], q_rope, 0.005, 0.0078125, ratio * q_rope.numel())
+    lsb("kv", out["kv"], kv, 1)
+    points("kr", out["kr"], kr, 1e-4, 0.0078125, 0.005 * kr.numel())
+    # a scale is 1/127 of a bf16 maximum: one bf16 step of that maximum is the resolution of the comparison
+    points("k_scale", out["ks"], ks, 2.5e-5, 0.008, 0)
+    lsb("q_norm", out["q_norm"], q_norm, 1)
+    points("q_norm_scale", out["q_norm_scale"], q_norm_scale, 0, 0.008, 0)
+    # tight: the oracle continued from the q_norm the device produced -- int32 GEMM, dequantisation and RoPE
+    # are then exact, the w_uk projection differs only by the library's accumulation order
+    x_nope, x_rope = orc.mla_prolog(inp["x"], inp["w_dq"], inp["w_uqqr"], inp["w_qb_scale"], inp["w_uk"], inp["w_dkvkr"],
+                                    inp["gamma_cq"], inp["gamma_ckv"], inp["cos"], inp["sin"], inp["cache_index"],
+                                    inp["kv_cache"], inp["kr_cache"], inp["ks_cache"],
+                                    q_norm_in=(out["q_norm"], out["q_norm_scale"]))[:2]
+    if not torch.equal(out["q_rope"], x_rope):
+        bad.append(f"q_rope from the device q_norm: {(out['q_rope'] != x_rope).sum()} elements differ")
+    points("q_nope from the device q_norm", out["q_nope"], x_nope, 0.005, 0.0078125, 0.0005 * x_nope.numel())
+    ipargs = (ip["w_idx_qb"], ip["w_idx_qb_scale"], ip["w_idx_k"], ip["w_idx_proj"], ip["layer_norm_gamma"],
+              ip["layer_norm_beta"], inp["cos"], inp["sin"], ip["hadamard_q"], ip["hadamard_k"], ip["idx_k_cache"],
+              ip["idx_k_scale_cache"], inp["cache_index"])
+    # indexer half, tight: the oracle fed with the q_norm the device produced
+    iq, iqs, ikc, iksc, w = orc.indexer_prolog(inp["x"], out["q_norm"], out["q_norm_scale"], *ipargs)
+    lsb("idx q_int8 (device q_norm)", out["q_int8"], iq.reshape(out["q_int8"].shape), 1)
+    points("idx q_scale (device q_norm)", out["q_scale"].reshape(-1), iqs.reshape(-1), 2.5e-5, 2e-3, 0.001 * iqs.numel())
+    lsb("idx k_int8", out["ikc"], ikc, 1)
+    points("idx k_scale", out["iksc"], iksc, 2.5e-5, 2e-3, 0)
+    points("idx weights", out["weights"], w.reshape(out["weights"].shape), 2.5e-5, 4e-3, 0.001 * w.numel())
+    # indexer half, end to end: the oracle chain with the reference's tolerances (:825-829)
+    iq, iqs, ikc, iksc, w = orc.indexer_prolog(inp["x"], q_norm, q_norm_scale, *ipargs)
+    points("idx q_int8", out["q_int8"], iq.reshape(out["q_int8"].shape), 2, 0, ratio * iq.numel())
+    points("idx q_scale", out["q_scale"].reshape(-1), iqs.reshape(-1), 2.5e-5, 0.006, max(1, scale_ratio * iqs.numel()))
+    assert not bad, "\n".join(bad)
+
+
+def test_mla_indexer_prolog_reference_golden_fixture():
+    g = helpers.load_mla_golden()
+    inp = helpers.mla_reference_inputs(g["seed"], g["b"], g["s1"], g["s2"])
+    ip = _indexer_side_inputs(3, inp["x"].shape[0], inp["kv_cache"].shape[0])
+    out = _run_mla(inp, ip)
+    ref = (g["q_nope"], g["q_rope"], g["q_norm"], g["q_norm_scale"], g["kv_cache"], g["kr_cache"], g["ks_cache"])
+    _check_mla(out, ref, ip, inp)
+
+
+@pytest.mark.parametrize("t", [1, 37, 128])
+def test_mla_indexer_prolog_seeded_vs_oracle(t):
+    g = torch.Generator().manual_seed(500 + t)
+    bf = torch.bfloat16
+    nblk = 6
+    u = lambda shape, a: ((torch.rand(shape, generator=g) * 2 - 1) * a)  # noqa: E731
+    w_uqqr_f = u((1536, 128 * 192), 0.1)
+    wamax = w_uqqr_f.abs().amax(0, keepdim=True)
+    ang = torch.rand((t, 64), generator=g) * 2 * math.pi
+    inp = dict(
+        x=u((t, 7168), 1.0).to(bf), w_dq=u((7168, 1536), 0.1).to(bf), w_uqqr=torch.round(w_uqqr_f * (127 / wamax)).to(torch.int8),
+        w_qb_scale=(wamax / 127).reshape(-1).float().contiguous(), w_uk=u((128, 128, 512), 0.1).to(bf),
+        w_dkvkr=u((7168, 576), 0.1).to(bf), gamma_cq=u((1536,), 1.0).to(bf), gamma_ckv=u((512,), 1.0).to(bf),
+        cos=torch.cos(ang).to(bf), sin=torch.sin(ang).to(bf),
+        cache_index=torch.randperm(nblk * 128, generator=g)[:t].to(torch.int64),
+        kv_cache=torch.randint(-127, 128, (nblk, 128, 1, 512), generator=g, dtype=torch.int8),
+        kr_cache=u((nblk, 128, 1, 64), 1.0).to(bf), ks_cache=torch.rand((nblk, 128, 1, 4), generator=g) * 0.02)
+    ip = _indexer_side_inputs(600 + t, t, nblk)
+    ref = orc.mla_prolog(inp["x"], inp["w_dq"], inp["w_uqqr"], inp["w_qb_scale"], inp["w_uk"], inp["w_dkvkr"],
+                         inp["gamma_cq"], inp["gamma_ckv"], inp["cos"], inp["sin"], inp["cache_index"], inp["kv_cache"],
+                         inp["kr_cache"], inp["ks_cache"])
+    # these value distributions are not the reference generator's: one-LSB differences of q_norm (library GEMM
+    # accumulation order) move a few more elements past the reference tolerance, so allow 1.5 % error points;
+    # the indexer's per-head scale is a maximum over 128 sums of those differences and moves with them (5 %)
+    _check_mla(_run_mla(inp, ip), ref, ip, inp, ratio=0.015, scale_ratio=0.05)

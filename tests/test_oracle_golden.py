@@ -83,3 +83,21 @@ def test_merge_topk_candidates_equals_global_topk():
     merged = orc.merge_topk_candidates(torch.cat(cs, 1), torch.cat(ci, 1), k)
     for i in range(2):
         assert merged[i].tolist() == orc.topk_indices_ref(scores[i], k).tolist()
+
+
+def test_mla_inputs_reproduce_and_oracle_matches_reference_golden():
+    g = helpers.load_mla_golden()
+    inp = helpers.mla_reference_inputs(g["seed"], g["b"], g["s1"], g["s2"])
+    for name, d in g["digests"].items():
+        assert helpers.digest(inp[name].reshape(-1)) == d, name
+    q_nope, q_rope, q_norm, q_norm_scale, kv, kr, ks = orc.mla_prolog(
+        inp["x"], inp["w_dq"], inp["w_uqqr"], inp["w_qb_scale"], inp["w_uk"], inp["w_dkvkr"], inp["gamma_cq"],
+        inp["gamma_ckv"], inp["cos"], inp["sin"], inp["cache_index"], inp["kv_cache"], inp["kr_cache"], inp["ks_cache"])
+    # the reference's own test tolerances (deepseekv32_mla_indexer_prolog_quant.py:808-828)
+    assert orc.reference_compare_count(q_nope, g["q_nope"], 0.005, 0.0078125) <= 0.005 * q_nope.numel()
+    assert orc.reference_compare_count(q_rope, g["q_rope"], 0.005, 0.0078125) <= 0.005 * q_rope.numel()
+    assert (q_norm.int() - g["q_norm"].int()).abs().max() <= 1
+    assert torch.allclose(q_norm_scale, g["q_norm_scale"], rtol=1e-3)
+    assert (kv.int() - g["kv_cache"].int()).abs().max() <= 1
+    assert orc.reference_compare_count(kr, g["kr_cache"], 1e-4, 0.0078125) <= 0.005 * kr.numel()
+    assert torch.allclose(ks, g["ks_cache"], rtol=1e-3, atol=1e-6)
