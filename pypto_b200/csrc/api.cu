@@ -69,11 +69,13 @@ uint64_t dsv32_launch_count(void) { return g_launches.load(std::memory_order_rel
 
 // ---- sparse flash attention ---------------------------------------------------------------------------
 size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t topk, int32_t kv_splits) {
-  if (b <= 0 || s1 <= 0 || n_q <= 0) return 0;
-  const int splits = pick_sfa_splits(b * s1, n_q, topk, kv_splits);
-  if (splits <= 1) return 0;
+  if (b <= 0 || s1 <= 0 || n_q <= 0 || topk <= 0) return 0;
   const size_t t = static_cast<size_t>(b) * s1;
-  return align_up(t * splits * n_q * kKvLora * sizeof(float), 256) + align_up(t * splits * n_q * sizeof(float), 256);
+  size_t bytes = align_up(t * topk * sizeof(int32_t), 256);  // cache row of every selected key
+  const int splits = pick_sfa_splits(b * s1, n_q, topk, kv_splits);
+  if (splits > 1)
+    bytes += align_up(t * splits * n_q * kKvLora * sizeof(float), 256) + align_up(t * splits * n_q * sizeof(float), 256);
+  return bytes;
 }
 
 int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
@@ -109,17 +111,25 @@ int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
   p.status = a->status;
   p.rows = a->rows;
   p.b = a->b; p.s1 = a->s1; p.nq = a->n_q; p.topk = a->topk; p.block_size = a->block_size;
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == a->block_size) p.bs_shift = sh;
   p.max_blocks = a->max_blocks; p.splits = splits; p.scale = a->softmax_scale;
-  if (splits > 1) {
+  {
     const size_t need = dsv32_sfa_workspace_bytes(a->b, a->s1, a->n_q, a->topk, splits);
     if (a->workspace == nullptr || a->workspace_bytes < need ||
         reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) {
       set_error("sfa: workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
       return DSV32_ERR_WORKSPACE;
     }
-    const size_t o_bytes = align_up(static_cast<size_t>(t) * splits * a->n_q * kKvLora * sizeof(float), 256);
-    p.part_o = static_cast<float*>(a->workspace);
-    p.part_lse = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + o_bytes);
+    char* ws = static_cast<char*>(a->workspace);
+    p.row_ids = reinterpret_cast<int32_t*>(ws);
+    ws += align_up(static_cast<size_t>(t) * a->topk * sizeof(int32_t), 256);
+    if (splits > 1) {
+      const size_t o_bytes = align_up(static_cast<size_t>(t) * splits * a->n_q * kKvLora * sizeof(float), 256);
+      p.part_o = reinterpret_cast<float*>(ws);
+      p.part_lse = reinterpret_cast<float*>(ws + o_bytes);
+    }
   }
   // bring-up switch: DSV32_SFA_IMPL=mma selects the warp-MMA kernel instead of the tcgen05 one
   static const bool use_mma = [] {

@@ -46,9 +46,11 @@ struct SfaParams {
   __nv_bfloat16* out;
   float* part_o;
   float* part_lse;
+  int32_t* row_ids;  // [t, topk] cache row + 1 of every selected key, 0 = none (scratch, tcgen05 kernel only)
   uint32_t* status;
   long long rows;
   int b, s1, nq, topk, block_size, max_blocks, splits;
+  int bs_shift;  // log2(block_size) when it is a power of two, else -1
   float scale;
 };
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);

@@ -28,7 +28,8 @@ constexpr int kStQChunkBytes = 128 * 128;          // one 64-dim chunk of Q (16 
 constexpr int kStQsBytes = 5 * kStQChunkBytes;     // dims 256..575
 constexpr int kStOffQ = 2 * kStStageBytes;
 constexpr int kStOffValid = kStOffQ + kStQsBytes;  // int[2][64]
-constexpr int kStOffBars = kStOffValid + 2 * kStTile * 4;
+constexpr int kStOffRing = kStOffValid + 2 * kStTile * 4;   // int[8 producer warps][4 tiles][8 rows]: row ids in flight
+constexpr int kStOffBars = kStOffRing + 8 * 4 * 8 * 4;
 constexpr int kStNumBars = 2 + 2 + 2 + 2 + 1;      // full[2], s_full[2], p_ready[2], pv_done[2], q_ready
 constexpr int kStOffTmem = kStOffBars + kStNumBars * 8;
 constexpr size_t kStSmemBytes = kStOffTmem + 16 + 1024;
@@ -48,6 +49,11 @@ __device__ unsigned long long g_sfa_trace[4][40][8];
 #define ST_TRACE(tile, slot) do { } while (0)
 #endif
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifdef DSV32_X_SPARTS
+constexpr int kSParts = DSV32_X_SPARTS;
+#else
+constexpr int kSParts = 1;     // S of a tile is issued in this many parts (1, 2 or 4); splitting measured slower
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -80,6 +86,33 @@ __device__ __forceinline__ void st_dequant16(const int4& raw, float sc, uint4& l
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+// Cache row of every selected key (row + 1; 0 = no key: a -1 entry, a position past the token's valid count,
+// or an entry that failed validation, which is also reported through the status word).  Paged-gather
+// semantics of python/pypto/experimental/gather.py:18-87: row = block_table[b, idx / block] * block + idx % block.
+__global__ void __launch_bounds__(256) sfa_row_ids_kernel(SfaParams p) {
+  const int tok = blockIdx.y;
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= p.topk) return;
+  const int bi = tok / p.s1, si = tok % p.s1;
+  const int cnt = min(max(p.act_seq[bi] - p.s1 + 1 + si, 0), p.topk);
+  int out = 0;
+  if (j < cnt) {
+    const int idx = __ldg(p.topk_idx + static_cast<size_t>(tok) * p.topk + j);
+    if (idx >= 0) {
+      const int lb = idx / p.block_size;
+      if (lb >= p.max_blocks) {
+        report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, idx);
+      } else {
+        const int pb = __ldg(p.block_table + static_cast<size_t>(bi) * p.max_blocks + lb);
+        const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
+        if (pb < 0 || row >= p.rows) report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, idx);
+        else out = static_cast<int>(row) + 1;
+      }
+    }
+  }
+  p.row_ids[static_cast<size_t>(tok) * p.topk + j] = out;
+}
+
 __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
                                                                const __grid_constant__ CUtensorMap qr_map,
                                                                SfaParams p) {
@@ -88,6 +121,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
   unsigned char* k_s = smem;
   unsigned char* q_s = smem + kStOffQ;
   int* valid_s = reinterpret_cast<int*>(smem + kStOffValid);
+  int* ring_s = reinterpret_cast<int*>(smem + kStOffRing);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStOffBars);
   uint64_t* full_bar = bars;         // [2] producers -> MMA            (8 warp arrivals)
   uint64_t* sfull_bar = bars + 2;    // [2] S complete -> softmax       (tcgen05.commit)
@@ -176,22 +210,29 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         v_lo[s] = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);  // MN-major (V)
       }
 
-      auto issue_s = [&](int i) {
+      // S of one tile is issued in four parts of nine MMAs, so that a PV whose P has just become ready does
+      // not wait behind a whole S (MMAs execute in issue order; S and PV use different accumulators).
+      auto issue_s_part = [&](int i, int part) {
         const int s = i & 1;
-        ST_TRACE(i, 2);
-        tc_fence_after();
+        if (part == 0) {
+          ST_TRACE(i, 2);
+          tc_fence_after();
+        }
         const uint32_t d = tmem_base + kColS + s * kStTile;
         const uint32_t klo = stage_lo[s];
 #pragma unroll
-        for (int ks = 0; ks < 16; ++ks)  // Q dims 0..255 from tensor memory
-          umma_f16_ts(d, tmem_base + kColQ + ks * 8, desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)),
-                      idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 16; ks < 36; ++ks)  // Q dims 256..575 from shared memory
-          umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
-                      desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
-        umma_commit(&sfull_bar[s]);
-        ST_TRACE(i, 3);
+        for (int ks = 0; ks < 36; ++ks) {
+          if (ks / (36 / kSParts) != part) continue;
+          const uint64_t kd = desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4));
+          if (ks < 16)  // Q dims 0..255 from tensor memory
+            umma_f16_ts(d, tmem_base + kColQ + ks * 8, kd, idesc_s, ks > 0 ? 1u : 0u);
+          else          // Q dims 256..575 from shared memory
+            umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)), kd, idesc_s, 1u);
+        }
+        if (part == kSParts - 1) {
+          umma_commit(&sfull_bar[s]);
+          ST_TRACE(i, 3);
+        }
       };
       auto issue_pv = [&](int i) {
         const int s = i & 1;
@@ -204,17 +245,26 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         umma_commit(&pvdone_bar[s]);
         ST_TRACE(i, 5);
       };
-      // Issue whichever is ready, PV first: finishing PV(i) frees K stage i for the producers, so the
-      // dequantisation of tile i+2 overlaps the S MMAs of tile i+1.  (S(i) never overtakes PV(i-2): the
-      // stage it reads is only refilled after that PV has completed.)
-      int next_s = 0, next_pv = 0;
+      // Issue whichever is ready, PV first: finishing PV(i) frees K stage i for the producers.  (S(i) never
+      // overtakes PV(i-2): it is only started once that PV has been issued.)
+      int next_s = 0, next_pv = 0, s_part = 0;  // s_part > 0: S(next_s) is partly issued
       long long t_idle = clock64();
       while (ok && next_pv < ntiles) {
-        if (next_pv < next_s && mbar_try_wait(&pready_bar[next_pv & 1], (next_pv >> 1) & 1)) {
+        if (next_pv < next_s && mbar_test_wait(&pready_bar[next_pv & 1], (next_pv >> 1) & 1)) {
           issue_pv(next_pv++);
           t_idle = clock64();
-        } else if (next_s < ntiles && next_s < next_pv + 2 && mbar_try_wait(&full_bar[next_s & 1], (next_s >> 1) & 1)) {
-          issue_s(next_s++);
+        } else if (s_part > 0) {
+          switch (s_part) {
+            case 1: issue_s_part(next_s, 1); break;
+            case 2: issue_s_part(next_s, 2); break;
+            default: issue_s_part(next_s, 3); break;
+          }
+          if (++s_part == kSParts) { s_part = 0; ++next_s; }
+          t_idle = clock64();
+        } else if (next_s < ntiles && next_s < next_pv + 2 && mbar_test_wait(&full_bar[next_s & 1], (next_s >> 1) & 1)) {
+          issue_s_part(next_s, 0);
+          s_part = 1;
+          if (s_part == kSParts) { s_part = 0; ++next_s; }
           t_idle = clock64();
         } else if (clock64() - t_idle > kWaitBudgetCycles) {
           report_status(p.status, DSV32_STATUS_TIMEOUT, 11, blockIdx.y);
@@ -250,7 +300,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     for (int i = 0; ok && i < ntiles; ++i) {
       const int s = i & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], (i >> 1) & 1, p.status, 20))) { ok = false; break; }
-      if (tid == 32) ST_TRACE(i, 6);
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + kColS + s * kStTile;
       uint32_t r0[32], r1[32];
@@ -312,7 +361,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pready_bar[s]);
-      if (tid == 32) ST_TRACE(i, 7);
     }
     // ---- epilogue: O / l -> bf16 (or fp32 partial + log-sum-exp for a key split) -----------------------------
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pvdone_bar[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, p.status, 22));
@@ -359,30 +407,29 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     const int ptid = tid - 160;            // 0..255
     const int pwarp_lane0 = (lane == 0);
     const int gkey = ptid >> 3, gpart = ptid & 7;  // two passes of 32 keys; 16-byte chunks gpart + 8*j
-    const int32_t* idx_row = p.topk_idx + static_cast<size_t>(tok) * p.topk;
-    const int32_t* bt = p.block_table + static_cast<size_t>(bi) * p.max_blocks;
-
-    // Address resolution is software-pipelined so that no iteration waits on a chain of dependent loads:
-    //   top-k index of tile i+4 -> page-table entry of tile i+3 -> row number + L2 prefetch of tile i+2
-    //   -> row data of tile i+1 into registers -> dequantise + store tile i.
-    // A value loaded in one iteration is first touched in the next one.
-    auto load_idx = [&](int tile, int pass) -> int {
-      const int j = k_lo + tile * kStTile + pass * 32 + gkey;
-      return (tile < ntiles && j < k_hi) ? __ldg(idx_row + j) : -1;
-    };
-    auto load_page = [&](int idx) -> int {  // page-table entry of a (possibly invalid) index; -1 = none
-      if (idx < 0) return -1;
-      const int lb = idx / p.block_size;
-      return (lb < p.max_blocks) ? __ldg(bt + lb) : -2;
-    };
-    auto make_row = [&](int idx, int pb) -> long long {
-      if (idx < 0) return -1;
-      const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
-      if (pb < 0 || row >= p.rows) {
-        report_status(p.status, pb == -2 ? DSV32_STATUS_BAD_INDEX : DSV32_STATUS_BAD_PAGE, tok, idx);
-        return -1;
+    // The cache row of every selected key was resolved by sfa_row_ids_kernel (row + 1, 0 = none).  Row ids
+    // travel global -> shared memory with 4-byte cp.async three tiles ahead, so no register holds a loaded
+    // value across the dequantisation of a tile: lanes 0..7 of a producer warp fetch the ids of the warp's
+    // eight rows of a tile (row = pass*32 + gkey, gkey = 4*warp + 0..3).
+    const int pw = warp - 5;
+    int* ring = ring_s + pw * 32;
+    const int32_t* ids_row = p.row_ids + static_cast<size_t>(tok) * p.topk;
+    auto fetch_ids = [&](int tile) {
+      if (lane < 8) {
+        const int j = k_lo + tile * kStTile + (lane >> 2) * 32 + 4 * pw + (lane & 3);
+        const bool in = tile < ntiles && j < k_hi;
+        const uint32_t dst = smem_u32(ring + (tile & 3) * 8 + lane);
+        const int32_t* src = ids_row + (in ? j : 0);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(in ? 4 : 0) : "memory");
       }
-      return row;
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto ids_wait_all_but_one = [&]() {
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      __syncwarp();
+    };
+    auto row_of = [&](int tile, int pass) -> long long {  // -1 = none
+      return static_cast<long long>(ring[(tile & 3) * 8 + pass * 4 + (lane >> 3)]) - 1;
     };
     auto l2_prefetch = [&](long long row) {  // the 656 bytes of a row: lanes 0..3 nope lines, 4 rope, 5 scales
       if (row < 0) return;
@@ -390,81 +437,97 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       if (gpart < 4) a = p.k_nope + row * kKvLora + gpart * 128;
       else if (gpart == 4) a = p.k_rope + row * kRopeDim;
       else if (gpart == 5) a = p.k_scales + row * 4;
+#ifndef DSV32_SFA_NO_PREFETCH
       if (a != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+#endif
     };
+    // Register layout of a row: nope[0..1] / sc.x,.y = this CTA's own value dims (128-dim groups 2*half, 2*half+1),
+    // nope[2..3] / sc.z,.w = the other half's.  The runtime half only enters the addresses.
+    const int q_own = 2 * half, q_oth = 2 * (half ^ 1);
     auto issue_loads = [&](long long row, StPrefetch& pf) {
       pf.valid = row >= 0;
       if (pf.valid) {
         const int4* src = reinterpret_cast<const int4*>(p.k_nope + row * kKvLora);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) pf.nope[q] = __ldg(src + gpart + 8 * q);
+        pf.nope[0] = __ldg(src + gpart + 8 * q_own);
+        pf.nope[1] = __ldg(src + gpart + 8 * (q_own + 1));
+        pf.nope[2] = __ldg(src + gpart + 8 * q_oth);
+        pf.nope[3] = __ldg(src + gpart + 8 * (q_oth + 1));
         pf.rope = __ldg(reinterpret_cast<const int4*>(p.k_rope + row * kRopeDim) + gpart);
-        pf.sc = __ldg(reinterpret_cast<const float4*>(p.k_scales + row * 4));
+        const float2 so = __ldg(reinterpret_cast<const float2*>(p.k_scales + row * 4 + q_own));
+        const float2 sx = __ldg(reinterpret_cast<const float2*>(p.k_scales + row * 4 + q_oth));
+        pf.sc = make_float4(so.x, so.y, sx.x, sx.y);
       }
     };
-    auto commit = [&](int tile, int pass, const StPrefetch& pf) {
-      const int s = tile & 1;
+    // one dequantised 16-dim group (two 16-byte units) of key row r, 128-dim group q, into its swizzled place
+    auto store_group = [&](unsigned char* stage, int r, int q, bool valid, const int4& raw, float sc) {
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      if (valid) st_dequant16(raw, sc, lo, hi);
+      const int chunk = 2 * q + (gpart >> 2);  // 64-dim chunk 0..7
+      const int u0 = (gpart & 3) * 2;          // first of two 16-byte units inside the 128-byte line
+      unsigned char* line = stage + chunk * kStChunkBytes + r * 128;
+      *reinterpret_cast<uint4*>(line + ((u0 ^ (r & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(line + (((u0 + 1) ^ (r & 7)) << 4)) = hi;
+    };
+    // The chunks that only S reads (the other half's value dims and the rope dims) ...
+    auto commit_other = [&](int tile, int pass, const StPrefetch& pf) {
+      unsigned char* stage = k_s + (tile & 1) * kStStageBytes;
       const int r = pass * 32 + gkey;  // row (key) inside the tile
+      store_group(stage, r, q_oth, pf.valid, pf.nope[2], pf.sc.z);
+      store_group(stage, r, q_oth + 1, pf.valid, pf.nope[3], pf.sc.w);
+      unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
+      const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
+      *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
+    };
+    // ... and the chunks that PV reads as V (this CTA's own value dims), plus the validity flag
+    auto commit_own = [&](int tile, int pass, const StPrefetch& pf) {
+      const int s = tile & 1;
       unsigned char* stage = k_s + s * kStStageBytes;
-      const float sc[4] = {pf.sc.x, pf.sc.y, pf.sc.z, pf.sc.w};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-        if (pf.valid) st_dequant16(pf.nope[q], sc[q], lo, hi);
-        const int ci = gpart + 8 * q;   // 16-dim group 0..31
-        const int chunk = ci >> 2;      // 64-dim chunk 0..7
-        const int u0 = (ci & 3) * 2;    // first of two 16-byte units inside the 128-byte line
-        unsigned char* line = stage + chunk * kStChunkBytes + r * 128;
-        *reinterpret_cast<uint4*>(line + ((u0 ^ (r & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(line + (((u0 + 1) ^ (r & 7)) << 4)) = hi;
-      }
-      {
-        unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
-        const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
-        *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
-        if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
-      }
+      const int r = pass * 32 + gkey;
+      store_group(stage, r, q_own, pf.valid, pf.nope[0], pf.sc.x);
+      store_group(stage, r, q_own + 1, pf.valid, pf.nope[1], pf.sc.y);
+      if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
     };
 
     StPrefetch pf0, pf1;
-    {
-      const int i0 = load_idx(0, 0), i1 = load_idx(0, 1);
-      issue_loads(make_row(i0, load_page(i0)), pf0);
-      issue_loads(make_row(i1, load_page(i1)), pf1);
-    }
-    int idx_b0 = load_idx(1, 0), idx_b1 = load_idx(1, 1);
-    long long row_n0 = make_row(idx_b0, load_page(idx_b0)), row_n1 = make_row(idx_b1, load_page(idx_b1));  // tile 1
-    l2_prefetch(row_n0);
-    l2_prefetch(row_n1);
-    idx_b0 = load_idx(2, 0);
-    idx_b1 = load_idx(2, 1);
-    int pb_b0 = load_page(idx_b0), pb_b1 = load_page(idx_b1);   // tile 2
-    int idx_c0 = load_idx(3, 0), idx_c1 = load_idx(3, 1);       // tile 3
+    fetch_ids(0);
+    fetch_ids(1);
+    fetch_ids(2);
+    ids_wait_all_but_one();  // tiles 0 and 1
+    issue_loads(row_of(0, 0), pf0);
+    issue_loads(row_of(0, 1), pf1);
+    l2_prefetch(row_of(1, 0));
+    l2_prefetch(row_of(1, 1));
     for (int i = 0; i < ntiles; ++i) {
       const int s = i & 1;
-      // the stage is free once the PV MMA of tile i-2 has completed (passes at once for i < 2)
-      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], ((i >> 1) & 1) ^ 1, p.status, 30))) break;
+      // Once S of tile i-2 has completed, every chunk of the stage except this CTA's own value chunks is free
+      // (both waits pass at once for i < 2): that part of the refill runs under the softmax and PV of tile i-2.
+      const uint32_t prev = ((i >> 1) & 1) ^ 1;
+#ifdef DSV32_X_LATE_OTHER
+      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], prev, p.status, 30))) break;
+#else
+      if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], prev, p.status, 30))) break;
+#endif
       if (ptid == 0) ST_TRACE(i, 0);
-      commit(i, 0, pf0);
-      commit(i, 1, pf1);
+      commit_other(i, 0, pf0);
+      commit_other(i, 1, pf1);
+      // the own value chunks (and the validity flags the softmax reads) are free once PV of tile i-2 has completed
+      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], prev, p.status, 31))) break;
+      commit_own(i, 0, pf0);
+      commit_own(i, 1, pf1);
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
       __syncwarp();
       if (pwarp_lane0) mbar_arrive(&full_bar[s]);
       if (ptid == 0) ST_TRACE(i, 1);
       if (i + 1 < ntiles) {
-        issue_loads(row_n0, pf0);                 // tile i+1
-        issue_loads(row_n1, pf1);
-        row_n0 = make_row(idx_b0, pb_b0);         // tile i+2
-        row_n1 = make_row(idx_b1, pb_b1);
-        l2_prefetch(row_n0);
-        l2_prefetch(row_n1);
-        idx_b0 = idx_c0;                          // tile i+3
-        idx_b1 = idx_c1;
-        pb_b0 = load_page(idx_b0);
-        pb_b1 = load_page(idx_b1);
-        idx_c0 = load_idx(i + 4, 0);              // tile i+4
-        idx_c1 = load_idx(i + 4, 1);
+        fetch_ids(i + 3);
+        ids_wait_all_but_one();                   // ids of tile i+2 have landed
+        issue_loads(row_of(i + 1, 0), pf0);       // tile i+1
+        issue_loads(row_of(i + 1, 1), pf1);
+        if (ptid == 0) ST_TRACE(i, 6);
+        l2_prefetch(row_of(i + 2, 0));            // tile i+2 (its slot holds zeros past the last tile)
+        l2_prefetch(row_of(i + 2, 1));
       }
+      if (ptid == 0) ST_TRACE(i, 7);
     }
   }
 
@@ -491,6 +554,14 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
   rc = make_tensor_map_2d_u8(&qr_map, p.q_rope, static_cast<uint64_t>(t) * p.nq, kRopeDim * 2, 128, 128);
   if (rc != DSV32_OK) return rc;
   cudaFuncSetAttribute(sfa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  if (p.rows > 0x7ffffffeLL) {
+    set_error("sfa: the tcgen05 kernel addresses at most 2^31-2 cache rows (got %lld)", static_cast<long long>(p.rows));
+    return DSV32_ERR_UNSUPPORTED;
+  }
+  sfa_row_ids_kernel<<<dim3((p.topk + 255) / 256, t), 256, 0, stream>>>(p);
+  count_launch();
+  rc = check_launch("sfa_row_ids_kernel");
+  if (rc != DSV32_OK) return rc;
   dim3 grid(2, t, p.splits);
   sfa_tc_kernel<<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
   count_launch();

@@ -33,17 +33,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe (try_wait may suspend the thread for a while before it answers "not yet"): for loops
+// that poll several barriers.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Returns false on timeout (status recorded with `where`).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t where) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (true) {
+    // try_wait with a suspend-time hint: the warp sleeps in hardware until the phase completes (or the
+    // hint expires), so a waiting warp does not burn issue slots that the working warps need
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
+        : "memory");
+    if (ok) return true;
     if (clock64() - t0 > kWaitBudgetCycles) {
       report_status(status, DSV32_STATUS_TIMEOUT, where, blockIdx.x);
       return false;
     }
   }
-  return true;
 }
 
 // ---- TMA (tiled, 2-D, no multicast) -----------------------------------------------------------------

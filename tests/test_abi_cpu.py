@@ -37,8 +37,9 @@ def test_library_exports_every_declared_symbol(lib):
 
 
 def test_workspace_queries(lib):
-    assert lib.dsv32_sfa_workspace_bytes(64, 2, 128, 2048, 0) == 0  # enough CTAs: single split
-    assert lib.dsv32_sfa_workspace_bytes(4, 1, 128, 2048, 0) > 0
+    # the row id of every selected key; key-split partials only when there are too few CTAs for one split
+    assert lib.dsv32_sfa_workspace_bytes(64, 2, 128, 2048, 0) == 64 * 2 * 2048 * 4
+    assert lib.dsv32_sfa_workspace_bytes(4, 1, 128, 2048, 0) > 4 * 2048 * 4
     assert lib.dsv32_indexer_workspace_bytes(2, 2, 4, 128) == 2 * 2 * 4 * 128 * 4
     assert lib.dsv32_prolog_workspace_bytes(16) > 0
     assert lib.dsv32_prolog_workspace_bytes(0) == 0
