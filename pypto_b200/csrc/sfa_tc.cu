@@ -11,8 +11,11 @@
 // Shared memory: Q dims 256..575 (five 128x64 bf16 chunks, 128-byte swizzle, loaded by TMA) and two K
 // stages of 64 gathered keys x 576 dims (nine 64x64 bf16 chunks, 128-byte swizzle).  A stage is read
 // K-major by S = Q K^T and MN-major (as V) by O += P V, so the dequantised rows are written once.
-// Warps: 0 = MMA issuer / tensor-memory owner, 1..4 = softmax + O rescale + epilogue (one head per thread,
-// so row max / row sum need no shuffles), 5..12 = gather + dequantise producers.
+// Warps: 0 = issuer of the S MMAs / tensor-memory owner, 1..4 = softmax + O rescale + epilogue (one head per
+// thread, so row max / row sum need no shuffles; lane 0 of warp 1 also issues the PV MMAs), 5..12 = gather +
+// dequantise producers.  A stage is refilled in two steps: the chunks only S reads (the other half's value
+// dims, the rope dims) as soon as S of the tile two back has completed, this CTA's own value chunks once its
+// PV has.  The cache row of every selected key comes from a pre-pass (sfa_row_ids_kernel).
 // The running maximum is only raised when a tile exceeds it by more than 2^8 (warp-uniform decision), so
 // the read-modify-write of O in tensor memory is rare; P stays below 2^8 in between.
 #include "kernels.cuh"
@@ -49,11 +52,6 @@ __device__ unsigned long long g_sfa_trace[4][40][8];
 #define ST_TRACE(tile, slot) do { } while (0)
 #endif
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-#ifdef DSV32_X_SPARTS
-constexpr int kSParts = DSV32_X_SPARTS;
-#else
-constexpr int kSParts = 1;     // S of a tile is issued in this many parts (1, 2 or 4); splitting measured slower
-#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -191,7 +189,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       tma_load_2d(q_s + 4 * kStQChunkBytes, &qr_map, 0, tok * p.nq, q_bar);
 
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, kStTile, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 256, false, true);
       bool ok = mbar_wait(q_bar, 0, p.status, 10);
 
       // Descriptors are assembled from precomputed 32-bit halves: per MMA only the start-address field moves.
@@ -202,74 +199,34 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         return d;
       };
       const uint32_t q_lo = ((smem_u32(q_s) >> 4) & 0x3FFFu) | (1u << 16);
-      uint32_t stage_lo[2], v_lo[2];
+      uint32_t stage_lo[2];
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const uint32_t a = smem_u32(k_s + s * kStStageBytes);
-        stage_lo[s] = ((a >> 4) & 0x3FFFu) | (1u << 16);                                              // K-major (S)
-        v_lo[s] = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);  // MN-major (V)
-      }
+      for (int s = 0; s < 2; ++s)
+        stage_lo[s] = ((smem_u32(k_s + s * kStStageBytes) >> 4) & 0x3FFFu) | (1u << 16);   // K-major (S)
 
-      // S of one tile is issued in four parts of nine MMAs, so that a PV whose P has just become ready does
-      // not wait behind a whole S (MMAs execute in issue order; S and PV use different accumulators).
-      auto issue_s_part = [&](int i, int part) {
+      // This thread issues S = Q K^T of every tile; PV is issued by a thread of the softmax group as soon as
+      // P is stored, so that it never waits behind the issue of the next S (this thread blocks while the
+      // tensor-core queue is full).  MMAs of both threads execute in the order they enter the queue; S(i+2),
+      // which overwrites the buffer PV(i) reads P from, is only issued after the producers have seen PV(i)
+      // complete (they refill its K stage before signalling `full`).
+      for (int i = 0; ok && i < ntiles; ++i) {
         const int s = i & 1;
-        if (part == 0) {
-          ST_TRACE(i, 2);
-          tc_fence_after();
-        }
+        ok = mbar_wait(&full_bar[s], (i >> 1) & 1, p.status, 11);
+        if (!ok) break;
+        ST_TRACE(i, 2);
+        tc_fence_after();
         const uint32_t d = tmem_base + kColS + s * kStTile;
         const uint32_t klo = stage_lo[s];
 #pragma unroll
-        for (int ks = 0; ks < 36; ++ks) {
-          if (ks / (36 / kSParts) != part) continue;
-          const uint64_t kd = desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4));
-          if (ks < 16)  // Q dims 0..255 from tensor memory
-            umma_f16_ts(d, tmem_base + kColQ + ks * 8, kd, idesc_s, ks > 0 ? 1u : 0u);
-          else          // Q dims 256..575 from shared memory
-            umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)), kd, idesc_s, 1u);
-        }
-        if (part == kSParts - 1) {
-          umma_commit(&sfull_bar[s]);
-          ST_TRACE(i, 3);
-        }
-      };
-      auto issue_pv = [&](int i) {
-        const int s = i & 1;
-        ST_TRACE(i, 4);
-        tc_fence_after();
+        for (int ks = 0; ks < 16; ++ks)  // Q dims 0..255 from tensor memory
+          umma_f16_ts(d, tmem_base + kColQ + ks * 8, desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)),
+                      idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
-          umma_f16_ts(tmem_base + kColO, tmem_base + kColS + s * kStTile + kk * 8, desc(v_lo[s] + ((kk * 2048) >> 4)),
-                      idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&pvdone_bar[s]);
-        ST_TRACE(i, 5);
-      };
-      // Issue whichever is ready, PV first: finishing PV(i) frees K stage i for the producers.  (S(i) never
-      // overtakes PV(i-2): it is only started once that PV has been issued.)
-      int next_s = 0, next_pv = 0, s_part = 0;  // s_part > 0: S(next_s) is partly issued
-      long long t_idle = clock64();
-      while (ok && next_pv < ntiles) {
-        if (next_pv < next_s && mbar_test_wait(&pready_bar[next_pv & 1], (next_pv >> 1) & 1)) {
-          issue_pv(next_pv++);
-          t_idle = clock64();
-        } else if (s_part > 0) {
-          switch (s_part) {
-            case 1: issue_s_part(next_s, 1); break;
-            case 2: issue_s_part(next_s, 2); break;
-            default: issue_s_part(next_s, 3); break;
-          }
-          if (++s_part == kSParts) { s_part = 0; ++next_s; }
-          t_idle = clock64();
-        } else if (next_s < ntiles && next_s < next_pv + 2 && mbar_test_wait(&full_bar[next_s & 1], (next_s >> 1) & 1)) {
-          issue_s_part(next_s, 0);
-          s_part = 1;
-          if (s_part == kSParts) { s_part = 0; ++next_s; }
-          t_idle = clock64();
-        } else if (clock64() - t_idle > kWaitBudgetCycles) {
-          report_status(p.status, DSV32_STATUS_TIMEOUT, 11, blockIdx.y);
-          ok = false;
-        }
+        for (int ks = 16; ks < 36; ++ks)  // Q dims 256..575 from shared memory
+          umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
+                      desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
+        umma_commit(&sfull_bar[s]);
+        ST_TRACE(i, 3);
       }
     }
   } else if (warp <= 4) {
@@ -361,6 +318,30 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pready_bar[s]);
+      if (warp == 1) {  // second MMA issuer: PV of this tile, as soon as all four softmax warps have stored P
+        bool okpv = true;
+        if (lane == 0) {
+          okpv = mbar_wait(&pready_bar[s], (i >> 1) & 1, p.status, 13);
+          if (okpv) {
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 256, false, true);
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+            const uint32_t a = smem_u32(k_s + s * kStStageBytes);
+            const uint32_t vlo = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);
+            ST_TRACE(i, 4);
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
+              uint64_t d;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(vlo + ((kk * 2048) >> 4)), "r"(kDescHi));
+              umma_f16_ts(tmem_base + kColO, tmem_base + kColS + s * kStTile + kk * 8, d, idesc_pv,
+                          (i > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(&pvdone_bar[s]);
+            ST_TRACE(i, 5);
+          }
+        }
+        if (!__all_sync(0xffffffffu, okpv)) { ok = false; break; }
+      }
     }
     // ---- epilogue: O / l -> bf16 (or fp32 partial + log-sum-exp for a key split) -----------------------------
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pvdone_bar[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, p.status, 22));
@@ -502,11 +483,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       // Once S of tile i-2 has completed, every chunk of the stage except this CTA's own value chunks is free
       // (both waits pass at once for i < 2): that part of the refill runs under the softmax and PV of tile i-2.
       const uint32_t prev = ((i >> 1) & 1) ^ 1;
-#ifdef DSV32_X_LATE_OTHER
-      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], prev, p.status, 30))) break;
-#else
       if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], prev, p.status, 30))) break;
-#endif
       if (ptid == 0) ST_TRACE(i, 0);
       commit_other(i, 0, pf0);
       commit_other(i, 1, pf1);
