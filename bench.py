@@ -56,8 +56,8 @@ def indexer_bytes_per_request(ctx, s1):
 # DRAM traffic per unit from the ncu capture summarised in profiles/tcgen05_kernels_b16_ctx64k.md
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch / units of that launch); it grows in proportion
 # to the units, so a full launch is units x this figure.
-NCU_SFA_TRAFFIC_PER_TOKEN = (51.919872e6 + 0.655360e6) / 32
-NCU_INDEXER_TRAFFIC_PER_REQUEST = (136.647680e6 + 6.585344e6) / 16
+NCU_SFA_TRAFFIC_PER_TOKEN = (51.868672e6 + 0.504832e6) / 32
+NCU_INDEXER_TRAFFIC_PER_REQUEST = (136.643584e6 + 5.581312e6) / 16
 
 
 def prolog_bytes_per_call(t):
