@@ -1,10 +1,10 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures in this directory from the UNMODIFIED reference goldens.
 
-Run in a container that has the reference checkout (default /root/reference, or
+Run where the reference checkout is available, with its root as the argument (or in
 $DSV32_REFERENCE_ROOT):
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <reference root>
 
 The reference's torch-CPU golden functions live in its operator test files.  Those
 files import `pypto` and `torch_npu` at module level; both are replaced here by
@@ -30,7 +30,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("DSV32_REFERENCE_ROOT", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DSV32_REFERENCE_ROOT", "")
 MODEL_DIR = os.path.join(REF, "models", "deepseek_v32_exp")
 
 

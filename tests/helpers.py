@@ -130,7 +130,8 @@ def prolog_reference_inputs(seed, b, s1, s2):
 
 
 def gen_sfa_inputs(seed, act_seq, s1=1, nq=128, topk=2048, block_size=128, pad_short=True, extra_blocks=0):
-    """Seeded synthetic SFA inputs in the operator's layouts (see DESIGN: config 0 distributions)."""
+    """Seeded synthetic SFA inputs in the operator's layouts: standard-normal bf16 queries and rope keys, full-range
+    int8 latent keys, scales uniform in [0.001, 0.02]."""
     g = torch.Generator().manual_seed(seed)
     b = len(act_seq)
     t = b * s1
