@@ -40,6 +40,9 @@ extern "C" {
  * (models/deepseek_v32_exp/sparse_flash_attention_quant_impl.py:655-674, 734, 572; compute
  * body :45-286).  For token t = b_idx*s1 + i only the first
  * K = min(max(act_seq[b_idx] - s1 + 1 + i, 0), topk) entries of topk_indices[t] are used.
+ * The workspace (always required; size from dsv32_sfa_workspace_bytes) holds the resolved cache
+ * row of every selected key and, when the keys of a token are split over several CTAs, the
+ * fp32 partial outputs.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   const void* query_nope;        /* bf16 [b*s1*n_q, 512]                  */
