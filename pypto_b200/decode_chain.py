@@ -80,3 +80,57 @@ class SparseDecodeStep:
         self.step()
         self.host_out.copy_(self.out, non_blocking=True)
         return self.host_out
+
+
+class HostPipelinedDecode:
+    """End-to-end decode loop with the host traffic overlapped with compute.
+
+    Every step still copies its own activations from pinned host memory and returns its own attention
+    output to pinned host memory, but on separate streams: while step k runs, the inputs of step k+1 are
+    copied in and the output of step k-1 is copied out (two device buffers per direction, events between the
+    three streams).  `submit(host_inputs)` enqueues one step and returns the pinned tensor its output will land
+    in; `drain()` makes the current stream wait for everything submitted so far.
+    """
+
+    def __init__(self, step: SparseDecodeStep):
+        self.step = step
+        dev = step.out.device
+        self.dev = dev
+        self.s_in = torch.cuda.Stream(dev)
+        self.s_out = torch.cuda.Stream(dev)
+        self.dev_in = [dict(step._dev_in), {k: torch.empty_like(v) for k, v in step._dev_in.items()}]
+        self.dev_out = [step.out, torch.empty_like(step.out)]
+        self.host_out = [torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory() for _ in range(2)]
+        self.in_ready = [torch.cuda.Event() for _ in range(2)]
+        self.run_done = [torch.cuda.Event() for _ in range(2)]
+        self.out_done = [torch.cuda.Event() for _ in range(2)]
+        self.k = 0
+
+    def submit(self, host_inputs):
+        step, p = self.step, self.k & 1
+        run = torch.cuda.current_stream(self.dev)
+        if self.k >= 2:
+            self.s_in.wait_event(self.run_done[p])      # the step two back has finished reading this input buffer
+        else:
+            self.s_in.wait_stream(run)                   # everything enqueued before the first steps
+        with torch.cuda.stream(self.s_in):
+            for name, h in host_inputs.items():
+                self.dev_in[p][name].copy_(h, non_blocking=True)
+            self.in_ready[p].record(self.s_in)
+        run.wait_event(self.in_ready[p])
+        if self.k >= 2:
+            run.wait_event(self.out_done[p])             # its output buffer has been copied out
+        step._dev_in, step.out = self.dev_in[p], self.dev_out[p]
+        step.step()
+        self.run_done[p].record(run)
+        self.s_out.wait_event(self.run_done[p])
+        with torch.cuda.stream(self.s_out):
+            self.host_out[p].copy_(self.dev_out[p], non_blocking=True)
+            self.out_done[p].record(self.s_out)
+        self.k += 1
+        return self.host_out[p]
+
+    def drain(self):
+        run = torch.cuda.current_stream(self.dev)
+        for e in self.out_done[: min(self.k, 2)]:
+            run.wait_event(e)

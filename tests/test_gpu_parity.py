@@ -554,3 +554,45 @@ def test_mla_indexer_prolog_seeded_vs_oracle(t):
     # accumulation order) move a few more elements past the reference tolerance, so allow 1.5 % error points;
     # the indexer's per-head scale is a maximum over 128 sums of those differences and moves with them (5 %)
     _check_mla(_run_mla(inp, ip), ref, ip, inp, ratio=0.015, scale_ratio=0.05)
+
+
+# --------------------------------------------------------------------------------------------------
+# decode loop with host I/O on separate streams
+# --------------------------------------------------------------------------------------------------
+def test_host_pipelined_decode_matches_serial_steps():
+    """Six steps with two alternating sets of host activations through the three-stream loop give, step by step,
+    the outputs of the serial host path (copy in, run, copy out on one stream)."""
+    from pypto_b200 import synth
+    from pypto_b200.decode_chain import HostPipelinedDecode, SparseDecodeStep
+    w = synth.make_decode_workload([3000, 700, 2600, 129], 2, 77, DEV)
+    step = SparseDecodeStep(w)
+    step.enable_host_io()
+    set_a = step.host_in
+    g = torch.Generator().manual_seed(5)
+    set_b = dict(set_a)
+    for name in ("q_nope", "q_rope", "x"):
+        set_b[name] = (torch.randn(set_a[name].shape, generator=g) * 0.5).to(set_a[name].dtype).pin_memory()
+    want = {}
+    for tag, hs in (("a", set_a), ("b", set_b)):
+        step.host_in = hs
+        want[tag] = step.step_from_host().clone()
+        torch.cuda.synchronize()
+        want[tag] = step.host_out.clone()
+    assert not torch.equal(want["a"], want["b"])
+    pipe = HostPipelinedDecode(step)
+    outs = []
+    for k in range(6):
+        tag = "ab"[k % 2] if k < 4 else "ba"[k % 2]
+        buf = pipe.submit(set_a if tag == "a" else set_b)
+        if k >= 1:  # the output of the previous step may be read once its copy has completed
+            pipe.out_done[(k - 1) & 1].synchronize()
+            outs.append((prev_tag, pipe.host_out[(k - 1) & 1].clone()))
+        prev_tag = tag
+    pipe.drain()
+    torch.cuda.synchronize()
+    outs.append((prev_tag, buf.clone()))
+    import pypto_b200
+    pypto_b200.check_status()
+    assert len(outs) == 6
+    for tag, o in outs:
+        assert torch.equal(o, want[tag])
