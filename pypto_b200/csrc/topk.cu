@@ -14,6 +14,13 @@
 
 namespace dsv32 {
 
+#ifdef DSV32_TOPK_TRACE
+__device__ unsigned long long g_topk_trace[16];
+#define TK_TRACE(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_topk_trace[slot] = clock64(); } while (0)
+#else
+#define TK_TRACE(slot) do { } while (0)
+#endif
+
 constexpr int kTopkThreads = 1024;
 constexpr int kTopkMaxK = 2048;
 constexpr int kHistBins = 4096;
@@ -161,6 +168,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   };
 
   bool emitted = false;
+  TK_TRACE(0);
   if (n > 0 && irow == nullptr) {
     // ---- fast path: scan 1 = histogram of the top 12 key bits (vectorised when the row is 16-byte aligned) ----
     for (int i = tid; i < kHistBins; i += kTopkThreads) hist[i] = 0;
@@ -192,8 +200,10 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
     }
     for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) atomicAdd(&hist[float_to_key(srow[j]) >> 20], 1u);
     __syncthreads();
+    TK_TRACE(1);
     uint32_t total;
     narrow(st, hist, warp_tot, s_tmp, 52, 0xFFFu, total);
+    TK_TRACE(2);
     if (!st.done && s_tmp[2] <= static_cast<uint32_t>(kCandCap)) {
       // ---- scan 2: winners go to the output list, the threshold bucket to the candidate list ---------------
       const uint32_t bin = static_cast<uint32_t>(st.prefix >> 52);
@@ -208,16 +218,37 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
       {
         int j = tid;
         for (; j + 3 * kTopkThreads < n4; j += 4 * kTopkThreads) {
+          // sixteen entries per thread: count first, reserve the slots of both lists with one atomic each,
+          // then store -- instead of one divergent atomic per entry
           float4 v[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) v[u] = srow4[j + u * kTopkThreads];
+          uint32_t nw = 0, nt = 0;
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const int e = 4 * (j + u * kTopkThreads);
-            place(v[u].x, e);
-            place(v[u].y, e + 1);
-            place(v[u].z, e + 2);
-            place(v[u].w, e + 3);
+            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t b = float_to_key(f[q]) >> 20;
+              nw += (b > bin) ? 1u : 0u;
+              nt += (b == bin) ? 1u : 0u;
+            }
+          }
+          if ((nw | nt) == 0) continue;
+          uint32_t pw = nw ? atomicAdd(&s_nsel, nw) : 0u;
+          uint32_t pt = nt ? atomicAdd(&s_ncand, nt) : 0u;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t k32 = float_to_key(f[q]);
+              const uint32_t b = k32 >> 20;
+              const uint64_t c = (static_cast<uint64_t>(k32) << 32) |
+                                 static_cast<uint64_t>(0xFFFFFFFFu - (idb + 4 * (j + u * kTopkThreads) + q));
+              if (b > bin) sel[pw++] = c;
+              else if (b == bin) cand[pt++] = c;
+            }
           }
         }
         for (; j < n4; j += kTopkThreads) {
@@ -230,12 +261,14 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
       }
       for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) place(srow[j], j);
       __syncthreads();
+      TK_TRACE(3);
       const int ncand = static_cast<int>(s_ncand);
       auto from_cand = [&](int j, uint64_t& c) -> bool {
         c = cand[j];
         return true;
       };
       radix_passes(st, 1, ncand, from_cand, hist, warp_tot, s_tmp);
+      TK_TRACE(4);
       for (int j = tid; j < ncand; j += kTopkThreads) {
         const uint64_t c = cand[j];
         if ((c & st.mask) >= st.prefix) sel[atomicAdd(&s_nsel, 1u)] = c;
@@ -265,23 +298,78 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   while (npad < nsel) npad <<= 1;
   for (int i = tid; i < npad; i += kTopkThreads)
     if (i >= nsel) sel[i] = 0ull;
+  TK_TRACE(5);
   // ---- bitonic sort, descending ------------------------------------------------------------------------------
-  for (int size = 2; size <= npad; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+  // Thread t owns elements 2t and 2t+1.  Compare-exchange steps with a stride of 32 or less stay inside a
+  // warp (stride 1 inside the thread, the others by shuffle), so only the steps with a stride of 64 or more
+  // go through shared memory and a block barrier: 15 of the 66 steps of a 2048-element sort.
+  if (npad >= 64) {
+    const int lane = tid & 31;
+    const bool active = tid < (npad >> 1);  // whole warps: npad/2 is a multiple of 32
+    const int e0 = 2 * tid;
+    auto warp_steps = [&](uint64_t& a, uint64_t& b, int size, int first_stride) {
+      const bool up = ((e0 & size) == 0);
+      for (int stride = first_stride; stride >= 2; stride >>= 1) {
+        const uint64_t pa = __shfl_xor_sync(0xffffffffu, a, stride >> 1);
+        const uint64_t pb = __shfl_xor_sync(0xffffffffu, b, stride >> 1);
+        const bool keep_max = (((e0 & stride) == 0) == up);
+        a = keep_max ? (a > pa ? a : pa) : (a < pa ? a : pa);
+        b = keep_max ? (b > pb ? b : pb) : (b < pb ? b : pb);
+      }
+      if ((a < b) == up) {  // stride 1
+        const uint64_t t = a;
+        a = b;
+        b = t;
+      }
+    };
+    __syncthreads();
+    if (active) {
+      uint64_t a = sel[e0], b = sel[e0 + 1];
+      for (int size = 2; size <= 64; size <<= 1) warp_steps(a, b, size, size >> 1);
+      sel[e0] = a;
+      sel[e0 + 1] = b;
+    }
+    for (int size = 128; size <= npad; size <<= 1) {
+      for (int stride = size >> 1; stride >= 64; stride >>= 1) {
+        __syncthreads();
+        if (active) {
+          const int i = 2 * tid - (tid & (stride - 1));
+          const int j = i + stride;
+          const bool up = ((i & size) == 0);
+          const uint64_t a = sel[i], b = sel[j];
+          if ((a < b) == up) {
+            sel[i] = b;
+            sel[j] = a;
+          }
+        }
+      }
       __syncthreads();
-      for (int t = tid; t < (npad >> 1); t += kTopkThreads) {
-        const int i = 2 * t - (t & (stride - 1));
-        const int j = i + stride;
-        const bool up = ((i & size) == 0);
-        const uint64_t a = sel[i], b = sel[j];
-        if ((a < b) == up) {
-          sel[i] = b;
-          sel[j] = a;
+      if (active) {
+        uint64_t a = sel[e0], b = sel[e0 + 1];
+        warp_steps(a, b, size, 32);
+        sel[e0] = a;
+        sel[e0 + 1] = b;
+      }
+    }
+  } else {
+    for (int size = 2; size <= npad; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        __syncthreads();
+        for (int t = tid; t < (npad >> 1); t += kTopkThreads) {
+          const int i = 2 * t - (t & (stride - 1));
+          const int j = i + stride;
+          const bool up = ((i & size) == 0);
+          const uint64_t a = sel[i], b = sel[j];
+          if ((a < b) == up) {
+            sel[i] = b;
+            sel[j] = a;
+          }
         }
       }
     }
   }
   __syncthreads();
+  TK_TRACE(6);
   for (int i = tid; i < p.k; i += kTopkThreads) {
     if (i < nsel) {
       const uint64_t c = sel[i];
@@ -293,6 +381,14 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
     }
   }
 }
+
+#ifdef DSV32_TOPK_TRACE
+}  // namespace dsv32
+extern "C" int dsv32_debug_topk_trace(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, dsv32::g_topk_trace, sizeof(dsv32::g_topk_trace));
+}
+namespace dsv32 {
+#endif
 
 int launch_topk(const TopkParams& p, int rows, cudaStream_t stream) {
   if (rows <= 0) return DSV32_OK;
