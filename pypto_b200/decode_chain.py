@@ -73,6 +73,33 @@ class SparseDecodeStep:
         self.attention()
         return self.out
 
+    # ---- CUDA graphs ------------------------------------------------------------------------------------
+    def capture(self, per_stage=False):
+        """Capture the step on its current input / output buffers into CUDA graphs (one graph, or one per stage
+        so that events can be recorded between the stages).  Returns the list of graphs; `replay()` runs them
+        in order on the current stream.  The buffers captured are the ones the step points at now."""
+        dev = self.out.device
+        cur = torch.cuda.current_stream(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):  # warm-up outside capture: lazy initialisation, tensor maps, allocator
+            self.step()
+        cur.wait_stream(side)
+        stages = (self.prolog, self.indexer, self.attention) if per_stage else (self.step,)
+        graphs = []
+        for fn in stages:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            graphs.append(g)
+        self.graphs = graphs
+        return graphs
+
+    def replay(self):
+        for g in self.graphs:
+            g.replay()
+        return self.out
+
     def step_from_host(self):
         """End-to-end step: pinned host activations -> device, the three stages, output -> pinned host."""
         for k, h in self.host_in.items():
@@ -92,19 +119,25 @@ class HostPipelinedDecode:
     in; `drain()` makes the current stream wait for everything submitted so far.
     """
 
-    def __init__(self, step: SparseDecodeStep):
+    def __init__(self, step: SparseDecodeStep, use_graphs=False):
         self.step = step
         dev = step.out.device
         self.dev = dev
         self.s_in = torch.cuda.Stream(dev)
         self.s_out = torch.cuda.Stream(dev)
-        self.dev_in = [dict(step._dev_in), {k: torch.empty_like(v) for k, v in step._dev_in.items()}]
+        self.dev_in = [dict(step._dev_in), {k: v.clone() for k, v in step._dev_in.items()}]  # both sets valid from the start
         self.dev_out = [step.out, torch.empty_like(step.out)]
         self.host_out = [torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory() for _ in range(2)]
         self.in_ready = [torch.cuda.Event() for _ in range(2)]
         self.run_done = [torch.cuda.Event() for _ in range(2)]
         self.out_done = [torch.cuda.Event() for _ in range(2)]
         self.k = 0
+        self.graphs = None
+        if use_graphs:  # one captured step per buffer pair
+            self.graphs = []
+            for p in range(2):
+                step._dev_in, step.out = self.dev_in[p], self.dev_out[p]
+                self.graphs.append(step.capture()[0])
 
     def submit(self, host_inputs):
         step, p = self.step, self.k & 1
@@ -121,7 +154,10 @@ class HostPipelinedDecode:
         if self.k >= 2:
             run.wait_event(self.out_done[p])             # its output buffer has been copied out
         step._dev_in, step.out = self.dev_in[p], self.dev_out[p]
-        step.step()
+        if self.graphs is not None:
+            self.graphs[p].replay()
+        else:
+            step.step()
         self.run_done[p].record(run)
         self.s_out.wait_event(self.run_done[p])
         with torch.cuda.stream(self.s_out):

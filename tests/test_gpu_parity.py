@@ -596,3 +596,30 @@ def test_host_pipelined_decode_matches_serial_steps():
     assert len(outs) == 6
     for tag, o in outs:
         assert torch.equal(o, want[tag])
+
+
+def test_captured_step_matches_eager_step():
+    """The step replayed from CUDA graphs (whole, per stage, and inside the host-pipelined loop) writes the same
+    bits as the eager step."""
+    import pypto_b200
+    from pypto_b200 import synth
+    from pypto_b200.decode_chain import HostPipelinedDecode, SparseDecodeStep
+    w = synth.make_decode_workload([2500, 300, 4100], 2, 78, DEV)
+    step = SparseDecodeStep(w)
+    want = step.step().clone()
+    want_topk = step.topk_res.clone()
+    torch.cuda.synchronize()
+    for per_stage in (False, True):
+        step.capture(per_stage=per_stage)
+        step.out.zero_()
+        step.topk_res.zero_()
+        got = step.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want) and torch.equal(step.topk_res, want_topk)
+    step.enable_host_io()
+    pipe = HostPipelinedDecode(step, use_graphs=True)
+    bufs = [pipe.submit(step.host_in) for _ in range(3)]
+    pipe.drain()
+    torch.cuda.synchronize()
+    pypto_b200.check_status()
+    assert torch.equal(bufs[-1], want.cpu()) and torch.equal(bufs[-2], want.cpu())
