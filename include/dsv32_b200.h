@@ -67,6 +67,34 @@ size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t top
 int dsv32_sfa_quant(const Dsv32SfaArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The same attention over the fused cache layout ("store 8, compute 16"): one 656-byte row per
+ * token = 512 int8 latent dims | 64 bf16 rope dims | 4 fp32 scales (one per 128-dim group).
+ * Replaces sparse_attention_antiquant_d / _p / _d_950
+ * (models/deepseek_v32_exp/sparse_attention_antiquant_impl.py:287-356, 358-420, 739-768;
+ * row layout: deepseekv32_sparse_attention_antiquant.py:262-272).  Workspace and status as for
+ * dsv32_sfa_quant (dsv32_sfa_workspace_bytes).
+ * ------------------------------------------------------------------------------------- */
+#define DSV32_ANTIQUANT_ROW_BYTES 656
+typedef struct {
+  const void* query_nope;        /* bf16 [b*s1*n_q, 512]                  */
+  const void* query_rope;        /* bf16 [b*s1*n_q, 64]                   */
+  const void* nope_cache;        /* int8 [rows, 656]                      */
+  const int32_t* topk_indices;   /* int32 [b*s1, topk]                    */
+  const int32_t* block_table;    /* int32 [b, max_blocks]                 */
+  const int32_t* kv_act_seqs;    /* int32 [b]                             */
+  void* attention_out;           /* bf16 [b, s1, n_q, 512]                */
+  void* workspace;               /* >= dsv32_sfa_workspace_bytes(...)     */
+  size_t workspace_bytes;
+  uint32_t* status;              /* device uint32[4] or NULL              */
+  int64_t rows;                  /* block_num * block_size                */
+  int32_t b, s1, n_q, topk, block_size, max_blocks;
+  int32_t kv_splits;             /* 0 = choose automatically              */
+  float softmax_scale;
+} Dsv32SaAntiquantArgs;
+
+int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * Lightning indexer: int8 q.k scores (+ReLU, 2^-11, fp16 round, per-head weighted sum,
  * key scale) and top-k selection.
  * Replaces lightning_indexer_decode

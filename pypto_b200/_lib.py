@@ -24,6 +24,16 @@ class SfaArgs(C.Structure):
     ]
 
 
+class SaAntiquantArgs(C.Structure):
+    _fields_ = [
+        ("query_nope", c_void_p), ("query_rope", c_void_p), ("nope_cache", c_void_p), ("topk_indices", c_void_p),
+        ("block_table", c_void_p), ("kv_act_seqs", c_void_p), ("attention_out", c_void_p), ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t), ("status", c_void_p), ("rows", c_i64), ("b", c_i32), ("s1", c_i32),
+        ("n_q", c_i32), ("topk", c_i32), ("block_size", c_i32), ("max_blocks", c_i32), ("kv_splits", c_i32),
+        ("softmax_scale", c_float),
+    ]
+
+
 class IndexerArgs(C.Structure):
     _fields_ = [
         ("idx_query", c_void_p), ("idx_query_scale", c_void_p), ("idx_key_cache", c_void_p),
@@ -70,6 +80,7 @@ EXPORTS = {
     "dsv32_launch_count": (C.c_uint64, []),
     "dsv32_sfa_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32, c_i32]),
     "dsv32_sfa_quant": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
+    "dsv32_sparse_attention_antiquant": (c_i32, [C.POINTER(SaAntiquantArgs), c_void_p]),
     "dsv32_indexer_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
     "dsv32_indexer_topk": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
     "dsv32_indexer_topk_noalloc": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),

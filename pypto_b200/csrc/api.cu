@@ -78,7 +78,7 @@ size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t top
   return bytes;
 }
 
-int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
+static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, int rope_stride, int scale_stride) {
   REQUIRE(a != nullptr, "sfa: args is NULL");
   REQUIRE(a->b >= 0 && a->s1 >= 1, "sfa: bad b=%d s1=%d", a->b, a->s1);
   if (a->b == 0) return DSV32_OK;
@@ -115,6 +115,7 @@ int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
   for (int sh = 0; sh < 31; ++sh)
     if ((1 << sh) == a->block_size) p.bs_shift = sh;
   p.max_blocks = a->max_blocks; p.splits = splits; p.scale = a->softmax_scale;
+  p.nope_stride = nope_stride; p.rope_stride = rope_stride; p.scale_stride = scale_stride;
   {
     const size_t need = dsv32_sfa_workspace_bytes(a->b, a->s1, a->n_q, a->topk, splits);
     if (a->workspace == nullptr || a->workspace_bytes < need ||
@@ -138,6 +139,33 @@ int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) {
   }();
   if (use_mma || a->n_q != 128) return launch_sfa_mma(p, static_cast<cudaStream_t>(cuda_stream));
   return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) { return sfa_run(a, cuda_stream, kKvLora, kRopeDim * 2, 16); }
+
+int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "sa_antiquant: args is NULL");
+  REQUIRE(a->b <= 0 || a->nope_cache != nullptr, "sa_antiquant: NULL cache pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->nope_cache) % 16 == 0, "sa_antiquant: the cache must be 16-byte aligned");
+  // one row = 512 int8 latent dims | 64 bf16 rope dims | 4 fp32 group scales
+  const char* cache = static_cast<const char*>(a->nope_cache);
+  Dsv32SfaArgs s{};
+  s.query_nope = a->query_nope;
+  s.query_rope = a->query_rope;
+  s.key_nope = cache;
+  s.key_rope = cache + kKvLora;
+  s.k_nope_scales = reinterpret_cast<const float*>(cache + kKvLora + kRopeDim * 2);
+  s.topk_indices = a->topk_indices;
+  s.block_table = a->block_table;
+  s.kv_act_seqs = a->kv_act_seqs;
+  s.attention_out = a->attention_out;
+  s.workspace = a->workspace;
+  s.workspace_bytes = a->workspace_bytes;
+  s.status = a->status;
+  s.rows = a->rows;
+  s.b = a->b; s.s1 = a->s1; s.n_q = a->n_q; s.topk = a->topk; s.block_size = a->block_size;
+  s.max_blocks = a->max_blocks; s.kv_splits = a->kv_splits; s.softmax_scale = a->softmax_scale;
+  return sfa_run(&s, cuda_stream, DSV32_ANTIQUANT_ROW_BYTES, DSV32_ANTIQUANT_ROW_BYTES, DSV32_ANTIQUANT_ROW_BYTES);
 }
 
 // ---- lightning indexer --------------------------------------------------------------------------------

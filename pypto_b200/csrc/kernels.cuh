@@ -51,6 +51,9 @@ struct SfaParams {
   long long rows;
   int b, s1, nq, topk, block_size, max_blocks, splits;
   int bs_shift;  // log2(block_size) when it is a power of two, else -1
+  // byte distance between consecutive cache rows in each of the three arrays: 512 / 128 / 16 for separate
+  // arrays, 656 / 656 / 656 when the three parts of a row sit side by side in one array
+  int nope_stride, rope_stride, scale_stride;
   float scale;
 };
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);

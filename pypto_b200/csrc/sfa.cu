@@ -109,11 +109,11 @@ __global__ void __launch_bounds__(kSfaThreads, 1) sfa_mma_kernel(SfaParams p) {
         }
         if (row >= 0) {
           pf.valid = true;
-          const int4* src = reinterpret_cast<const int4*>(p.k_nope + row * kKvLora);
+          const int4* src = reinterpret_cast<const int4*>(reinterpret_cast<const unsigned char*>(p.k_nope) + row * p.nope_stride);
 #pragma unroll
           for (int q = 0; q < 4; ++q) pf.nope[q] = __ldg(src + gpart + 8 * q);
-          pf.rope = __ldg(reinterpret_cast<const int4*>(p.k_rope + row * kRopeDim) + gpart);
-          pf.sc = __ldg(reinterpret_cast<const float4*>(p.k_scales + row * 4));
+          pf.rope = __ldg(reinterpret_cast<const int4*>(reinterpret_cast<const unsigned char*>(p.k_rope) + row * p.rope_stride) + gpart);
+          pf.sc = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const unsigned char*>(p.k_scales) + row * p.scale_stride));
         }
       }
     }

@@ -412,12 +412,22 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     auto row_of = [&](int tile, int pass) -> long long {  // -1 = none
       return static_cast<long long>(ring[(tile & 3) * 8 + pass * 4 + (lane >> 3)]) - 1;
     };
-    auto l2_prefetch = [&](long long row) {  // the 656 bytes of a row: lanes 0..3 nope lines, 4 rope, 5 scales
+    const unsigned char* nope_b = reinterpret_cast<const unsigned char*>(p.k_nope);
+    const unsigned char* rope_b = reinterpret_cast<const unsigned char*>(p.k_rope);
+    const unsigned char* scale_b = reinterpret_cast<const unsigned char*>(p.k_scales);
+    const bool fused_rows = p.nope_stride != kKvLora;  // one 656-byte row holds all three parts
+    auto l2_prefetch = [&](long long row) {  // the 128-byte lines of a row, one per thread column
       if (row < 0) return;
       const void* a = nullptr;
-      if (gpart < 4) a = p.k_nope + row * kKvLora + gpart * 128;
-      else if (gpart == 4) a = p.k_rope + row * kRopeDim;
-      else if (gpart == 5) a = p.k_scales + row * 4;
+      if (fused_rows) {
+        if (gpart < 6) a = nope_b + row * p.nope_stride + gpart * 128;  // 656 bytes touch at most six lines
+      } else if (gpart < 4) {
+        a = nope_b + row * p.nope_stride + gpart * 128;
+      } else if (gpart == 4) {
+        a = rope_b + row * p.rope_stride;
+      } else if (gpart == 5) {
+        a = scale_b + row * p.scale_stride;
+      }
 #ifndef DSV32_SFA_NO_PREFETCH
       if (a != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
 #endif
@@ -428,14 +438,15 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     auto issue_loads = [&](long long row, StPrefetch& pf) {
       pf.valid = row >= 0;
       if (pf.valid) {
-        const int4* src = reinterpret_cast<const int4*>(p.k_nope + row * kKvLora);
+        const int4* src = reinterpret_cast<const int4*>(nope_b + row * p.nope_stride);
         pf.nope[0] = __ldg(src + gpart + 8 * q_own);
         pf.nope[1] = __ldg(src + gpart + 8 * (q_own + 1));
         pf.nope[2] = __ldg(src + gpart + 8 * q_oth);
         pf.nope[3] = __ldg(src + gpart + 8 * (q_oth + 1));
-        pf.rope = __ldg(reinterpret_cast<const int4*>(p.k_rope + row * kRopeDim) + gpart);
-        const float2 so = __ldg(reinterpret_cast<const float2*>(p.k_scales + row * 4 + q_own));
-        const float2 sx = __ldg(reinterpret_cast<const float2*>(p.k_scales + row * 4 + q_oth));
+        pf.rope = __ldg(reinterpret_cast<const int4*>(rope_b + row * p.rope_stride) + gpart);
+        const float* sc_row = reinterpret_cast<const float*>(scale_b + row * p.scale_stride);
+        const float2 so = __ldg(reinterpret_cast<const float2*>(sc_row + q_own));
+        const float2 sx = __ldg(reinterpret_cast<const float2*>(sc_row + q_oth));
         pf.sc = make_float4(so.x, so.y, sx.x, sx.y);
       }
     };

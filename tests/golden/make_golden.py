@@ -16,6 +16,7 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
   indexer_small.npz  inputs + topk_res of lightning_indexer_compute (+ oracle scores)
   prolog_small.npz   seed + input digests + outputs of indexer_prolog
   mla_small.npz      seed + input digests + outputs of mla_prolog_quant_v32_compute
+  sa_antiquant_small.npz  inputs + output of compute_attention_aq (fused 656-byte cache rows)
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -112,6 +113,21 @@ def make_sfa():
         k_scales=kn_scales.numpy(), topk_indices=topk_indices.numpy(), block_table=block_table.numpy(),
         out=bits16(atten_out))
     print("sfa_small: out", tuple(atten_out.shape))
+
+
+def make_sa_antiquant():
+    import deepseekv32_sparse_attention_antiquant as ref  # noqa: reference module
+    torch.manual_seed(21)
+    b, nq, nkv, s1 = 3, 128, 1, 2
+    act_seq = [2300, 900, 40]
+    input_params, data, atten_out = ref.gen_gather_select_attention_golden_aq(torch.bfloat16, (b, nq, nkv, s1), 1, act_seq)
+    q_nope, q_rope, nope_cache_2d, topk_indices, block_table, _ = data
+    np.savez_compressed(
+        os.path.join(HERE, "sa_antiquant_small.npz"),
+        b=b, s1=s1, nq=nq, softmax_scale=np.float64(input_params[-1]), act_seq=np.array(act_seq, dtype=np.int32),
+        q_nope=bits16(q_nope), q_rope=bits16(q_rope), nope_cache=nope_cache_2d.numpy(),
+        topk_indices=topk_indices.numpy(), block_table=block_table.numpy(), out=bits16(atten_out))
+    print("sa_antiquant_small: out", tuple(atten_out.shape))
 
 
 def make_indexer():
@@ -217,6 +233,7 @@ if __name__ == "__main__":
     install_reference_stubs()
     make_kat()
     make_sfa()
+    make_sa_antiquant()
     make_indexer()
     make_prolog()
     make_mla()

@@ -239,6 +239,56 @@ def test_sfa_reference_golden_fixture():
     _assert_attention_close(out, _sfa_oracle(g))
 
 
+def _run_sa_antiquant(d, cache, entry="d", flat_out=False):
+    import pypto_b200
+    from pypto_b200 import sparse_attention_antiquant_impl as sa
+    c = _cuda(d)
+    shape = (d["b"] * d["s1"] * d["nq"], 512) if flat_out else (d["b"], d["s1"], d["nq"], 512)
+    out = torch.full(shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+    fn = {"d": sa.sparse_attention_antiquant_d, "p": sa.sparse_attention_antiquant_p,
+          "d950": sa.sparse_attention_antiquant_d_950}[entry]
+    fn(c["q_nope"], c["q_rope"], cache.to(DEV), c["topk_indices"], c["block_table"], c["act_seq"], out, d["nq"], 1,
+       d["softmax_scale"], d.get("topk", 2048), 128, d["block_table"].shape[1], sa.SaTileShapeConfig())
+    pypto_b200.check_status()
+    return out.cpu().reshape(d["b"], d["s1"], d["nq"], 512)
+
+
+def test_sa_antiquant_reference_golden_fixture():
+    g = helpers.load_sa_antiquant_golden()
+    out = _run_sa_antiquant(g, g["nope_cache"], flat_out=True)  # the reference test passes a [t*nq, 512] output
+    _assert_attention_close(out, g["out"])
+    _assert_attention_close(out, orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"],
+                                                  g["block_table"], g["act_seq"], g["nq"], g["softmax_scale"]))
+
+
+@pytest.mark.parametrize("entry,act_seq,s1", [("d", [2600, 700, 15, 0], 2), ("p", [5000, 2049], 4), ("d950", [64, 2048], 1)])
+def test_sa_antiquant_fused_rows_equal_split_arrays(entry, act_seq, s1):
+    """The fused 656-byte row holds the same bytes as the three arrays: the two operators return the same bits."""
+    from pypto_b200.sparse_attention_antiquant_impl import pack_cache_rows
+    d = helpers.gen_sfa_inputs(300 + s1, act_seq, s1=s1, extra_blocks=1)
+    cache = pack_cache_rows(d["k_nope"], d["k_rope"], d["k_scales"])
+    kn, kr, sc = orc.unpack_cache_rows(cache)
+    assert torch.equal(kn, d["k_nope"]) and torch.equal(kr, d["k_rope"]) and torch.equal(sc, d["k_scales"])
+    fused = _run_sa_antiquant(d, cache, entry=entry)
+    assert torch.equal(fused, _run_sfa(d))
+    _assert_attention_close(fused, _sfa_oracle(d))
+
+
+def test_sa_antiquant_rejects_bad_arguments():
+    from pypto_b200 import sparse_attention_antiquant_impl as sa
+    d = helpers.gen_sfa_inputs(9, [300], s1=1)
+    c = _cuda(d)
+    out = torch.empty((1, 1, 128, 512), dtype=torch.bfloat16, device=DEV)
+    cache = sa.pack_cache_rows(c["k_nope"], c["k_rope"], c["k_scales"])
+    with pytest.raises(ValueError):  # wrong row width
+        sa.sparse_attention_antiquant_d(c["q_nope"], c["q_rope"], cache[:, :640].contiguous(), c["topk_indices"],
+                                        c["block_table"], c["act_seq"], out, 128, 1, 0.04, 2048, 128,
+                                        d["block_table"].shape[1], None)
+    with pytest.raises(ValueError):  # more than one KV head
+        sa.sparse_attention_antiquant_d(c["q_nope"], c["q_rope"], cache, c["topk_indices"], c["block_table"],
+                                        c["act_seq"], out, 128, 2, 0.04, 2048, 128, d["block_table"].shape[1], None)
+
+
 @pytest.mark.parametrize("entry", ["d", "p", "d950"])
 def test_sfa_config0_seeded_vs_oracle(entry):
     g = torch.Generator().manual_seed(1000)

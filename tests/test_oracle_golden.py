@@ -28,6 +28,19 @@ def test_sfa_oracle_matches_reference_golden():
     assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
 
 
+def test_sa_antiquant_oracle_matches_reference_golden():
+    g = helpers.load_sa_antiquant_golden()
+    out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
+                           g["nq"], g["softmax_scale"])
+    assert out.shape == g["out"].shape
+    assert torch.allclose(out.float(), g["out"].float(), rtol=1e-2, atol=1e-3)
+    assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
+    # the fused row is the three arrays side by side
+    kn, kr, sc = orc.unpack_cache_rows(g["nope_cache"])
+    assert kn.shape[1] == 512 and kr.dtype == torch.bfloat16 and sc.dtype == torch.float32
+    assert float(sc.min()) > 0 and float(kr.float().abs().max()) <= 1.0
+
+
 def test_indexer_oracle_matches_reference_golden():
     g = helpers.load_indexer_golden()
     res, scores = orc.lightning_indexer(g["query"], g["q_scale"], g["key"], g["k_scale"], g["weights"], g["act_seq"],
