@@ -12,6 +12,8 @@
 //   D[token, 192] = x[token, slice] (bf16) x [wk | w_proj][slice, 192] (bf16, MN-major) -> fp32 partial sums;
 //   the per-token finish kernel (prolog.cu) reduces them in a fixed order and completes the K and W paths.
 // Weights stream through a 4-stage TMA ring exactly once per CTA; no multicast.
+#include <mutex>
+
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
@@ -357,6 +359,36 @@ int launch_prolog_finish(const PrologParams& p, int splits, cudaStream_t stream)
 
 int prolog_tc_splits() { return 16; }  // 7 reduction chunks of 64 per CTA
 
+// The Q path and the K/W path of the prolog are independent (64 and 16 CTAs per 128 tokens, both latency-
+// bound), so the Q kernel runs on a side stream of the library, forked from and joined back into the caller's
+// stream with events; the pattern is legal under stream capture.  One side stream and event pair per device,
+// created on the first call for that device (make that call outside a capture: creating a stream is not a
+// capturable operation).
+struct PrologFork {
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static PrologFork* prolog_fork_for_device() {
+  static PrologFork forks[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  PrologFork& f = forks[dev];
+  if (f.side == nullptr) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming) != cudaSuccess) {
+      (void)st;
+      (void)cudaGetLastError();
+      f = PrologFork{};
+      return nullptr;  // fall back to one stream
+    }
+  }
+  return &f;
+}
+
 int launch_prolog_tc(const PrologParams& p, cudaStream_t stream) {
   if (p.t <= 0) return DSV32_OK;
   const int tiles = (p.t + 127) / 128;
@@ -368,19 +400,34 @@ int launch_prolog_tc(const PrologParams& p, cudaStream_t stream) {
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wk_map, p.wk, 7168, 256, 64, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wp_map, p.w_proj, 7168, 128, 64, 128);
   if (rc != DSV32_OK) return rc;
+  PrologFork* fk = prolog_fork_for_device();
+  cudaStream_t q_stream = stream;
+  if (fk != nullptr) {
+    if (cudaEventRecord(fk->fork, stream) == cudaSuccess && cudaStreamWaitEvent(fk->side, fk->fork, 0) == cudaSuccess) {
+      q_stream = fk->side;
+    } else {
+      (void)cudaGetLastError();
+      fk = nullptr;
+    }
+  }
   cudaFuncSetAttribute(prolog_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPqSmemBytes);
-  prolog_q_tc_kernel<<<dim3(64, tiles), kPqThreads, kPqSmemBytes, stream>>>(qn_map, w_map, h_map, p);
+  prolog_q_tc_kernel<<<dim3(64, tiles), kPqThreads, kPqSmemBytes, q_stream>>>(qn_map, w_map, h_map, p);
   count_launch();
   rc = check_launch("prolog_q_tc_kernel");
-  if (rc != DSV32_OK) return rc;
-  const int splits = prolog_tc_splits();
-  const int per = (kKwChunksTotal + splits - 1) / splits;
-  cudaFuncSetAttribute(prolog_kw_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKwSmemBytes);
-  prolog_kw_tc_kernel<<<dim3(splits, tiles), kPqThreads, kKwSmemBytes, stream>>>(x_map, wk_map, wp_map, p, per);
-  count_launch();
-  rc = check_launch("prolog_kw_tc_kernel");
-  if (rc != DSV32_OK) return rc;
-  return launch_prolog_finish(p, splits, stream);
+  if (fk != nullptr && cudaEventRecord(fk->join, fk->side) != cudaSuccess) rc = check_launch("prolog side stream");
+  if (rc == DSV32_OK) {
+    const int splits = prolog_tc_splits();
+    const int per = (kKwChunksTotal + splits - 1) / splits;
+    cudaFuncSetAttribute(prolog_kw_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKwSmemBytes);
+    prolog_kw_tc_kernel<<<dim3(splits, tiles), kPqThreads, kKwSmemBytes, stream>>>(x_map, wk_map, wp_map, p, per);
+    count_launch();
+    rc = check_launch("prolog_kw_tc_kernel");
+    if (rc == DSV32_OK) rc = launch_prolog_finish(p, splits, stream);
+  }
+  // always join, also after an error above: the caller's stream must not run ahead of the side stream
+  if (fk != nullptr && cudaStreamWaitEvent(stream, fk->join, 0) != cudaSuccess && rc == DSV32_OK)
+    rc = check_launch("prolog side stream join");
+  return rc;
 }
 
 }  // namespace dsv32
