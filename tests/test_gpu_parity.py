@@ -304,6 +304,14 @@ def test_sfa_ragged_edges_vs_oracle(act_seq, s1):
     _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
 
 
+@pytest.mark.parametrize("nq,topk,act_seq", [(64, 2048, [2600, 90]), (128, 512, [3000, 300]), (128, 1024, [1024, 5000]),
+                                             (64, 1024, [700])])
+def test_sfa_other_head_counts_and_selection_sizes(nq, topk, act_seq):
+    """64 heads run on the warp-level MMA kernel; a smaller top-k shortens every index row."""
+    d = helpers.gen_sfa_inputs(40 + nq + topk, act_seq, s1=2, nq=nq, topk=topk)
+    _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
+
+
 def test_sfa_negative_index_inside_prefix_is_skipped():
     d = helpers.gen_sfa_inputs(5, [3000], s1=1)
     d["topk_indices"][0, 10:200] = -1
