@@ -65,6 +65,10 @@ typedef struct {
 
 size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t topk, int32_t kv_splits);
 int dsv32_sfa_quant(const Dsv32SfaArgs* args, void* cuda_stream);
+/* The branch of the same operator for a latent cache that is not quantised
+ * (sparse_flash_attention_quant_impl.py:216-259): key_nope is bf16 [rows, 512], k_nope_scales is
+ * ignored and may be NULL.  n_q must be 128. */
+int dsv32_sfa_bf16_cache(const Dsv32SfaArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
  * The same attention over the fused cache layout ("store 8, compute 16"): one 656-byte row per

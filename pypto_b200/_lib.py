@@ -80,6 +80,7 @@ EXPORTS = {
     "dsv32_launch_count": (C.c_uint64, []),
     "dsv32_sfa_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32, c_i32]),
     "dsv32_sfa_quant": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
+    "dsv32_sfa_bf16_cache": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
     "dsv32_sparse_attention_antiquant": (c_i32, [C.POINTER(SaAntiquantArgs), c_void_p]),
     "dsv32_indexer_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
     "dsv32_indexer_topk": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),

@@ -78,7 +78,8 @@ size_t dsv32_sfa_workspace_bytes(int32_t b, int32_t s1, int32_t n_q, int32_t top
   return bytes;
 }
 
-static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, int rope_stride, int scale_stride) {
+static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, int rope_stride, int scale_stride,
+                   bool bf16_cache = false) {
   REQUIRE(a != nullptr, "sfa: args is NULL");
   REQUIRE(a->b >= 0 && a->s1 >= 1, "sfa: bad b=%d s1=%d", a->b, a->s1);
   if (a->b == 0) return DSV32_OK;
@@ -87,8 +88,8 @@ static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, in
   REQUIRE(a->block_size >= 1 && a->max_blocks >= 1, "sfa: bad block_size=%d max_blocks=%d", a->block_size,
           a->max_blocks);
   REQUIRE(a->rows >= 0, "sfa: rows=%lld must be >= 0", static_cast<long long>(a->rows));
-  REQUIRE(a->query_nope && a->query_rope && a->key_nope && a->key_rope && a->k_nope_scales && a->topk_indices &&
-              a->block_table && a->kv_act_seqs && a->attention_out,
+  REQUIRE(a->query_nope && a->query_rope && a->key_nope && a->key_rope && (a->k_nope_scales || bf16_cache) &&
+              a->topk_indices && a->block_table && a->kv_act_seqs && a->attention_out,
           "sfa: NULL tensor pointer");
   REQUIRE(reinterpret_cast<uintptr_t>(a->key_nope) % 16 == 0 && reinterpret_cast<uintptr_t>(a->key_rope) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(a->k_nope_scales) % 16 == 0 &&
@@ -116,6 +117,7 @@ static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, in
     if ((1 << sh) == a->block_size) p.bs_shift = sh;
   p.max_blocks = a->max_blocks; p.splits = splits; p.scale = a->softmax_scale;
   p.nope_stride = nope_stride; p.rope_stride = rope_stride; p.scale_stride = scale_stride;
+  p.kn_bf16 = bf16_cache ? 1 : 0;
   {
     const size_t need = dsv32_sfa_workspace_bytes(a->b, a->s1, a->n_q, a->topk, splits);
     if (a->workspace == nullptr || a->workspace_bytes < need ||
@@ -137,11 +139,19 @@ static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, in
     const char* e = getenv("DSV32_SFA_IMPL");
     return e != nullptr && e[0] == 'm';
   }();
+  if (bf16_cache && (use_mma || a->n_q != 128)) {
+    set_error("sfa: the bf16 latent cache is only supported by the tcgen05 kernel (n_q == 128, got %d)", a->n_q);
+    return DSV32_ERR_UNSUPPORTED;
+  }
   if (use_mma || a->n_q != 128) return launch_sfa_mma(p, static_cast<cudaStream_t>(cuda_stream));
   return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int dsv32_sfa_quant(const Dsv32SfaArgs* a, void* cuda_stream) { return sfa_run(a, cuda_stream, kKvLora, kRopeDim * 2, 16); }
+
+int dsv32_sfa_bf16_cache(const Dsv32SfaArgs* a, void* cuda_stream) {
+  return sfa_run(a, cuda_stream, kKvLora * 2, kRopeDim * 2, 0, true);
+}
 
 int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* a, void* cuda_stream) {
   REQUIRE(a != nullptr, "sa_antiquant: args is NULL");

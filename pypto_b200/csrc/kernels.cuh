@@ -54,6 +54,7 @@ struct SfaParams {
   // byte distance between consecutive cache rows in each of the three arrays: 512 / 128 / 16 for separate
   // arrays, 656 / 656 / 656 when the three parts of a row sit side by side in one array
   int nope_stride, rope_stride, scale_stride;
+  int kn_bf16;  // 1: the latent cache is bf16 [rows, 512] and there are no scales (tcgen05 kernel only)
   float scale;
 };
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);

@@ -59,8 +59,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-struct StPrefetch {
-  int4 nope[4];
+// Raw cache data of one row as held by one producer thread.  kBf16: the latent cache is already bf16 (no scales;
+// twice the bytes), otherwise int8 with one fp32 scale per 128-dim group.
+template <bool kBf16>
+struct StPrefetchT {
+  int4 nope[kBf16 ? 8 : 4];
   int4 rope;
   float4 sc;
   bool valid;
@@ -111,6 +114,7 @@ __global__ void __launch_bounds__(256) sfa_row_ids_kernel(SfaParams p) {
   p.row_ids[static_cast<size_t>(tok) * p.topk + j] = out;
 }
 
+template <bool kBf16>
 __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
                                                                const __grid_constant__ CUtensorMap qr_map,
                                                                SfaParams p) {
@@ -415,12 +419,15 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     const unsigned char* nope_b = reinterpret_cast<const unsigned char*>(p.k_nope);
     const unsigned char* rope_b = reinterpret_cast<const unsigned char*>(p.k_rope);
     const unsigned char* scale_b = reinterpret_cast<const unsigned char*>(p.k_scales);
-    const bool fused_rows = p.nope_stride != kKvLora;  // one 656-byte row holds all three parts
+    const bool fused_rows = p.nope_stride == p.rope_stride;  // one 656-byte row holds all three parts
     auto l2_prefetch = [&](long long row) {  // the 128-byte lines of a row, one per thread column
       if (row < 0) return;
       const void* a = nullptr;
       if (fused_rows) {
         if (gpart < 6) a = nope_b + row * p.nope_stride + gpart * 128;  // 656 bytes touch at most six lines
+      } else if constexpr (kBf16) {
+        a = nope_b + row * p.nope_stride + gpart * 128;                 // eight lines of bf16 latent dims
+        if (gpart == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(rope_b + row * p.rope_stride));
       } else if (gpart < 4) {
         a = nope_b + row * p.nope_stride + gpart * 128;
       } else if (gpart == 4) {
@@ -435,37 +442,63 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     // Register layout of a row: nope[0..1] / sc.x,.y = this CTA's own value dims (128-dim groups 2*half, 2*half+1),
     // nope[2..3] / sc.z,.w = the other half's.  The runtime half only enters the addresses.
     const int q_own = 2 * half, q_oth = 2 * (half ^ 1);
+    using StPrefetch = StPrefetchT<kBf16>;
     auto issue_loads = [&](long long row, StPrefetch& pf) {
       pf.valid = row >= 0;
       if (pf.valid) {
         const int4* src = reinterpret_cast<const int4*>(nope_b + row * p.nope_stride);
-        pf.nope[0] = __ldg(src + gpart + 8 * q_own);
-        pf.nope[1] = __ldg(src + gpart + 8 * (q_own + 1));
-        pf.nope[2] = __ldg(src + gpart + 8 * q_oth);
-        pf.nope[3] = __ldg(src + gpart + 8 * (q_oth + 1));
-        pf.rope = __ldg(reinterpret_cast<const int4*>(rope_b + row * p.rope_stride) + gpart);
-        const float* sc_row = reinterpret_cast<const float*>(scale_b + row * p.scale_stride);
-        const float2 so = __ldg(reinterpret_cast<const float2*>(sc_row + q_own));
-        const float2 sx = __ldg(reinterpret_cast<const float2*>(sc_row + q_oth));
-        pf.sc = make_float4(so.x, so.y, sx.x, sx.y);
+        if constexpr (kBf16) {  // this thread's 16 dims of a 128-dim group are two consecutive 16-byte units
+          pf.nope[0] = __ldg(src + 2 * gpart + 16 * q_own);
+          pf.nope[1] = __ldg(src + 2 * gpart + 16 * q_own + 1);
+          pf.nope[2] = __ldg(src + 2 * gpart + 16 * (q_own + 1));
+          pf.nope[3] = __ldg(src + 2 * gpart + 16 * (q_own + 1) + 1);
+          pf.nope[4] = __ldg(src + 2 * gpart + 16 * q_oth);
+          pf.nope[5] = __ldg(src + 2 * gpart + 16 * q_oth + 1);
+          pf.nope[6] = __ldg(src + 2 * gpart + 16 * (q_oth + 1));
+          pf.nope[7] = __ldg(src + 2 * gpart + 16 * (q_oth + 1) + 1);
+          pf.rope = __ldg(reinterpret_cast<const int4*>(rope_b + row * p.rope_stride) + gpart);
+        } else {
+          pf.nope[0] = __ldg(src + gpart + 8 * q_own);
+          pf.nope[1] = __ldg(src + gpart + 8 * (q_own + 1));
+          pf.nope[2] = __ldg(src + gpart + 8 * q_oth);
+          pf.nope[3] = __ldg(src + gpart + 8 * (q_oth + 1));
+          pf.rope = __ldg(reinterpret_cast<const int4*>(rope_b + row * p.rope_stride) + gpart);
+          const float* sc_row = reinterpret_cast<const float*>(scale_b + row * p.scale_stride);
+          const float2 so = __ldg(reinterpret_cast<const float2*>(sc_row + q_own));
+          const float2 sx = __ldg(reinterpret_cast<const float2*>(sc_row + q_oth));
+          pf.sc = make_float4(so.x, so.y, sx.x, sx.y);
+        }
       }
     };
-    // one dequantised 16-dim group (two 16-byte units) of key row r, 128-dim group q, into its swizzled place
-    auto store_group = [&](unsigned char* stage, int r, int q, bool valid, const int4& raw, float sc) {
-      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-      if (valid) st_dequant16(raw, sc, lo, hi);
+    // one 16-dim group (two 16-byte units of bf16) of key row r, 128-dim group q, into its swizzled place
+    auto store_units = [&](unsigned char* stage, int r, int q, const uint4& lo, const uint4& hi) {
       const int chunk = 2 * q + (gpart >> 2);  // 64-dim chunk 0..7
       const int u0 = (gpart & 3) * 2;          // first of two 16-byte units inside the 128-byte line
       unsigned char* line = stage + chunk * kStChunkBytes + r * 128;
       *reinterpret_cast<uint4*>(line + ((u0 ^ (r & 7)) << 4)) = lo;
       *reinterpret_cast<uint4*>(line + (((u0 + 1) ^ (r & 7)) << 4)) = hi;
     };
+    // group k of the row held in pf: k = 0, 1 -> this CTA's own value dims, 2, 3 -> the other half's
+    auto store_group = [&](unsigned char* stage, int r, int q, int k, const StPrefetch& pf) {
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      if constexpr (kBf16) {
+        if (pf.valid) {
+          const int4 a = pf.nope[2 * k], b = pf.nope[2 * k + 1];
+          lo = make_uint4(a.x, a.y, a.z, a.w);
+          hi = make_uint4(b.x, b.y, b.z, b.w);
+        }
+      } else {
+        const float sc = k == 0 ? pf.sc.x : k == 1 ? pf.sc.y : k == 2 ? pf.sc.z : pf.sc.w;
+        if (pf.valid) st_dequant16(pf.nope[k], sc, lo, hi);
+      }
+      store_units(stage, r, q, lo, hi);
+    };
     // The chunks that only S reads (the other half's value dims and the rope dims) ...
     auto commit_other = [&](int tile, int pass, const StPrefetch& pf) {
       unsigned char* stage = k_s + (tile & 1) * kStStageBytes;
       const int r = pass * 32 + gkey;  // row (key) inside the tile
-      store_group(stage, r, q_oth, pf.valid, pf.nope[2], pf.sc.z);
-      store_group(stage, r, q_oth + 1, pf.valid, pf.nope[3], pf.sc.w);
+      store_group(stage, r, q_oth, 2, pf);
+      store_group(stage, r, q_oth + 1, 3, pf);
       unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
       const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
       *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
@@ -475,8 +508,8 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       const int s = tile & 1;
       unsigned char* stage = k_s + s * kStStageBytes;
       const int r = pass * 32 + gkey;
-      store_group(stage, r, q_own, pf.valid, pf.nope[0], pf.sc.x);
-      store_group(stage, r, q_own + 1, pf.valid, pf.nope[1], pf.sc.y);
+      store_group(stage, r, q_own, 0, pf);
+      store_group(stage, r, q_own + 1, 1, pf);
       if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
     };
 
@@ -541,7 +574,8 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
   if (rc != DSV32_OK) return rc;
   rc = make_tensor_map_2d_u8(&qr_map, p.q_rope, static_cast<uint64_t>(t) * p.nq, kRopeDim * 2, 128, 128);
   if (rc != DSV32_OK) return rc;
-  cudaFuncSetAttribute(sfa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  cudaFuncSetAttribute(sfa_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  cudaFuncSetAttribute(sfa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
   if (p.rows > 0x7ffffffeLL) {
     set_error("sfa: the tcgen05 kernel addresses at most 2^31-2 cache rows (got %lld)", static_cast<long long>(p.rows));
     return DSV32_ERR_UNSUPPORTED;
@@ -551,7 +585,8 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
   rc = check_launch("sfa_row_ids_kernel");
   if (rc != DSV32_OK) return rc;
   dim3 grid(2, t, p.splits);
-  sfa_tc_kernel<<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
+  if (p.kn_bf16) sfa_tc_kernel<true><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
+  else sfa_tc_kernel<false><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
   count_launch();
   rc = check_launch("sfa_tc_kernel");
   if (rc == DSV32_OK && p.splits > 1) rc = launch_sfa_combine(p, stream);

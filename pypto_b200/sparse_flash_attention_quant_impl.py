@@ -37,12 +37,15 @@ def _sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_i
     bf16 = torch.bfloat16
     rt.check_tensor(query_nope, "query_nope", bf16, (None, 512))
     rt.check_tensor(query_rope, "query_rope", bf16, (query_nope.shape[0], 64))
-    if key_nope_2d.dtype != torch.int8:
-        raise ValueError(f"key_nope_2d: expected the int8 quantized cache, got {key_nope_2d.dtype}")
-    rt.check_tensor(key_nope_2d, "key_nope_2d", torch.int8, (None, 512))
+    # int8 cache with per-group scales, or the bf16 cache of the reference's non-quantised branch (:216-259)
+    quant = key_nope_2d.dtype == torch.int8
+    if not quant and key_nope_2d.dtype != bf16:
+        raise ValueError(f"key_nope_2d: expected the int8 quantized cache or a bf16 cache, got {key_nope_2d.dtype}")
+    rt.check_tensor(key_nope_2d, "key_nope_2d", torch.int8 if quant else bf16, (None, 512))
     rows = key_nope_2d.shape[0]
     rt.check_tensor(key_rope_2d, "key_rope_2d", bf16, (rows, 64))
-    rt.check_tensor(k_nope_scales, "k_nope_scales", torch.float32, (rows, 4))
+    if quant:
+        rt.check_tensor(k_nope_scales, "k_nope_scales", torch.float32, (rows, 4))
     rt.check_tensor(topk_indices, "topk_indices", torch.int32, (None, int(n_kv) * int(topk)))
     rt.check_tensor(block_table, "block_table", torch.int32, (None, int(max_blocknum_perbatch)))
     b = block_table.shape[0]
@@ -56,18 +59,20 @@ def _sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_i
     if query_nope.shape[0] != t * int(nq):
         raise ValueError(f"query_nope rows {query_nope.shape[0]} != t*nq = {t * int(nq)}")
     rt.check_tensor(attention_out, "attention_out", bf16, (b, s1, int(nq), 512))
-    dev = rt.same_device(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices, block_table,
-                         kv_act_seqs, attention_out)
+    dev = rt.same_device(query_nope, query_rope, key_nope_2d, key_rope_2d, topk_indices, block_table, kv_act_seqs,
+                         attention_out, *([k_nope_scales] if quant else []))
     lib = _lib.load()
     with torch.cuda.device(dev):
         ws_bytes = lib.dsv32_sfa_workspace_bytes(b, s1, int(nq), int(topk), int(kv_splits))
         ws = rt.workspace(ws_bytes, dev)
         a = _lib.SfaArgs(
-            rt.ptr(query_nope), rt.ptr(query_rope), rt.ptr(key_nope_2d), rt.ptr(key_rope_2d), rt.ptr(k_nope_scales),
+            rt.ptr(query_nope), rt.ptr(query_rope), rt.ptr(key_nope_2d), rt.ptr(key_rope_2d),
+            rt.ptr(k_nope_scales) if quant else None,
             rt.ptr(topk_indices), rt.ptr(block_table), rt.ptr(kv_act_seqs), rt.ptr(attention_out), rt.ptr(ws),
             int(ws_bytes), rt.ptr(rt.status_word(dev)), rows, b, s1, int(nq), int(topk), int(block_size),
             int(max_blocknum_perbatch), int(kv_splits), float(softmax_scale))
-        rt.check(lib.dsv32_sfa_quant(C.byref(a), rt.stream_ptr(dev)), "sparse_flash_attention_quant")
+        fn = lib.dsv32_sfa_quant if quant else lib.dsv32_sfa_bf16_cache
+        rt.check(fn(C.byref(a), rt.stream_ptr(dev)), "sparse_flash_attention_quant")
     return None
 
 

@@ -16,6 +16,7 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
   indexer_small.npz  inputs + topk_res of lightning_indexer_compute (+ oracle scores)
   prolog_small.npz   seed + input digests + outputs of indexer_prolog
   mla_small.npz      seed + input digests + outputs of mla_prolog_quant_v32_compute
+  sfa_bf16_small.npz inputs + output of compute_attention_no_flash with a bf16 (not quantised) cache
   sa_antiquant_small.npz  inputs + output of compute_attention_aq (fused 656-byte cache rows)
   kat.json           the two interpreter known-answer tests, restated as data
 
@@ -113,6 +114,22 @@ def make_sfa():
         k_scales=kn_scales.numpy(), topk_indices=topk_indices.numpy(), block_table=block_table.numpy(),
         out=bits16(atten_out))
     print("sfa_small: out", tuple(atten_out.shape))
+
+
+def make_sfa_bf16():
+    import deepseekv32_sparse_flash_attention_quant as ref  # noqa: reference module
+    torch.manual_seed(31)
+    b, nq, nkv, s1 = 2, 128, 1, 2
+    act_seq = [2200, 130]
+    input_params, data, atten_out = ref.gen_gather_select_attention_golden(torch.bfloat16, (b, nq, nkv, s1), 0, act_seq)
+    q_nope, q_rope, kn, kr, _, topk_indices, block_table, _ = data
+    assert kn.dtype == torch.bfloat16
+    np.savez_compressed(
+        os.path.join(HERE, "sfa_bf16_small.npz"),
+        b=b, s1=s1, nq=nq, softmax_scale=np.float64(input_params[-1]), act_seq=np.array(act_seq, dtype=np.int32),
+        q_nope=bits16(q_nope), q_rope=bits16(q_rope), k_nope=bits16(kn), k_rope=bits16(kr),
+        topk_indices=topk_indices.numpy(), block_table=block_table.numpy(), out=bits16(atten_out))
+    print("sfa_bf16_small: out", tuple(atten_out.shape))
 
 
 def make_sa_antiquant():
@@ -233,6 +250,7 @@ if __name__ == "__main__":
     install_reference_stubs()
     make_kat()
     make_sfa()
+    make_sfa_bf16()
     make_sa_antiquant()
     make_indexer()
     make_prolog()

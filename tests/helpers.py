@@ -38,6 +38,17 @@ def load_sfa_golden():
         block_table=torch.from_numpy(z["block_table"]), out=from_bits16(z["out"], bf))
 
 
+def load_sfa_bf16_golden():
+    z = np.load(os.path.join(GOLDEN, "sfa_bf16_small.npz"))
+    bf = torch.bfloat16
+    return dict(
+        b=int(z["b"]), s1=int(z["s1"]), nq=int(z["nq"]), softmax_scale=float(z["softmax_scale"]),
+        act_seq=torch.from_numpy(z["act_seq"]), q_nope=from_bits16(z["q_nope"], bf), q_rope=from_bits16(z["q_rope"], bf),
+        k_nope=from_bits16(z["k_nope"], bf), k_rope=from_bits16(z["k_rope"], bf), k_scales=None,
+        topk_indices=torch.from_numpy(z["topk_indices"]), block_table=torch.from_numpy(z["block_table"]),
+        out=from_bits16(z["out"], bf))
+
+
 def load_sa_antiquant_golden():
     z = np.load(os.path.join(GOLDEN, "sa_antiquant_small.npz"))
     bf = torch.bfloat16

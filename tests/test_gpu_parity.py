@@ -239,6 +239,19 @@ def test_sfa_reference_golden_fixture():
     _assert_attention_close(out, _sfa_oracle(g))
 
 
+def test_sfa_bf16_cache_reference_golden_fixture_and_seeded():
+    """The operator's branch for a cache that is not quantised (bf16 latent rows, no scales)."""
+    g = helpers.load_sfa_bf16_golden()
+    out = _run_sfa(g)
+    _assert_attention_close(out, g["out"])
+    _assert_attention_close(out, _sfa_oracle(g))
+    d = helpers.gen_sfa_inputs(61, [3000, 64, 2049], s1=2, extra_blocks=1)
+    d["k_nope"] = (d["k_nope"].float() * 0.01).to(torch.bfloat16)
+    d["k_scales"] = None
+    _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
+    _assert_attention_close(_run_sfa(d, kv_splits=3), _sfa_oracle(d))
+
+
 def _run_sa_antiquant(d, cache, entry="d", flat_out=False):
     import pypto_b200
     from pypto_b200 import sparse_attention_antiquant_impl as sa

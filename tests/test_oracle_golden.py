@@ -28,6 +28,14 @@ def test_sfa_oracle_matches_reference_golden():
     assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
 
 
+def test_sfa_oracle_matches_reference_golden_bf16_cache():
+    g = helpers.load_sfa_bf16_golden()
+    out = orc.sfa_quant(g["q_nope"], g["q_rope"], g["k_nope"], g["k_rope"], None, g["topk_indices"], g["block_table"],
+                        g["act_seq"], g["nq"], g["softmax_scale"])
+    assert torch.allclose(out.float(), g["out"].float(), rtol=1e-2, atol=1e-3)
+    assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
