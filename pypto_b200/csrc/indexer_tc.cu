@@ -21,7 +21,7 @@
 namespace dsv32 {
 
 constexpr int kTcStages = 4;
-constexpr int kTcBlocksPerCta = 32;
+constexpr int kTcBlocksPerCta = 64;  // upper bound; the launcher picks the actual count per call
 constexpr int kKeyTileBytes = 128 * 128;
 
 struct TcSmemLayout {
@@ -30,11 +30,12 @@ struct TcSmemLayout {
   static constexpr int q = kTcStages * kKeyTileBytes;          // up to 256 rows x 128 B
   static constexpr int ws = q + 256 * 128;                     // 256 floats
   static constexpr int phys = ws + 256 * 4;                    // 32 ints
-  static constexpr int bars = phys + kTcBlocksPerCta * 4;      // 8-byte aligned
+  static constexpr int bars = phys + ((kTcBlocksPerCta * 4 + 7) / 8) * 8;  // 8-byte aligned
   static constexpr int nbars = 2 * kTcStages + 4 + 1;
   static constexpr int tmem_ptr = bars + nbars * 8;
   static constexpr int total = tmem_ptr + 16;
 };
+static_assert(TcSmemLayout::bars % 8 == 0, "mbarriers are 8-byte aligned");
 constexpr size_t kTcSmemBytes = TcSmemLayout::total + 1024;  // slack for manual 1024-byte alignment
 
 template <int TOK>
@@ -73,23 +74,25 @@ __global__ void __launch_bounds__(TcShape<TOK>::kThreads, 2) indexer_scores_tc_k
   const int L = p.act_seq[b];
   const int hi = min(L, p.key_end);
   const int bs = 128;
-  const int blk_begin = p.key_begin / bs + blockIdx.x * kTcBlocksPerCta;
-  const int blk_end = min(blk_begin + kTcBlocksPerCta, (hi + bs - 1) / bs);
+  const int blk_begin = p.key_begin / bs + blockIdx.x * p.blocks_per_cta;
+  const int blk_end = min(blk_begin + p.blocks_per_cta, (hi + bs - 1) / bs);
   if (blk_begin >= blk_end || hi <= p.key_begin) return;  // uniform for the CTA
   const int nblk = blk_end - blk_begin;
   const size_t row0 = static_cast<size_t>(b) * p.s1 + tok0;
 
   // ---- setup ----------------------------------------------------------------------------------------
   if (warp == 0) {
-    int phys = 0;
-    if (lane < nblk) {
-      phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + blk_begin + lane];
-      if (phys < 0 || phys >= p.num_blocks) {
-        report_status(p.status, DSV32_STATUS_BAD_PAGE, b, blk_begin + lane);
-        phys = 0;
+    for (int j = lane; j < kTcBlocksPerCta; j += 32) {
+      int phys = 0;
+      if (j < nblk) {
+        phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + blk_begin + j];
+        if (phys < 0 || phys >= p.num_blocks) {
+          report_status(p.status, DSV32_STATUS_BAD_PAGE, b, blk_begin + j);
+          phys = 0;
+        }
       }
+      phys_s[j] = phys;
     }
-    phys_s[lane] = phys;
     if (lane == 0) {
       tma_prefetch_desc(&key_map);
       tma_prefetch_desc(&q_map);
@@ -289,11 +292,32 @@ int launch_indexer_scores_tc(const IndexerParams& p, cudaStream_t stream) {
   CUtensorMap key_map;
   int rc = make_tensor_map_2d_u8(&key_map, p.keys, static_cast<uint64_t>(p.num_blocks) * 128, 128, 128, 128);
   if (rc != DSV32_OK) return rc;
-  dim3 grid((nblk + kTcBlocksPerCta - 1) / kTcBlocksPerCta, p.b, 1);
-  if (p.s1 == 1) return launch_tc<1>(p, key_map, grid, stream);
-  if (p.s1 == 2) return launch_tc<2>(p, key_map, grid, stream);
+  // Key blocks per CTA.  The CTAs run in rounds of (resident CTAs per SM) x (SMs), and a CTA spends about two
+  // block times filling its pipeline; pick the count that minimises rounds x (count + 2), so that the last
+  // round is not mostly empty (measured: 57 instead of 32 blocks per CTA at 64 requests x 512 blocks, -5 %).
+  // Context lengths live on the device, so the longest request stands for all of them.
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tok_groups = p.s1 <= 2 ? 1 : (p.s1 + 3) / 4;
+  const long long slots = static_cast<long long>(sms) * (p.s1 <= 2 ? 2 : 1);  // tensor memory: 512 columns per SM
+  int best_chunk = 32;
+  long long best_cost = -1;
+  for (int chunk = 8; chunk <= kTcBlocksPerCta; ++chunk) {
+    const long long ctas = static_cast<long long>((nblk + chunk - 1) / chunk) * p.b * tok_groups;
+    const long long rounds = (ctas + slots - 1) / slots;
+    const long long cost = rounds * (chunk + 2);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best_chunk = chunk;
+    }
+  }
+  IndexerParams q = p;
+  q.blocks_per_cta = best_chunk;
+  dim3 grid((nblk + best_chunk - 1) / best_chunk, p.b, 1);
+  if (p.s1 == 1) return launch_tc<1>(q, key_map, grid, stream);
+  if (p.s1 == 2) return launch_tc<2>(q, key_map, grid, stream);
   grid.z = (p.s1 + 3) / 4;
-  return launch_tc<4>(p, key_map, grid, stream);
+  return launch_tc<4>(q, key_map, grid, stream);
 }
 
 }  // namespace dsv32

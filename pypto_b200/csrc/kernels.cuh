@@ -30,6 +30,7 @@ struct IndexerParams {
   long long num_blocks;
   int b, s1, block_size, max_blocks, ld;
   int key_begin, key_end;
+  int blocks_per_cta;  // key blocks one CTA of the tcgen05 kernel walks (chosen by its launcher)
 };
 int launch_indexer_scores_mma(const IndexerParams& p, cudaStream_t stream);
 int launch_indexer_scores_tc(const IndexerParams& p, cudaStream_t stream);
