@@ -20,23 +20,25 @@
 
 namespace dsv32 {
 
-constexpr int kTcStages = 4;
 constexpr int kTcBlocksPerCta = 64;  // upper bound; the launcher picks the actual count per call
 constexpr int kKeyTileBytes = 128 * 128;
 
+// Shared memory of one CTA (offsets from the 1024-byte aligned base).  The ring of key blocks is what keeps
+// bytes in flight: with up to two tokens the query tile is 16 KB and five stages fit twice per SM.
+template <int TOK>
 struct TcSmemLayout {
-  // offsets from the 1024-byte aligned base
-  static constexpr int keys = 0;                               // kTcStages x 16 KB
-  static constexpr int q = kTcStages * kKeyTileBytes;          // up to 256 rows x 128 B
-  static constexpr int ws = q + 256 * 128;                     // 256 floats
-  static constexpr int phys = ws + 256 * 4;                    // 32 ints
+  static constexpr int stages = TOK <= 2 ? 5 : 4;
+  static constexpr int keys = 0;                               // stages x 16 KB
+  static constexpr int q = stages * kKeyTileBytes;             // 64 * TOK rows x 128 B
+  static constexpr int ws = q + 64 * TOK * 128;                // 64 * TOK fp16 weights (1 KB reserved)
+  static constexpr int phys = ws + 256 * 4;                    // kTcBlocksPerCta ints
   static constexpr int bars = phys + ((kTcBlocksPerCta * 4 + 7) / 8) * 8;  // 8-byte aligned
-  static constexpr int nbars = 2 * kTcStages + 4 + 1;
+  static constexpr int nbars = 2 * stages + 4 + 1;
   static constexpr int tmem_ptr = bars + nbars * 8;
   static constexpr int total = tmem_ptr + 16;
+  static constexpr size_t bytes = total + 1024;                // slack for manual 1024-byte alignment
+  static_assert(bars % 8 == 0 && q % 1024 == 0, "shared-memory layout alignment");
 };
-static_assert(TcSmemLayout::bars % 8 == 0, "mbarriers are 8-byte aligned");
-constexpr size_t kTcSmemBytes = TcSmemLayout::total + 1024;  // slack for manual 1024-byte alignment
 
 template <int TOK>
 struct TcShape {
@@ -55,17 +57,19 @@ __global__ void __launch_bounds__(TcShape<TOK>::kThreads, 2) indexer_scores_tc_k
   constexpr uint32_t kTmemCols = 2 * N < 32 ? 32 : 2 * N;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* k_s = smem + TcSmemLayout::keys;
-  unsigned char* q_s = smem + TcSmemLayout::q;
-  uint32_t* ws_s = reinterpret_cast<uint32_t*>(smem + TcSmemLayout::ws);  // fp16 pairs
-  int* phys_s = reinterpret_cast<int*>(smem + TcSmemLayout::phys);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmemLayout::bars);
+  using Lay = TcSmemLayout<TOK>;
+  constexpr int kTcStages = Lay::stages;
+  unsigned char* k_s = smem + Lay::keys;
+  unsigned char* q_s = smem + Lay::q;
+  uint32_t* ws_s = reinterpret_cast<uint32_t*>(smem + Lay::ws);  // fp16 pairs
+  int* phys_s = reinterpret_cast<int*>(smem + Lay::phys);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Lay::bars);
   uint64_t* full_bar = bars;                       // [kTcStages]
   uint64_t* empty_bar = bars + kTcStages;          // [kTcStages]
   uint64_t* tfull_bar = bars + 2 * kTcStages;      // [2]
   uint64_t* tempty_bar = bars + 2 * kTcStages + 2; // [2]
   uint64_t* q_bar = bars + 2 * kTcStages + 4;
-  uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + TcSmemLayout::tmem_ptr);
+  uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + Lay::tmem_ptr);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.y;
@@ -123,13 +127,16 @@ __global__ void __launch_bounds__(TcShape<TOK>::kThreads, 2) indexer_scores_tc_k
   if (warp == 0) {
     // ---- TMA producer ----------------------------------------------------------------------------------
     if (lane == 0) {
+      // the key cache is read once per call and is far larger than L2: mark it evict-first so that the score rows
+      // written below stay in L2 for the top-k that follows
+      const uint64_t evict_first = l2_policy_evict_first();
       mbar_arrive_expect_tx(q_bar, N * 128);
       tma_load_2d(q_s, &q_map, 0, static_cast<int>(row0 * 64), q_bar);
       for (int i = 0; i < nblk; ++i) {
         const int s = i % kTcStages;
         if (!mbar_wait(&empty_bar[s], ((i / kTcStages) & 1) ^ 1, p.status, 1)) break;
         mbar_arrive_expect_tx(&full_bar[s], kKeyTileBytes);
-        tma_load_2d(k_s + s * kKeyTileBytes, &key_map, 0, phys_s[i] * 128, &full_bar[s]);
+        tma_load_2d_hint(k_s + s * kKeyTileBytes, &key_map, 0, phys_s[i] * 128, &full_bar[s], evict_first);
       }
     }
   } else if (warp == 1) {
@@ -276,8 +283,8 @@ static int launch_tc(const IndexerParams& p, const CUtensorMap& key_map, dim3 gr
   const uint64_t q_rows = static_cast<uint64_t>(p.b) * p.s1 * 64;
   int rc = make_tensor_map_2d_u8(&q_map, p.q, q_rows, 128, 64 * TOK, 128);
   if (rc != DSV32_OK) return rc;
-  cudaFuncSetAttribute(indexer_scores_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
-  indexer_scores_tc_kernel<TOK><<<grid, TcShape<TOK>::kThreads, kTcSmemBytes, stream>>>(key_map, q_map, p);
+  cudaFuncSetAttribute(indexer_scores_tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmemLayout<TOK>::bytes);
+  indexer_scores_tc_kernel<TOK><<<grid, TcShape<TOK>::kThreads, TcSmemLayout<TOK>::bytes, stream>>>(key_map, q_map, p);
   count_launch();
   return check_launch("indexer_scores_tc_kernel");
 }
