@@ -18,6 +18,9 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
   mla_small.npz      seed + input digests + outputs of mla_prolog_quant_v32_compute
   sfa_bf16_small.npz inputs + output of compute_attention_no_flash with a bf16 (not quantised) cache
   sa_antiquant_small.npz  inputs + output of compute_attention_aq (fused 656-byte cache rows)
+  scfa_small.npz     inputs + output of the DeepSeek-V4 sparse compress attention golden
+                     (models/deepseek_v4/test_sparse_compress_flash_attention.py: window keys + selected
+                     compressed keys + attention sinks)
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -232,6 +235,30 @@ def make_mla():
     print("mla_small: q_nope", tuple(q_nope.shape))
 
 
+def make_scfa():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        import test_sparse_compress_flash_attention as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    b, nq, nkv, cmp_ratio = 3, 64, 1, 4
+    actual_seq_q = [0, 2, 3, 5]
+    ori_seq = [2100, 130, 700]   # compressed lengths 525 (> top-k 512: random selection), 32, 175
+    input_params, data, atten_out = ref.gen_sparse_compress_attention_golden(
+        torch.bfloat16, (b, nq, nkv, 2), actual_seq_q, ori_seq, cmp_ratio)
+    q, cmp_kv, ori_kv, topk_indices, cmp_bt, ori_bt, seq_q, seq_kv, sink = data
+    block_size, win_size, topk, scalar = input_params[7], input_params[8], input_params[9], input_params[10]
+    np.savez_compressed(
+        os.path.join(HERE, "scfa_small.npz"),
+        b=b, nq=nq, cmp_ratio=cmp_ratio, block_size=block_size, win_size=win_size, topk=topk,
+        softmax_scale=np.float64(scalar), actual_seq_q=np.array(seq_q, dtype=np.int32),
+        seqused_kv=seq_kv.numpy(), q=bits16(q), cmp_kv=bits16(cmp_kv), ori_kv=bits16(ori_kv),
+        cmp_sparse_indices=topk_indices.numpy(), cmp_block_table=cmp_bt.numpy(), ori_block_table=ori_bt.numpy(),
+        atten_sink=sink.numpy(), out=bits16(atten_out))
+    print("scfa_small: out", tuple(atten_out.shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -255,3 +282,4 @@ if __name__ == "__main__":
     make_indexer()
     make_prolog()
     make_mla()
+    make_scfa()

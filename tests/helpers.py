@@ -49,6 +49,20 @@ def load_sfa_bf16_golden():
         out=from_bits16(z["out"], bf))
 
 
+def load_scfa_golden():
+    """DeepSeek-V4 sparse compress attention fixture (window keys + selected compressed keys + sinks)."""
+    z = np.load(os.path.join(GOLDEN, "scfa_small.npz"))
+    bf = torch.bfloat16
+    return dict(
+        b=int(z["b"]), nq=int(z["nq"]), cmp_ratio=int(z["cmp_ratio"]), block_size=int(z["block_size"]),
+        win_size=int(z["win_size"]), topk=int(z["topk"]), softmax_scale=float(z["softmax_scale"]),
+        actual_seq_q=torch.from_numpy(z["actual_seq_q"]), seqused_kv=torch.from_numpy(z["seqused_kv"]),
+        q=from_bits16(z["q"], bf), cmp_kv=from_bits16(z["cmp_kv"], bf), ori_kv=from_bits16(z["ori_kv"], bf),
+        cmp_sparse_indices=torch.from_numpy(z["cmp_sparse_indices"]),
+        cmp_block_table=torch.from_numpy(z["cmp_block_table"]), ori_block_table=torch.from_numpy(z["ori_block_table"]),
+        atten_sink=torch.from_numpy(z["atten_sink"]), out=from_bits16(z["out"], bf))
+
+
 def load_sa_antiquant_golden():
     z = np.load(os.path.join(GOLDEN, "sa_antiquant_small.npz"))
     bf = torch.bfloat16

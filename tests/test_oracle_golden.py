@@ -36,6 +36,21 @@ def test_sfa_oracle_matches_reference_golden_bf16_cache():
     assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
 
 
+def test_scfa_oracle_matches_reference_golden():
+    g = helpers.load_scfa_golden()
+    out = orc.scfa(g["q"], g["actual_seq_q"], g["ori_kv"], g["cmp_kv"], g["ori_block_table"], g["cmp_block_table"],
+                   g["atten_sink"], g["seqused_kv"], g["cmp_sparse_indices"], g["nq"], g["softmax_scale"],
+                   g["win_size"], g["cmp_ratio"], g["block_size"])
+    ref = g["out"].reshape(out.shape)
+    assert torch.allclose(out.float(), ref.float(), rtol=1e-2, atol=1e-3)
+    assert orc.reference_compare_count(out, ref, 1e-4, 5e-3) <= 0.005 * out.numel()
+    # the window and the selected compressed keys both matter: dropping either changes the result
+    no_sel = orc.scfa(g["q"], g["actual_seq_q"], g["ori_kv"], g["cmp_kv"], g["ori_block_table"], g["cmp_block_table"],
+                      g["atten_sink"], g["seqused_kv"], g["cmp_sparse_indices"][:, :0], g["nq"], g["softmax_scale"],
+                      g["win_size"], g["cmp_ratio"], g["block_size"])
+    assert not torch.allclose(no_sel.float(), ref.float(), rtol=1e-2, atol=1e-3)
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
