@@ -99,6 +99,41 @@ typedef struct {
 int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * DeepSeek-V4 sparse compress attention: every query token attends to the last win_size
+ * positions of its request in the un-compressed bf16 cache (the window) and to the rows
+ * of the compressed bf16 cache that cmp_sparse_indices selects; a cache row of 512 dims is
+ * key and value at once, and one attention sink per head joins the softmax denominator.
+ * Replaces sparse_compress_flash_attention_kernel / npu_sparse_compress_flash_attention
+ * (models/deepseek_v4/sparse_compress_flash_attention_impl.py:172-213 / 240-299; compute
+ * :47-168).  Token i of a request with s1 = actual_seq_q[r+1] - actual_seq_q[r] tokens:
+ *   cur_len  = max(seqused_kv[r] - s1 + 1 + i, 0), window = positions [cur_len - min(cur_len,
+ *   win_size), cur_len);  selected = first min(max(seqused_kv[r] / cmp_ratio - s1 + 1 + i, 0),
+ *   topk) entries of cmp_sparse_indices[token] (negative entries are skipped).
+ * workspace: dsv32_scfa_workspace_bytes(t, topk, win_size) bytes, 256-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* query;                  /* bf16 [t*n_q, 512]                         */
+  const int32_t* actual_seq_q;        /* int32 [b+1], first token of each request; [b] = t */
+  const void* ori_kv;                 /* bf16 [ori_rows, 512]                      */
+  const void* cmp_kv;                 /* bf16 [cmp_rows, 512]                      */
+  const int32_t* ori_block_table;     /* int32 [b, ori_max_blocks]                 */
+  const int32_t* cmp_block_table;     /* int32 [b, cmp_max_blocks]                 */
+  const float* atten_sink;            /* fp32 [n_q]                                */
+  const int32_t* seqused_kv;          /* int32 [b], un-compressed sequence lengths */
+  const int32_t* cmp_sparse_indices;  /* int32 [t, topk]                           */
+  void* attention_out;                /* bf16 [t*n_q, 512]                         */
+  void* workspace;
+  size_t workspace_bytes;
+  uint32_t* status;                   /* device uint32[4] or NULL                  */
+  int64_t ori_rows, cmp_rows;
+  int32_t t, b, n_q, topk, block_size, win_size, cmp_ratio, ori_max_blocks, cmp_max_blocks;
+  float softmax_scale;
+} Dsv32ScfaArgs;
+
+int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* args, void* cuda_stream);
+size_t dsv32_scfa_workspace_bytes(int32_t t, int32_t topk, int32_t win_size);
+
+/* ---------------------------------------------------------------------------------------
  * Lightning indexer: int8 q.k scores (+ReLU, 2^-11, fp16 round, per-head weighted sum,
  * key scale) and top-k selection.
  * Replaces lightning_indexer_decode

@@ -34,6 +34,18 @@ class SaAntiquantArgs(C.Structure):
     ]
 
 
+class ScfaArgs(C.Structure):
+    _fields_ = [
+        ("query", c_void_p), ("actual_seq_q", c_void_p), ("ori_kv", c_void_p), ("cmp_kv", c_void_p),
+        ("ori_block_table", c_void_p), ("cmp_block_table", c_void_p), ("atten_sink", c_void_p),
+        ("seqused_kv", c_void_p), ("cmp_sparse_indices", c_void_p), ("attention_out", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("status", c_void_p), ("ori_rows", c_i64),
+        ("cmp_rows", c_i64), ("t", c_i32), ("b", c_i32), ("n_q", c_i32), ("topk", c_i32), ("block_size", c_i32),
+        ("win_size", c_i32), ("cmp_ratio", c_i32), ("ori_max_blocks", c_i32), ("cmp_max_blocks", c_i32),
+        ("softmax_scale", c_float),
+    ]
+
+
 class IndexerArgs(C.Structure):
     _fields_ = [
         ("idx_query", c_void_p), ("idx_query_scale", c_void_p), ("idx_key_cache", c_void_p),
@@ -82,6 +94,8 @@ EXPORTS = {
     "dsv32_sfa_quant": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
     "dsv32_sfa_bf16_cache": (c_i32, [C.POINTER(SfaArgs), c_void_p]),
     "dsv32_sparse_attention_antiquant": (c_i32, [C.POINTER(SaAntiquantArgs), c_void_p]),
+    "dsv32_sparse_compress_attention": (c_i32, [C.POINTER(ScfaArgs), c_void_p]),
+    "dsv32_scfa_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32]),
     "dsv32_indexer_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
     "dsv32_indexer_topk": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
     "dsv32_indexer_topk_noalloc": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),

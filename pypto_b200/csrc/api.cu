@@ -178,6 +178,70 @@ int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* a, void* cuda_s
   return sfa_run(&s, cuda_stream, DSV32_ANTIQUANT_ROW_BYTES, DSV32_ANTIQUANT_ROW_BYTES, DSV32_ANTIQUANT_ROW_BYTES);
 }
 
+// ---- DeepSeek-V4 sparse compress attention ------------------------------------------------------------------
+size_t dsv32_scfa_workspace_bytes(int32_t t, int32_t topk, int32_t win_size) {
+  if (t <= 0 || topk < 0 || win_size < 0) return 0;
+  // cache row of every listed key + the length of every token's list
+  return align_up(static_cast<size_t>(t) * (static_cast<size_t>(topk) + win_size) * sizeof(int32_t), 256) +
+         align_up(static_cast<size_t>(t) * sizeof(int32_t), 256);
+}
+
+int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "scfa: args is NULL");
+  REQUIRE(a->t >= 0 && a->b >= 0, "scfa: bad t=%d b=%d", a->t, a->b);
+  if (a->t == 0 || a->b == 0) return DSV32_OK;
+  REQUIRE(a->n_q >= 1 && a->n_q <= 128, "scfa: n_q=%d must be in [1, 128]", a->n_q);
+  REQUIRE(a->topk >= 0 && a->win_size >= 0 && a->topk + a->win_size >= 1, "scfa: bad topk=%d win_size=%d", a->topk,
+          a->win_size);
+  REQUIRE(a->cmp_ratio >= 1, "scfa: cmp_ratio=%d must be >= 1", a->cmp_ratio);
+  REQUIRE(a->block_size >= 1 && a->ori_max_blocks >= 1 && a->cmp_max_blocks >= 1,
+          "scfa: bad block_size=%d ori_max_blocks=%d cmp_max_blocks=%d", a->block_size, a->ori_max_blocks,
+          a->cmp_max_blocks);
+  REQUIRE(a->ori_rows >= 0 && a->cmp_rows >= 0, "scfa: bad ori_rows=%lld cmp_rows=%lld",
+          static_cast<long long>(a->ori_rows), static_cast<long long>(a->cmp_rows));
+  REQUIRE(a->query && a->actual_seq_q && a->ori_kv && a->cmp_kv && a->ori_block_table && a->cmp_block_table &&
+              a->atten_sink && a->seqused_kv && a->cmp_sparse_indices && a->attention_out,
+          "scfa: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->query) % 16 == 0 && reinterpret_cast<uintptr_t>(a->ori_kv) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->cmp_kv) % 16 == 0 && reinterpret_cast<uintptr_t>(a->attention_out) % 16 == 0,
+          "scfa: tensors must be 16-byte aligned");
+  SfaParams p{};
+  p.compress = 1;
+  p.kn_bf16 = 1;
+  p.q_nope = static_cast<const __nv_bfloat16*>(a->query);
+  p.k_nope = static_cast<const int8_t*>(a->ori_kv);
+  p.k_nope2 = static_cast<const __nv_bfloat16*>(a->cmp_kv);
+  p.topk_idx = a->cmp_sparse_indices;
+  p.block_table = a->ori_block_table;
+  p.block_table2 = a->cmp_block_table;
+  p.act_seq = a->seqused_kv;
+  p.seq_q = a->actual_seq_q;
+  p.sinks = a->atten_sink;
+  p.out = static_cast<__nv_bfloat16*>(a->attention_out);
+  p.status = a->status;
+  p.rows = a->ori_rows;
+  p.rows2 = a->cmp_rows;
+  p.b = a->b; p.s1 = 1; p.t_total = a->t; p.nq = a->n_q;
+  p.topk = a->topk + a->win_size;  // length of a token's key list
+  p.sel_topk = a->topk; p.win_size = a->win_size; p.cmp_ratio = a->cmp_ratio;
+  p.block_size = a->block_size;
+  p.bs_shift = -1;
+  p.max_blocks = a->ori_max_blocks; p.max_blocks2 = a->cmp_max_blocks;
+  p.splits = 1;
+  p.scale = a->softmax_scale;
+  p.nope_stride = kKvLora * 2; p.rope_stride = 0; p.scale_stride = 0;
+  const size_t need = dsv32_scfa_workspace_bytes(a->t, a->topk, a->win_size);
+  if (a->workspace == nullptr || a->workspace_bytes < need || reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) {
+    set_error("scfa: workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
+  char* ws = static_cast<char*>(a->workspace);
+  p.row_ids = reinterpret_cast<int32_t*>(ws);
+  p.key_counts = reinterpret_cast<int32_t*>(
+      ws + align_up(static_cast<size_t>(a->t) * (static_cast<size_t>(a->topk) + a->win_size) * sizeof(int32_t), 256));
+  return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
 // ---- lightning indexer --------------------------------------------------------------------------------
 size_t dsv32_indexer_workspace_bytes(int32_t b, int32_t s1, int32_t max_blocks, int32_t block_size) {
   if (b <= 0 || s1 <= 0 || max_blocks <= 0 || block_size <= 0) return 0;

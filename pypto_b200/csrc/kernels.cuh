@@ -57,6 +57,18 @@ struct SfaParams {
   int nope_stride, rope_stride, scale_stride;
   int kn_bf16;  // 1: the latent cache is bf16 [rows, 512] and there are no scales (tcgen05 kernel only)
   float scale;
+  // DeepSeek-V4 sparse compress attention only (compress != 0; tcgen05 kernel, bf16 rows of 512 dims that serve
+  // as key and value, no rope part).  A token's key list is its window rows of k_nope (paged by block_table)
+  // followed by the rows of k_nope2 that sel_idx selects (paged by block_table2); `topk` is then the length of
+  // that list (win_size + sel_topk) and act_seq holds the un-compressed sequence lengths.
+  int compress;
+  const __nv_bfloat16* k_nope2;
+  const int32_t* block_table2;
+  const int32_t* seq_q;     // [b + 1] first token of every request, seq_q[b] = number of tokens
+  const float* sinks;       // [nq] attention sinks
+  int32_t* key_counts;      // [t] scratch: keys in each token's list
+  long long rows2;
+  int max_blocks2, win_size, sel_topk, cmp_ratio, t_total;
 };
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);
 int launch_sfa_tc(const SfaParams& p, cudaStream_t stream);

@@ -18,6 +18,12 @@
 // PV has.  The cache row of every selected key comes from a pre-pass (sfa_row_ids_kernel).
 // The running maximum is only raised when a tile exceeds it by more than 2^8 (warp-uniform decision), so
 // the read-modify-write of O in tensor memory is rare; P stays below 2^8 in between.
+//
+// The same kernel, as mode 2, is the DeepSeek-V4 sparse compress attention
+// (models/deepseek_v4/sparse_compress_flash_attention_impl.py:47-168): bf16 rows of 512 dims that are key and
+// value at once (no rope part: 32 instead of 36 MMAs per S tile), a key list made of the token's window rows of
+// one cache followed by selected rows of a second (compressed) cache, up to 128 query heads (heads past n_q
+// are idle lanes of the M = 128 tile), and one attention sink per head added to the softmax denominator.
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
@@ -61,6 +67,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Raw cache data of one row as held by one producer thread.  kBf16: the latent cache is already bf16 (no scales;
 // twice the bytes), otherwise int8 with one fp32 scale per 128-dim group.
+constexpr int kModeInt8 = 0, kModeBf16 = 1, kModeCompress = 2;
+
 template <bool kBf16>
 struct StPrefetchT {
   int4 nope[kBf16 ? 8 : 4];
@@ -114,7 +122,63 @@ __global__ void __launch_bounds__(256) sfa_row_ids_kernel(SfaParams p) {
   p.row_ids[static_cast<size_t>(tok) * p.topk + j] = out;
 }
 
-template <bool kBf16>
+// Key list of every token for the sparse compress attention: first the window rows (the last
+// min(cur_len, win_size) positions before cur_len = max(seq - s1 + 1 + i, 0), paged by block_table), then the
+// rows of the compressed cache named by the first min(max(seq / cmp_ratio - s1 + 1 + i, 0), sel_topk) entries of
+// the token's index row (paged by block_table2)  (sparse_compress_flash_attention_impl.py:83-131).
+// An entry is row + 1, with bit 31 set for a row of the compressed cache; 0 = no key.
+__global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
+  const int tok = blockIdx.y;
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= p.topk) return;
+  // request of this token: the last bi with seq_q[bi] <= tok
+  int lo = 0, hi = p.b;  // invariant: seq_q[lo] <= tok < seq_q[hi] for well-formed input
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(p.seq_q + mid) <= tok) lo = mid; else hi = mid;
+  }
+  const int bi = lo;
+  const int q0 = __ldg(p.seq_q + bi), q1 = __ldg(p.seq_q + bi + 1);
+  int out = 0, win = 0, sel = 0;
+  if (tok < q0 || tok >= q1) {
+    if (j == 0) report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, bi);
+  } else {
+    const int s1 = q1 - q0, si = tok - q0;
+    const int seq = __ldg(p.act_seq + bi);
+    const int cur_len = max(seq - s1 + 1 + si, 0);
+    win = min(cur_len, p.win_size);
+    sel = min(max(seq / p.cmp_ratio - s1 + 1 + si, 0), p.sel_topk);
+    if (j < win) {
+      const int pos = cur_len - win + j;
+      const int lb = pos / p.block_size;
+      if (lb >= p.max_blocks) {
+        report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, pos);
+      } else {
+        const int pb = __ldg(p.block_table + static_cast<size_t>(bi) * p.max_blocks + lb);
+        const long long row = static_cast<long long>(pb) * p.block_size + pos % p.block_size;
+        if (pb < 0 || row >= p.rows) report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, pos);
+        else out = static_cast<int>(row) + 1;
+      }
+    } else if (j < win + sel) {
+      const int idx = __ldg(p.topk_idx + static_cast<size_t>(tok) * p.sel_topk + (j - win));
+      if (idx >= 0) {
+        const int lb = idx / p.block_size;
+        if (lb >= p.max_blocks2) {
+          report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, idx);
+        } else {
+          const int pb = __ldg(p.block_table2 + static_cast<size_t>(bi) * p.max_blocks2 + lb);
+          const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
+          if (pb < 0 || row >= p.rows2) report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, idx);
+          else out = static_cast<int>((static_cast<uint32_t>(row) + 1u) | 0x80000000u);
+        }
+      }
+    }
+  }
+  p.row_ids[static_cast<size_t>(tok) * p.topk + j] = out;
+  if (j == 0) p.key_counts[tok] = win + sel;
+}
+
+template <int kMode>
 __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
                                                                const __grid_constant__ CUtensorMap qr_map,
                                                                SfaParams p) {
@@ -136,8 +200,16 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
   const int half = blockIdx.x;  // which 256 value dims
   const int tok = blockIdx.y;
   const int split = blockIdx.z;
-  const int bi = tok / p.s1, si = tok % p.s1;
-  const int cnt = min(max(p.act_seq[bi] - p.s1 + 1 + si, 0), p.topk);
+  constexpr bool kBf16 = kMode != kModeInt8;
+  constexpr bool kCompress = kMode == kModeCompress;
+  constexpr int kSteps = kCompress ? 32 : 36;  // 16-dim MMA steps of one S tile (no rope dims in mode 2)
+  int cnt;
+  if constexpr (kCompress) {
+    cnt = min(max(p.key_counts[tok], 0), p.topk);
+  } else {
+    const int bi = tok / p.s1, si = tok % p.s1;
+    cnt = min(max(p.act_seq[bi] - p.s1 + 1 + si, 0), p.topk);
+  }
   const int per = (((cnt + p.splits - 1) / p.splits) + kStTile - 1) / kStTile * kStTile;
   const int k_lo = split * per;
   const int k_hi = min(cnt, k_lo + per);
@@ -146,6 +218,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
   if (ntiles == 0) {  // nothing to attend to: zero row block (uniform for the CTA)
     for (int i = tid; i < 128 * 64; i += kStThreads) {
       const int h = i >> 6, c = i & 63;  // 64 chunks of 4 dims
+      if (h >= p.nq) continue;
       if (p.splits == 1) {
         *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(tok) * p.nq + h) * kKvLora + half * 256 + c * 4) =
             make_uint2(0u, 0u);
@@ -187,10 +260,10 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     // ================================ MMA issuer ==========================================================
     if (lane == 0) {
       // Q dims 256..575 -> shared memory (TMA, 128-byte swizzle): nope chunks 4..7 and the rope chunk
-      mbar_arrive_expect_tx(q_bar, kStQsBytes);
+      mbar_arrive_expect_tx(q_bar, kCompress ? 4 * kStQChunkBytes : kStQsBytes);
       for (int c = 0; c < 4; ++c)
         tma_load_2d(q_s + c * kStQChunkBytes, &qn_map, (4 + c) * 128, tok * p.nq, q_bar);
-      tma_load_2d(q_s + 4 * kStQChunkBytes, &qr_map, 0, tok * p.nq, q_bar);
+      if constexpr (!kCompress) tma_load_2d(q_s + 4 * kStQChunkBytes, &qr_map, 0, tok * p.nq, q_bar);
 
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, kStTile, false, false);
       bool ok = mbar_wait(q_bar, 0, p.status, 10);
@@ -226,7 +299,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
           umma_f16_ts(d, tmem_base + kColQ + ks * 8, desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)),
                       idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 16; ks < 36; ++ks)  // Q dims 256..575 from shared memory
+        for (int ks = 16; ks < kSteps; ++ks)  // Q dims 256..575 (256..511 in mode 2) from shared memory
           umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
                       desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
         umma_commit(&sfull_bar[s]);
@@ -246,7 +319,8 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         uint32_t r[32];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint4 v = __ldg(qrow + c * 8 + j);
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (!kCompress || head < p.nq) v = __ldg(qrow + c * 8 + j);
           r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
         }
         tmem_st_32x32b_x32(tmem_base + lane_addr + kColQ + c * 32, r);
@@ -351,8 +425,13 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pvdone_bar[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, p.status, 22));
     if (ok) {
       tc_fence_after();
+      if constexpr (kCompress) {  // the sink joins the denominator only: + exp(sink - max), in the units of m_run
+        if (head < p.nq && m_run != -INFINITY) l_run += exp2f(fmaf(__ldg(p.sinks + head), 1.4426950408889634f, -m_run));
+      }
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      if (p.splits == 1) {
+      if (kCompress && head >= p.nq) {
+        // idle lane of the M = 128 tile: nothing to store
+      } else if (p.splits == 1) {
         __nv_bfloat16* orow = p.out + (static_cast<size_t>(tok) * p.nq + head) * kKvLora + half * 256;
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
@@ -413,14 +492,26 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       asm volatile("cp.async.wait_group 1;" ::: "memory");
       __syncwarp();
     };
-    auto row_of = [&](int tile, int pass) -> long long {  // -1 = none
-      return static_cast<long long>(ring[(tile & 3) * 8 + pass * 4 + (lane >> 3)]) - 1;
+    // Mode 2 keeps the pre-pass entry as it is (bit 31 = row of the second cache, low bits = row + 1, 0 = none);
+    // the other modes turn it into the row, -1 = none.
+    auto row_of = [&](int tile, int pass) -> long long {
+      const int v = ring[(tile & 3) * 8 + pass * 4 + (lane >> 3)];
+      if constexpr (kCompress) return static_cast<long long>(v);
+      else return static_cast<long long>(v) - 1;
     };
     const unsigned char* nope_b = reinterpret_cast<const unsigned char*>(p.k_nope);
     const unsigned char* rope_b = reinterpret_cast<const unsigned char*>(p.k_rope);
     const unsigned char* scale_b = reinterpret_cast<const unsigned char*>(p.k_scales);
     const bool fused_rows = p.nope_stride == p.rope_stride;  // one 656-byte row holds all three parts
     auto l2_prefetch = [&](long long row) {  // the 128-byte lines of a row, one per thread column
+      if constexpr (kCompress) {
+        const int v = static_cast<int>(row);
+        if (v != 0) {
+          const unsigned char* base = v < 0 ? reinterpret_cast<const unsigned char*>(p.k_nope2) : nope_b;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<long long>((v & 0x7fffffff) - 1) * 1024 + gpart * 128));
+        }
+        return;
+      }
       if (row < 0) return;
       const void* a = nullptr;
       if (fused_rows) {
@@ -444,9 +535,17 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     const int q_own = 2 * half, q_oth = 2 * (half ^ 1);
     using StPrefetch = StPrefetchT<kBf16>;
     auto issue_loads = [&](long long row, StPrefetch& pf) {
-      pf.valid = row >= 0;
+      const int4* src;
+      if constexpr (kCompress) {
+        const int v = static_cast<int>(row);
+        pf.valid = v != 0;
+        const unsigned char* base = v < 0 ? reinterpret_cast<const unsigned char*>(p.k_nope2) : nope_b;
+        src = reinterpret_cast<const int4*>(base + static_cast<long long>((v & 0x7fffffff) - 1) * 1024);
+      } else {
+        pf.valid = row >= 0;
+        src = reinterpret_cast<const int4*>(nope_b + row * p.nope_stride);
+      }
       if (pf.valid) {
-        const int4* src = reinterpret_cast<const int4*>(nope_b + row * p.nope_stride);
         if constexpr (kBf16) {  // this thread's 16 dims of a 128-dim group are two consecutive 16-byte units
           pf.nope[0] = __ldg(src + 2 * gpart + 16 * q_own);
           pf.nope[1] = __ldg(src + 2 * gpart + 16 * q_own + 1);
@@ -456,7 +555,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
           pf.nope[5] = __ldg(src + 2 * gpart + 16 * q_oth + 1);
           pf.nope[6] = __ldg(src + 2 * gpart + 16 * (q_oth + 1));
           pf.nope[7] = __ldg(src + 2 * gpart + 16 * (q_oth + 1) + 1);
-          pf.rope = __ldg(reinterpret_cast<const int4*>(rope_b + row * p.rope_stride) + gpart);
+          if constexpr (!kCompress) pf.rope = __ldg(reinterpret_cast<const int4*>(rope_b + row * p.rope_stride) + gpart);
         } else {
           pf.nope[0] = __ldg(src + gpart + 8 * q_own);
           pf.nope[1] = __ldg(src + gpart + 8 * (q_own + 1));
@@ -499,9 +598,11 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       const int r = pass * 32 + gkey;  // row (key) inside the tile
       store_group(stage, r, q_oth, 2, pf);
       store_group(stage, r, q_oth + 1, 3, pf);
-      unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
-      const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
-      *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
+      if constexpr (!kCompress) {
+        unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
+        const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
+        *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
+      }
     };
     // ... and the chunks that PV reads as V (this CTA's own value dims), plus the validity flag
     auto commit_own = [&](int tile, int pass, const StPrefetch& pf) {
@@ -563,30 +664,46 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
 }
 
 int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
-  const int t = p.b * p.s1;
+  const int t = p.compress ? p.t_total : p.b * p.s1;
   if (t <= 0) return DSV32_OK;
-  if (p.nq != 128) {
-    set_error("sfa: the tcgen05 kernel needs n_q == 128 (got %d)", p.nq);
+  if (p.compress ? (p.nq < 1 || p.nq > 128) : p.nq != 128) {
+    set_error("sfa: the tcgen05 kernel needs n_q == 128 (1..128 for the compress variant), got %d", p.nq);
+    return DSV32_ERR_UNSUPPORTED;
+  }
+  if (p.compress && p.splits != 1) {
+    set_error("sfa: the compress variant runs without a key split");
     return DSV32_ERR_UNSUPPORTED;
   }
   CUtensorMap qn_map, qr_map;
   int rc = make_tensor_map_2d_u8(&qn_map, p.q_nope, static_cast<uint64_t>(t) * p.nq, kKvLora * 2, 128, 128);
   if (rc != DSV32_OK) return rc;
-  rc = make_tensor_map_2d_u8(&qr_map, p.q_rope, static_cast<uint64_t>(t) * p.nq, kRopeDim * 2, 128, 128);
-  if (rc != DSV32_OK) return rc;
-  cudaFuncSetAttribute(sfa_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
-  cudaFuncSetAttribute(sfa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
-  if (p.rows > 0x7ffffffeLL) {
+  if (p.compress) {
+    qr_map = qn_map;  // no rope part: the second map is never used
+  } else {
+    rc = make_tensor_map_2d_u8(&qr_map, p.q_rope, static_cast<uint64_t>(t) * p.nq, kRopeDim * 2, 128, 128);
+    if (rc != DSV32_OK) return rc;
+  }
+  cudaFuncSetAttribute(sfa_tc_kernel<kModeInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  cudaFuncSetAttribute(sfa_tc_kernel<kModeBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  cudaFuncSetAttribute(sfa_tc_kernel<kModeCompress>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  if (p.rows > 0x7ffffffeLL || (p.compress && p.rows2 > 0x7ffffffeLL)) {
     set_error("sfa: the tcgen05 kernel addresses at most 2^31-2 cache rows (got %lld)", static_cast<long long>(p.rows));
     return DSV32_ERR_UNSUPPORTED;
   }
-  sfa_row_ids_kernel<<<dim3((p.topk + 255) / 256, t), 256, 0, stream>>>(p);
-  count_launch();
-  rc = check_launch("sfa_row_ids_kernel");
+  if (p.compress) {
+    scfa_row_ids_kernel<<<dim3((p.topk + 255) / 256, t), 256, 0, stream>>>(p);
+    count_launch();
+    rc = check_launch("scfa_row_ids_kernel");
+  } else {
+    sfa_row_ids_kernel<<<dim3((p.topk + 255) / 256, t), 256, 0, stream>>>(p);
+    count_launch();
+    rc = check_launch("sfa_row_ids_kernel");
+  }
   if (rc != DSV32_OK) return rc;
   dim3 grid(2, t, p.splits);
-  if (p.kn_bf16) sfa_tc_kernel<true><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
-  else sfa_tc_kernel<false><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
+  if (p.compress) sfa_tc_kernel<kModeCompress><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
+  else if (p.kn_bf16) sfa_tc_kernel<kModeBf16><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
+  else sfa_tc_kernel<kModeInt8><<<grid, kStThreads, kStSmemBytes, stream>>>(qn_map, qr_map, p);
   count_launch();
   rc = check_launch("sfa_tc_kernel");
   if (rc == DSV32_OK && p.splits > 1) rc = launch_sfa_combine(p, stream);

@@ -192,6 +192,45 @@ def gen_sfa_inputs(seed, act_seq, s1=1, nq=128, topk=2048, block_size=128, pad_s
                 softmax_scale=576 ** -0.5, topk=topk, block_size=block_size)
 
 
+def gen_scfa_inputs(seed, ori_seq, s1_list, nq=64, topk=512, win_size=128, cmp_ratio=4, block_size=128, holes=0,
+                    scale=1.0):
+    """Seeded synthetic inputs of the DeepSeek-V4 sparse compress attention in the operator's layouts: queries,
+    both caches and the sinks uniform in [-scale, scale) (the reference test uses [-1, 1)), pages randomly
+    permuted, selected indices a random subset of each request's compressed positions.  `holes`: this many
+    entries of every index row are replaced by -1."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    b = len(ori_seq)
+    seq_q = [0]
+    for s1 in s1_list:
+        seq_q.append(seq_q[-1] + s1)
+    t = seq_q[-1]
+    cmp_seq = [int(L) // cmp_ratio for L in ori_seq]
+    ori_blocks, ori_bt = make_block_table([max(int(L), 1) for L in ori_seq], block_size, g, 1)
+    cmp_blocks, cmp_bt = make_block_table([max(L, 1) for L in cmp_seq], block_size, g, 1)
+
+    def uni(shape):
+        return ((torch.rand(shape, generator=g) * 2 - 1) * scale).to(bf)
+
+    q = uni((t * nq, 512))
+    ori_kv = uni((ori_blocks * block_size, 512))
+    cmp_kv = uni((cmp_blocks * block_size, 512))
+    sink = (torch.rand((nq,), generator=g) * 2 - 1) * scale
+    idx = torch.full((t, topk), -1, dtype=torch.int32)
+    for bi in range(b):
+        for si in range(s1_list[bi]):
+            tok = seq_q[bi] + si
+            n = min(cmp_seq[bi], topk)
+            if n > 0:
+                idx[tok, :n] = torch.randperm(cmp_seq[bi], generator=g)[:n].to(torch.int32)
+            if holes:
+                idx[tok, torch.randperm(topk, generator=g)[:holes]] = -1
+    return dict(q=q, ori_kv=ori_kv, cmp_kv=cmp_kv, atten_sink=sink, cmp_sparse_indices=idx, ori_block_table=ori_bt,
+                cmp_block_table=cmp_bt, actual_seq_q=torch.tensor(seq_q, dtype=torch.int32),
+                seqused_kv=torch.tensor(ori_seq, dtype=torch.int32), b=b, nq=nq, topk=topk, win_size=win_size,
+                cmp_ratio=cmp_ratio, block_size=block_size, softmax_scale=512 ** -0.5)
+
+
 def gen_indexer_inputs(seed, act_seq, s1=1, block_size=128, extra_blocks=0):
     g = torch.Generator().manual_seed(seed)
     b = len(act_seq)

@@ -221,13 +221,13 @@ def _sfa_oracle(d, tokens=None):
                          tokens=tokens)
 
 
-def _assert_attention_close(out, ref):
+def _assert_attention_close(out, ref, strict_frac=0.15):
     o, r = out.float(), ref.float()
     assert not torch.isnan(o).any()
     err = (o - r).abs()
     assert torch.allclose(o, r, rtol=1e-2, atol=1e-2), f"max-abs {err.max():.4g} mean-abs {err.mean():.4g}"
     strict = orc.reference_compare_count(out, ref, 1e-4, 5e-3)
-    assert strict <= 0.15 * out.numel(), f"{strict} of {out.numel()} outside the reference's own last-bit rule"
+    assert strict <= strict_frac * out.numel(), f"{strict} of {out.numel()} outside the reference's own last-bit rule"
     assert err.mean() <= 1e-2 * r.abs().mean() + 1e-6, f"mean-abs {err.mean():.4g} vs mean |ref| {r.abs().mean():.4g}"
     return float(err.max()), float(err.mean())
 
@@ -250,6 +250,113 @@ def test_sfa_bf16_cache_reference_golden_fixture_and_seeded():
     d["k_scales"] = None
     _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
     _assert_attention_close(_run_sfa(d, kv_splits=3), _sfa_oracle(d))
+
+
+# ---- DeepSeek-V4 sparse compress attention (window + selected compressed keys + sinks) -------------------------
+def _run_scfa(d, entry="kernel"):
+    import pypto_b200
+    from pypto_b200 import sparse_compress_flash_attention_impl as scfa
+    c = _cuda(d)
+    args = (c["q"], c["actual_seq_q"], c["ori_kv"], c["cmp_kv"], c["ori_block_table"], c["cmp_block_table"],
+            c["atten_sink"], c["seqused_kv"], c["cmp_sparse_indices"])
+    if entry == "kernel":
+        out = torch.full_like(c["q"], float("nan"))
+        cfg = scfa.SCFATileShapeConfig(64, [64, 64, 128, 512, 128, 128], [32, 640], [64, 64, 128, 640, 256, 256])
+        assert scfa.sparse_compress_flash_attention_kernel(*args, out, d["nq"], 1, d["softmax_scale"], d["topk"],
+                                                           d["block_size"], d["win_size"], d["cmp_ratio"], cfg) is None
+    else:
+        fn = scfa.npu_sparse_compress_flash_attention if entry == "npu" else scfa.sparse_compress_flash_attention_graph
+        out = fn(*args, d["softmax_scale"], d["win_size"], d["cmp_ratio"])
+    pypto_b200.check_status()
+    return out.cpu()
+
+
+def _scfa_oracle(d):
+    return orc.scfa(d["q"], d["actual_seq_q"], d["ori_kv"], d["cmp_kv"], d["ori_block_table"], d["cmp_block_table"],
+                    d["atten_sink"], d["seqused_kv"], d["cmp_sparse_indices"], d["nq"], d["softmax_scale"],
+                    d["win_size"], d["cmp_ratio"], d["block_size"])
+
+
+def test_scfa_reference_golden_fixture():
+    g = helpers.load_scfa_golden()
+    out = _run_scfa(g)
+    _assert_attention_close(out, g["out"].reshape(out.shape))
+    _assert_attention_close(out, _scfa_oracle(g))
+    assert torch.equal(_run_scfa(g, "npu"), out)
+    assert torch.equal(_run_scfa(g, "graph"), out)
+
+
+@pytest.mark.parametrize("seed,ori_seq,s1_list,nq,kw", [
+    (1, [8192, 8192, 8192, 8192], [2, 2, 2, 2], 64, {}),                       # the reference's decode shape, 4 requests
+    (2, [65536, 130, 700, 50], [16, 1, 3, 4], 64, {}),                         # ragged s1; a context shorter than the window
+    (3, [3, 1, 2100, 0], [1, 3, 2, 2], 64, {}),                                # no compressed key; tokens with no key at all
+    (4, [2100, 4000], [2, 1], 128, {"holes": 37}),                             # 128 heads; -1 entries among the selected
+    (5, [5000, 300], [1, 2], 32, {"topk": 200, "win_size": 64, "cmp_ratio": 8, "scale": 3.0}),   # other sizes, peaked softmax
+    (6, [900], [5], 64, {"topk": 64, "win_size": 300, "cmp_ratio": 2}),        # window longer than two pages
+])
+def test_scfa_seeded_cases(seed, ori_seq, s1_list, nq, kw):
+    d = helpers.gen_scfa_inputs(700 + seed, ori_seq, s1_list, nq=nq, **kw)
+    out = _run_scfa(d)
+    ref = _scfa_oracle(d)
+    # With a peaked softmax few keys carry the sum, so the bf16 rounding of the probabilities (un-normalised in the
+    # kernel, normalised in the reference) shows in the last bit of more outputs; the 1e-2 bar is unchanged.
+    _assert_attention_close(out, ref, strict_frac=0.35 if kw.get("scale", 1.0) > 1.0 else 0.15)
+    # a token without any key (context shorter than its position) yields a zero row, as in the oracle
+    assert torch.equal(out.float().abs().sum(-1) == 0, ref.float().abs().sum(-1) == 0)
+
+
+def test_scfa_sink_and_window_matter():
+    """The sink only enters the denominator; dropping it, or the window, must change the result."""
+    d = helpers.gen_scfa_inputs(770, [1000, 600], [1, 2])
+    out = _run_scfa(d)
+    d2 = dict(d, atten_sink=torch.full_like(d["atten_sink"], -1e30))
+    no_sink = _run_scfa(d2)
+    _assert_attention_close(no_sink, _scfa_oracle(d2))
+    assert not torch.allclose(out.float(), no_sink.float(), rtol=1e-2, atol=1e-4)
+    big = dict(d, atten_sink=torch.full_like(d["atten_sink"], 30.0))   # a dominant sink drives the output to zero
+    assert _run_scfa(big).float().abs().max() < 1e-6
+    d3 = dict(d, win_size=0)
+    _assert_attention_close(_run_scfa(d3), _scfa_oracle(d3))
+
+
+def test_scfa_bad_arguments_and_bad_pages():
+    import pypto_b200
+    from pypto_b200 import sparse_compress_flash_attention_impl as scfa
+    d = helpers.gen_scfa_inputs(780, [600, 300], [1, 1])
+    c = _cuda(d)
+
+    def call(**over):
+        a = dict(c, **over)
+        out = torch.zeros_like(a["q"])
+        scfa.sparse_compress_flash_attention_kernel(
+            a["q"], a["actual_seq_q"], a["ori_kv"], a["cmp_kv"], a["ori_block_table"], a["cmp_block_table"],
+            a["atten_sink"], a["seqused_kv"], a["cmp_sparse_indices"], out, over.get("nq", d["nq"]), over.get("n_kv", 1),
+            d["softmax_scale"], d["topk"], d["block_size"], d["win_size"], over.get("cmp_ratio", d["cmp_ratio"]), None)
+
+    with pytest.raises(ValueError):
+        call(q=c["q"].float())
+    with pytest.raises(ValueError):
+        call(n_kv=2)
+    with pytest.raises(ValueError):
+        call(actual_seq_q=c["actual_seq_q"][:-1].contiguous())
+    with pytest.raises(ValueError):
+        call(atten_sink=c["atten_sink"][:-1].contiguous())
+    with pytest.raises(ValueError):
+        call(cmp_ratio=0)
+    with pytest.raises(RuntimeError):
+        call(q=d["q"])                                    # host tensor
+    bad = c["cmp_block_table"].clone()
+    bad[0, 0] = -1                                        # a selected key on a page that is not mapped
+    call(cmp_block_table=bad)
+    with pytest.raises(RuntimeError):
+        pypto_b200.check_status()
+    bad = c["ori_block_table"].clone()
+    bad[1, 2] = 10 ** 6                                   # a window row past the end of the cache
+    call(ori_block_table=bad)
+    with pytest.raises(RuntimeError):
+        pypto_b200.check_status()
+    call()                                                # the context stays usable
+    pypto_b200.check_status()
 
 
 def _run_sa_antiquant(d, cache, entry="d", flat_out=False):
