@@ -109,8 +109,16 @@ int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* args, void* cud
  *   cur_len  = max(seqused_kv[r] - s1 + 1 + i, 0), window = positions [cur_len - min(cur_len,
  *   win_size), cur_len);  selected = first min(max(seqused_kv[r] / cmp_ratio - s1 + 1 + i, 0),
  *   topk) entries of cmp_sparse_indices[token] (negative entries are skipped).
+ * cmp_mode DSV32_SCFA_ALL_COMPRESSED instead takes every compressed position
+ *   [0, min(cur_len / cmp_ratio, topk)) and ignores cmp_sparse_indices (may be NULL): the
+ *   compress_flash_attention operator (models/deepseek_v4/compress_flash_attention_impl.py:
+ *   60-112 cfa_attention, :119-219 c128_decode_impl).  topk == 0 leaves the window alone: the
+ *   sliding-window attention operator (models/deepseek_v4/win_attention_impl.py:78-260,263-289);
+ *   cmp_kv / cmp_block_table may then be NULL.
  * workspace: dsv32_scfa_workspace_bytes(t, topk, win_size) bytes, 256-byte aligned.
  * ------------------------------------------------------------------------------------- */
+#define DSV32_SCFA_SELECTED 0
+#define DSV32_SCFA_ALL_COMPRESSED 1
 typedef struct {
   const void* query;                  /* bf16 [t*n_q, 512]                         */
   const int32_t* actual_seq_q;        /* int32 [b+1], first token of each request; [b] = t */
@@ -127,6 +135,7 @@ typedef struct {
   uint32_t* status;                   /* device uint32[4] or NULL                  */
   int64_t ori_rows, cmp_rows;
   int32_t t, b, n_q, topk, block_size, win_size, cmp_ratio, ori_max_blocks, cmp_max_blocks;
+  int32_t cmp_mode;                   /* DSV32_SCFA_SELECTED or DSV32_SCFA_ALL_COMPRESSED */
   float softmax_scale;
 } Dsv32ScfaArgs;
 

@@ -42,7 +42,7 @@ class ScfaArgs(C.Structure):
         ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("status", c_void_p), ("ori_rows", c_i64),
         ("cmp_rows", c_i64), ("t", c_i32), ("b", c_i32), ("n_q", c_i32), ("topk", c_i32), ("block_size", c_i32),
         ("win_size", c_i32), ("cmp_ratio", c_i32), ("ori_max_blocks", c_i32), ("cmp_max_blocks", c_i32),
-        ("softmax_scale", c_float),
+        ("cmp_mode", c_i32), ("softmax_scale", c_float),
     ]
 
 

@@ -194,14 +194,19 @@ int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
   REQUIRE(a->topk >= 0 && a->win_size >= 0 && a->topk + a->win_size >= 1, "scfa: bad topk=%d win_size=%d", a->topk,
           a->win_size);
   REQUIRE(a->cmp_ratio >= 1, "scfa: cmp_ratio=%d must be >= 1", a->cmp_ratio);
-  REQUIRE(a->block_size >= 1 && a->ori_max_blocks >= 1 && a->cmp_max_blocks >= 1,
+  REQUIRE(a->block_size >= 1 && a->ori_max_blocks >= 1 && (a->cmp_max_blocks >= 1 || a->topk == 0),
           "scfa: bad block_size=%d ori_max_blocks=%d cmp_max_blocks=%d", a->block_size, a->ori_max_blocks,
           a->cmp_max_blocks);
   REQUIRE(a->ori_rows >= 0 && a->cmp_rows >= 0, "scfa: bad ori_rows=%lld cmp_rows=%lld",
           static_cast<long long>(a->ori_rows), static_cast<long long>(a->cmp_rows));
-  REQUIRE(a->query && a->actual_seq_q && a->ori_kv && a->cmp_kv && a->ori_block_table && a->cmp_block_table &&
-              a->atten_sink && a->seqused_kv && a->cmp_sparse_indices && a->attention_out,
+  REQUIRE(a->cmp_mode == DSV32_SCFA_SELECTED || a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED, "scfa: bad cmp_mode=%d",
+          a->cmp_mode);
+  REQUIRE(a->query && a->actual_seq_q && a->ori_kv && a->ori_block_table && a->atten_sink && a->seqused_kv &&
+              a->attention_out,
           "scfa: NULL tensor pointer");
+  REQUIRE(a->topk == 0 || (a->cmp_kv && a->cmp_block_table &&
+                           (a->cmp_sparse_indices || a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED)),
+          "scfa: NULL compressed-cache pointer");
   REQUIRE(reinterpret_cast<uintptr_t>(a->query) % 16 == 0 && reinterpret_cast<uintptr_t>(a->ori_kv) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(a->cmp_kv) % 16 == 0 && reinterpret_cast<uintptr_t>(a->attention_out) % 16 == 0,
           "scfa: tensors must be 16-byte aligned");
@@ -224,6 +229,7 @@ int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
   p.b = a->b; p.s1 = 1; p.t_total = a->t; p.nq = a->n_q;
   p.topk = a->topk + a->win_size;  // length of a token's key list
   p.sel_topk = a->topk; p.win_size = a->win_size; p.cmp_ratio = a->cmp_ratio;
+  p.cmp_dense = a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED ? 1 : 0;
   p.block_size = a->block_size;
   p.bs_shift = -1;
   p.max_blocks = a->ori_max_blocks; p.max_blocks2 = a->cmp_max_blocks;

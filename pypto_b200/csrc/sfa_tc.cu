@@ -125,7 +125,8 @@ __global__ void __launch_bounds__(256) sfa_row_ids_kernel(SfaParams p) {
 // Key list of every token for the sparse compress attention: first the window rows (the last
 // min(cur_len, win_size) positions before cur_len = max(seq - s1 + 1 + i, 0), paged by block_table), then the
 // rows of the compressed cache named by the first min(max(seq / cmp_ratio - s1 + 1 + i, 0), sel_topk) entries of
-// the token's index row (paged by block_table2)  (sparse_compress_flash_attention_impl.py:83-131).
+// the token's index row (paged by block_table2)  (sparse_compress_flash_attention_impl.py:83-131) -- or, with
+// cmp_dense, every compressed position below cur_len / cmp_ratio (compress_flash_attention_impl.py:160-186).
 // An entry is row + 1, with bit 31 set for a row of the compressed cache; 0 = no key.
 __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
   const int tok = blockIdx.y;
@@ -147,7 +148,8 @@ __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
     const int seq = __ldg(p.act_seq + bi);
     const int cur_len = max(seq - s1 + 1 + si, 0);
     win = min(cur_len, p.win_size);
-    sel = min(max(seq / p.cmp_ratio - s1 + 1 + si, 0), p.sel_topk);
+    sel = p.cmp_dense ? min(cur_len / p.cmp_ratio, p.sel_topk)
+                      : min(max(seq / p.cmp_ratio - s1 + 1 + si, 0), p.sel_topk);
     if (j < win) {
       const int pos = cur_len - win + j;
       const int lb = pos / p.block_size;
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
         else out = static_cast<int>(row) + 1;
       }
     } else if (j < win + sel) {
-      const int idx = __ldg(p.topk_idx + static_cast<size_t>(tok) * p.sel_topk + (j - win));
+      const int idx = p.cmp_dense ? j - win : __ldg(p.topk_idx + static_cast<size_t>(tok) * p.sel_topk + (j - win));
       if (idx >= 0) {
         const int lb = idx / p.block_size;
         if (lb >= p.max_blocks2) {

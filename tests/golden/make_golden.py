@@ -21,6 +21,10 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
   scfa_small.npz     inputs + output of the DeepSeek-V4 sparse compress attention golden
                      (models/deepseek_v4/test_sparse_compress_flash_attention.py: window keys + selected
                      compressed keys + attention sinks)
+  cfa_small.npz      a query + the output of the DeepSeek-V4 compress flash attention golden (ifa_golden,
+                     models/deepseek_v4/test_compress_flash_attention.py) on the caches of scfa_small.npz
+  win_small.npz      the output of the DeepSeek-V4 sliding-window attention golden (win_atten_calc_tnd,
+                     models/deepseek_v4/test_win_attention.py) on the inputs of scfa_small.npz
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -259,6 +263,76 @@ def make_scfa():
     print("scfa_small: out", tuple(atten_out.shape))
 
 
+def _load_scfa_inputs():
+    z = np.load(os.path.join(HERE, "scfa_small.npz"))
+    bf = lambda a: torch.from_numpy(a).view(torch.bfloat16)  # noqa: E731
+    return z, bf
+
+
+def make_cfa():
+    """compress flash attention: window + every compressed row.  Reuses the caches, page tables and sequence
+    lengths of scfa_small.npz (cmp_ratio 4) with a fresh query of two tokens per request."""
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        import test_compress_flash_attention as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    z, bf = _load_scfa_inputs()
+    b, nq, s1, cmp_ratio = int(z["b"]), int(z["nq"]), 2, int(z["cmp_ratio"])
+    torch.manual_seed(4242)
+    q = torch.empty((b * s1, nq, 512), dtype=torch.bfloat16).uniform_(-1, 1)
+    cmp_kv = bf(z["cmp_kv"]).reshape(-1, 128, 1, 512)
+    ori_kv = bf(z["ori_kv"]).reshape(-1, 128, 1, 512)
+    out = torch.zeros_like(q)
+    ref.ifa_golden(q, cmp_kv, torch.from_numpy(z["atten_sink"]), torch.from_numpy(z["cmp_block_table"]),
+                   torch.from_numpy(z["seqused_kv"]), out, None, enable_flash=False, cmp_ratio=cmp_ratio,
+                   is_new_sink=True, ori_kv=ori_kv, ori_block_table=torch.from_numpy(z["ori_block_table"]))
+    np.savez_compressed(os.path.join(HERE, "cfa_small.npz"), s1=s1, q=bits16(q), out=bits16(out))
+    print("cfa_small: out", tuple(out.shape))
+
+
+class _NpuDeviceAsCpu:
+    """The window-attention golden allocates its result with device='npu:<id>'; while it runs, torch.zeros places
+    such tensors on the CPU instead.  The golden itself is not modified."""
+
+    def __enter__(self):
+        self._zeros = torch.zeros
+
+        def zeros(*args, **kwargs):
+            if str(kwargs.get("device", "")).startswith("npu"):
+                kwargs["device"] = "cpu"
+            return self._zeros(*args, **kwargs)
+
+        torch.zeros = zeros
+        return self
+
+    def __exit__(self, *exc):
+        torch.zeros = self._zeros
+        return False
+
+
+def make_win():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        import test_win_attention as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    z, bf = _load_scfa_inputs()
+    nq, win = int(z["nq"]), int(z["win_size"])
+    seq_q = [int(x) for x in z["actual_seq_q"]]
+    t = seq_q[-1]
+    q = bf(z["q"]).reshape(t, nq, 512)
+    kv_cache = bf(z["ori_kv"]).reshape(-1, 128, 1, 512)
+    params = [t, 1, nq, 512, win, 512 ** -0.5]
+    with _NpuDeviceAsCpu():
+        out = ref.win_atten_calc_tnd(params, [int(x) for x in z["seqused_kv"]], torch.from_numpy(z["atten_sink"]), q,
+                                     kv_cache, torch.from_numpy(z["ori_block_table"]), seq_q, 0)
+    np.savez_compressed(os.path.join(HERE, "win_small.npz"), out=bits16(out))
+    print("win_small: out", tuple(out.shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -283,3 +357,5 @@ if __name__ == "__main__":
     make_prolog()
     make_mla()
     make_scfa()
+    make_cfa()
+    make_win()

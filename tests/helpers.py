@@ -63,6 +63,27 @@ def load_scfa_golden():
         atten_sink=torch.from_numpy(z["atten_sink"]), out=from_bits16(z["out"], bf))
 
 
+def load_cfa_golden():
+    """DeepSeek-V4 compress flash attention fixture: its own query (two tokens per request) and output; caches,
+    page tables, sinks and sequence lengths are those of the sparse compress attention fixture."""
+    g = load_scfa_golden()
+    z = np.load(os.path.join(GOLDEN, "cfa_small.npz"))
+    bf = torch.bfloat16
+    q = from_bits16(z["q"], bf)
+    return dict(g, s1=int(z["s1"]), q=q, out=from_bits16(z["out"], bf),
+                cmp_kv=g["cmp_kv"].reshape(-1, 128, 1, 512), ori_kv=g["ori_kv"].reshape(-1, 128, 1, 512))
+
+
+def load_win_golden():
+    """DeepSeek-V4 sliding-window attention fixture: the inputs of the sparse compress attention fixture (query,
+    un-compressed cache, its page table, sinks, ragged query counts) with the window-only golden output."""
+    g = load_scfa_golden()
+    z = np.load(os.path.join(GOLDEN, "win_small.npz"))
+    t = int(g["actual_seq_q"][-1])
+    return dict(g, q=g["q"].reshape(t, g["nq"], 512), ori_kv=g["ori_kv"].reshape(-1, 128, 1, 512),
+                out=from_bits16(z["out"], torch.bfloat16))
+
+
 def load_sa_antiquant_golden():
     z = np.load(os.path.join(GOLDEN, "sa_antiquant_small.npz"))
     bf = torch.bfloat16

@@ -359,6 +359,120 @@ def test_scfa_bad_arguments_and_bad_pages():
     pypto_b200.check_status()
 
 
+# ---- DeepSeek-V4 compress flash attention (window + every compressed row) and sliding-window attention ---------
+def _run_cfa(d, graph=False):
+    import pypto_b200
+    from pypto_b200 import compress_flash_attention_impl as cfa
+    c = _cuda(d)
+    fn = cfa.cfa_graph if graph else cfa.cfa_attention
+    out = fn(c["q"], c["cmp_kv"], c["atten_sink"], c["cmp_block_table"], c["seqused_kv"], c["ori_kv"],
+             c["ori_block_table"], d["cmp_ratio"])
+    pypto_b200.check_status()
+    assert out.shape == d["q"].shape
+    return out.cpu()
+
+
+def _cfa_oracle(d):
+    return orc.cfa(d["q"], d["cmp_kv"], d["atten_sink"], d["cmp_block_table"], d["seqused_kv"], d["ori_kv"],
+                   d["ori_block_table"], d["cmp_ratio"])
+
+
+def _as_cfa_inputs(d, s1):
+    """Seeded sparse-compress inputs in the 3-D / 4-D layouts of the compress flash attention operator."""
+    t = d["b"] * s1
+    return dict(d, q=d["q"].reshape(t, d["nq"], 512), cmp_kv=d["cmp_kv"].reshape(-1, 128, 1, 512),
+                ori_kv=d["ori_kv"].reshape(-1, 128, 1, 512))
+
+
+def test_cfa_reference_golden_fixture():
+    g = helpers.load_cfa_golden()
+    out = _run_cfa(g)
+    _assert_attention_close(out, g["out"])
+    _assert_attention_close(out, _cfa_oracle(g))
+    assert torch.equal(_run_cfa(g, graph=True), out)
+
+
+@pytest.mark.parametrize("seed,ori_seq,s1,nq,cmp_ratio", [
+    (1, [8192] * 4, 2, 64, 128),          # the reference's decode shape (64 compressed rows), 4 requests
+    (2, [65536, 130, 700, 50], 2, 64, 128),   # 512 compressed rows; a context shorter than the window
+    (3, [3000, 5, 1, 2], 3, 64, 4),       # compression ratio 4: 750 compressed rows; tokens with no key at all
+    (4, [2100, 4000], 1, 128, 4),         # 128 heads
+])
+def test_cfa_seeded_cases(seed, ori_seq, s1, nq, cmp_ratio):
+    d = _as_cfa_inputs(helpers.gen_scfa_inputs(800 + seed, ori_seq, [s1] * len(ori_seq), nq=nq, cmp_ratio=cmp_ratio), s1)
+    out = _run_cfa(d)
+    ref = _cfa_oracle(d)
+    _assert_attention_close(out, ref)
+    assert torch.equal(out.float().abs().sum(-1) == 0, ref.float().abs().sum(-1) == 0)
+
+
+def _run_win(d, graph=False):
+    import pypto_b200
+    from pypto_b200 import win_attention_impl as wa
+    c = _cuda(d)
+    mask = wa.get_mask(4, d["nq"], DEV, 128)
+    fn = wa.sliding_win_atten_graph if graph else wa.deepseekv4_win_atten
+    out = fn(c["q"], c["ori_block_table"], c["ori_kv"], c["seqused_kv"], c["atten_sink"], d["win_size"], mask,
+             c["actual_seq_q"])
+    pypto_b200.check_status()
+    assert out.shape == d["q"].shape
+    return out.cpu()
+
+
+def _win_oracle(d):
+    return orc.win_attention(d["q"], d["ori_block_table"], d["ori_kv"], d["seqused_kv"], d["atten_sink"], d["win_size"],
+                             d["actual_seq_q"])
+
+
+def test_win_attention_reference_golden_fixture():
+    g = helpers.load_win_golden()
+    out = _run_win(g)
+    _assert_attention_close(out, g["out"])
+    _assert_attention_close(out, _win_oracle(g))
+    assert torch.equal(_run_win(g, graph=True), out)
+
+
+@pytest.mark.parametrize("seed,ori_seq,s1_list,nq,win", [
+    (1, [8192] * 4, [2, 2, 2, 2], 64, 128),         # the reference's decode shape, 4 requests
+    (2, [300, 129, 128, 7, 1], [5, 4, 1, 9, 3], 64, 128),   # ragged query counts; windows cut by the start of the context
+    (3, [1000, 40], [2, 1], 128, 300),              # 128 heads; a window over more than two pages
+])
+def test_win_attention_seeded_cases(seed, ori_seq, s1_list, nq, win):
+    d = helpers.gen_scfa_inputs(900 + seed, ori_seq, s1_list, nq=nq, win_size=win)
+    t = int(d["actual_seq_q"][-1])
+    d = dict(d, q=d["q"].reshape(t, nq, 512), ori_kv=d["ori_kv"].reshape(-1, 128, 1, 512))
+    out = _run_win(d)
+    ref = _win_oracle(d)
+    _assert_attention_close(out, ref)
+    assert torch.equal(out.float().abs().sum(-1) == 0, ref.float().abs().sum(-1) == 0)
+
+
+def test_cfa_and_win_attention_bad_arguments():
+    from pypto_b200 import compress_flash_attention_impl as cfa
+    from pypto_b200 import win_attention_impl as wa
+    d = _as_cfa_inputs(helpers.gen_scfa_inputs(990, [600, 300], [2, 2]), 2)
+    c = _cuda(d)
+    args = [c["q"], c["cmp_kv"], c["atten_sink"], c["cmp_block_table"], c["seqused_kv"], c["ori_kv"], c["ori_block_table"]]
+    with pytest.raises(ValueError):
+        cfa.cfa_attention(c["q"].reshape(-1, 512), *args[1:])          # 2-D query
+    with pytest.raises(ValueError):
+        cfa.cfa_attention(args[0], c["cmp_kv"].reshape(-1, 512), *args[2:])   # 2-D cache
+    with pytest.raises(ValueError):
+        cfa.cfa_attention(c["q"][:3].contiguous(), *args[1:])          # tokens not a multiple of the batch
+    with pytest.raises(ValueError):
+        cfa.cfa_attention(*args, cmp_ratio=0)
+    with pytest.raises(ValueError):
+        cfa.cfa_attention(args[0], args[1], c["atten_sink"][:5].contiguous(), *args[3:])
+    with pytest.raises(RuntimeError):
+        cfa.cfa_attention(d["q"], *args[1:])                           # host tensor
+    with pytest.raises(ValueError):
+        wa.deepseekv4_win_atten(c["q"], c["ori_block_table"], c["ori_kv"], c["seqused_kv"], c["atten_sink"], 0, None,
+                                c["actual_seq_q"])
+    with pytest.raises(ValueError):
+        wa.deepseekv4_win_atten(c["q"], c["ori_block_table"], c["ori_kv"], c["seqused_kv"], c["atten_sink"], 128, None,
+                                None)
+
+
 def _run_sa_antiquant(d, cache, entry="d", flat_out=False):
     import pypto_b200
     from pypto_b200 import sparse_attention_antiquant_impl as sa

@@ -51,6 +51,24 @@ def test_scfa_oracle_matches_reference_golden():
     assert not torch.allclose(no_sel.float(), ref.float(), rtol=1e-2, atol=1e-3)
 
 
+def test_cfa_oracle_matches_reference_golden():
+    g = helpers.load_cfa_golden()
+    out = orc.cfa(g["q"], g["cmp_kv"], g["atten_sink"], g["cmp_block_table"], g["seqused_kv"], g["ori_kv"],
+                  g["ori_block_table"], g["cmp_ratio"])
+    assert out.shape == g["out"].shape
+    assert torch.allclose(out.float(), g["out"].float(), rtol=1e-2, atol=1e-3)
+    assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
+
+
+def test_win_attention_oracle_matches_reference_golden():
+    g = helpers.load_win_golden()
+    out = orc.win_attention(g["q"], g["ori_block_table"], g["ori_kv"], g["seqused_kv"], g["atten_sink"], g["win_size"],
+                            g["actual_seq_q"])
+    assert out.shape == g["out"].shape
+    assert torch.allclose(out.float(), g["out"].float(), rtol=1e-2, atol=1e-3)
+    assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
