@@ -254,6 +254,35 @@ size_t dsv32_prolog_workspace_bytes(int32_t t);
 int dsv32_indexer_prolog(const Dsv32PrologArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * DeepSeek-V4 indexer prolog (quant): query path and head weights, no key path.
+ * Replaces quant_lightning_indexer_prolog_kernel / npu_quant_lightning_indexer_prolog
+ * (models/deepseek_v4/lightning_indexer_prolog_quant_v4_impl.py:118-266 / 78-115):
+ *   q = int8 quant per (token, head) of  bf16( [nope | irope(rope)] . hadamard ),
+ *       [nope | rope] = bf16( int32(qr . idx_wq_b) * qr_scale * idx_wq_b_scale ) per head (64 + 64 dims),
+ *       irope = interleaved inverse rotary embedding on the last 64 dims;
+ *   weights = fp16( float(bf16(x . weights_proj)) * 64^-0.5 * 128^-0.5 ).
+ * Fixed sizes: q_lora_rank 1024, 64 heads of 128 dims, rope 64; h (hidden size) is free.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const int8_t* qr;               /* int8 [t, 1024]                       */
+  const int8_t* idx_wq_b;         /* int8 [1024, 8192], row-major         */
+  const void* x;                  /* bf16 [t, h]                          */
+  const void* weights_proj;       /* bf16 [h, 64], row-major              */
+  const void* cos;                /* bf16 [t, 64]                         */
+  const void* sin;                /* bf16 [t, 64]                         */
+  const void* hadamard;           /* bf16 [128, 128]                      */
+  const float* qr_scale;          /* fp32 [t, 1]                          */
+  const float* idx_wq_b_scale;    /* fp32 [8192, 1]                       */
+  int8_t* q;                      /* out int8 [t, 64, 128]                */
+  void* weights;                  /* out fp16 [t, 64]                     */
+  void* q_scale;                  /* out fp16 [t, 64]                     */
+  uint32_t* status;
+  int32_t t, h;
+} Dsv32PrologV4Args;
+
+int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * Fused element-wise stages of the MLA prolog (quant), the MLA half of
  * mla_indexer_prolog_quant_d / _p
  * (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:112-211,486-528; helpers

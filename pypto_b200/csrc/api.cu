@@ -344,6 +344,38 @@ int dsv32_topk_select(const Dsv32TopkArgs* a, void* cuda_stream) {
 }
 
 // ---- indexer prolog -----------------------------------------------------------------------------------
+int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "prolog v4: args is NULL");
+  REQUIRE(a->t >= 0, "prolog v4: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  REQUIRE(a->h >= 1, "prolog v4: bad h=%d", a->h);
+  REQUIRE(a->qr && a->idx_wq_b && a->x && a->weights_proj && a->cos && a->sin && a->hadamard && a->qr_scale &&
+              a->idx_wq_b_scale && a->q && a->weights && a->q_scale,
+          "prolog v4: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->qr) % 16 == 0 && reinterpret_cast<uintptr_t>(a->idx_wq_b) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->hadamard) % 16 == 0 && reinterpret_cast<uintptr_t>(a->q) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->cos) % 4 == 0 && reinterpret_cast<uintptr_t>(a->sin) % 4 == 0,
+          "prolog v4: qr / idx_wq_b / hadamard / q must be 16-byte aligned, cos / sin 4-byte aligned");
+  PrologParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.q_norm = a->qr;
+  p.q_norm_scale = a->qr_scale;
+  p.w_qb = a->idx_wq_b;
+  p.w_qb_scale = a->idx_wq_b_scale;
+  p.w_proj = static_cast<const __nv_bfloat16*>(a->weights_proj);
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos);
+  p.sin = static_cast<const __nv_bfloat16*>(a->sin);
+  p.had_q = static_cast<const __nv_bfloat16*>(a->hadamard);
+  p.q_int8 = a->q;
+  p.q_scale = static_cast<__half*>(a->q_scale);
+  p.weights = static_cast<__half*>(a->weights);
+  p.status = a->status;
+  p.t = a->t;
+  // 64^-0.5 * 128^-0.5 as the reference multiplies it in: (w * 0.125) * 128^-0.5, the first factor being exact
+  const float w_scale = 0.125f * static_cast<float>(1.0 / sqrt(128.0));
+  return launch_prolog_v4(p, a->h, w_scale, static_cast<cudaStream_t>(cuda_stream));
+}
+
 size_t dsv32_prolog_workspace_bytes(int32_t t) { return t > 0 ? align_up(prolog_workspace_bytes(t), 256) : 0; }
 
 int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {

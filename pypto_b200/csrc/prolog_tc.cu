@@ -12,6 +12,12 @@
 //   D[token, 192] = x[token, slice] (bf16) x [wk | w_proj][slice, 192] (bf16, MN-major) -> fp32 partial sums;
 //   the per-token finish kernel (prolog.cu) reduces them in a fixed order and completes the K and W paths.
 // Weights stream through a 4-stage TMA ring exactly once per CTA; no multicast.
+//
+// The Q kernel has a second instantiation for the DeepSeek-V4 indexer prolog
+// (models/deepseek_v4/lightning_indexer_prolog_quant_v4_impl.py:118-266): reduction length 1024 instead of 1536
+// and, in epilogue 1, the rotary embedding on dims 64..127 in its interleaved, inverse form
+// (out[2i] = x[2i] cos[2i] + x[2i+1] sin[2i], out[2i+1] = x[2i+1] cos[2i+1] - x[2i] sin[2i+1]).  That operator has
+// no K path; its head weights come from prolog_v4_weights_kernel.
 #include <mutex>
 
 #include "kernels.cuh"
@@ -29,10 +35,11 @@ constexpr int kPqOffBars = kPqOffWs + 512;
 constexpr int kPqNumBars = 2 * kPqStages + 4;             // full, empty, h_bar, d1_full, r_ready, d2_full
 constexpr int kPqOffTmem = kPqOffBars + kPqNumBars * 8;
 constexpr size_t kPqSmemBytes = kPqOffTmem + 16 + 1024;
-constexpr int kQr = 1536;
+constexpr int kVariantV32 = 0, kVariantV4 = 1;
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+template <int kVariant>
 __global__ void __launch_bounds__(kPqThreads, 1) prolog_q_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
                                                                     const __grid_constant__ CUtensorMap w_map,
                                                                     const __grid_constant__ CUtensorMap h_map,
@@ -54,7 +61,8 @@ __global__ void __launch_bounds__(kPqThreads, 1) prolog_q_tc_kernel(const __grid
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int head = blockIdx.x;
   const int t0 = blockIdx.y * 128;
-  constexpr int kChunks = kQr / 128;  // 12 reduction chunks of 128
+  constexpr int kQr = kVariant == kVariantV4 ? 1024 : 1536;
+  constexpr int kChunks = kQr / 128;  // 12 (8) reduction chunks of 128
 
   if (warp == 0) {
     if (lane == 0) {
@@ -136,6 +144,7 @@ __global__ void __launch_bounds__(kPqThreads, 1) prolog_q_tc_kernel(const __grid
     if (ok) {
       tc_fence_after();
       const float qs = p.q_norm_scale[tk];
+      if constexpr (kVariant == kVariantV32) {
       // ---- dims 0..63: dequantise, round to bf16, RoPE (rotate-half over pairs d, d+32), round to bf16 -------
       uint32_t r0[32], r1[32];
       tmem_ld_32x32b_x32(tmem_base + lane_addr + kColD1, r0);
@@ -189,6 +198,44 @@ __global__ void __launch_bounds__(kPqThreads, 1) prolog_q_tc_kernel(const __grid
                                         __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r1[j + 1])), qs), ws_s[97 + j]));
       }
       tmem_st_32x32b_x32(tmem_base + lane_addr + kColR + 32, pk);
+      } else {
+        // ---- dims 0..63: dequantise and round to bf16 only ---------------------------------------------------
+        uint32_t r0[32], r1[32], pk[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColD1, r0);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColD1 + 32, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          pk[j >> 1] = pack_bf16x2(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r0[j])), qs), ws_s[j]),
+                                   __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r0[j + 1])), qs), ws_s[j + 1]));
+          pk[16 + (j >> 1)] = pack_bf16x2(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r1[j])), qs), ws_s[32 + j]),
+                                          __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r1[j + 1])), qs), ws_s[33 + j]));
+        }
+        tmem_st_32x32b_x32(tmem_base + lane_addr + kColR, pk);
+        // ---- dims 64..127: dequantise, round to bf16, interleaved inverse rotary embedding, round to bf16 ------
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColD1 + 64, r0);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColD1 + 96, r1);
+        tmem_ld_wait();
+        const uint32_t* cosw = reinterpret_cast<const uint32_t*>(p.cos + static_cast<size_t>(tk) * 64);
+        const uint32_t* sinw = reinterpret_cast<const uint32_t*>(p.sin + static_cast<size_t>(tk) * 64);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t* r = half == 0 ? r0 : r1;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {  // rope dims 32*half + j, + j + 1 (head dims 64 + those)
+            const int d = 32 * half + j;
+            const float xe = bf16_round(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), qs), ws_s[64 + d]));
+            const float xo = bf16_round(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j + 1])), qs), ws_s[65 + d]));
+            const uint32_t cw = __ldg(cosw + (d >> 1)), sw = __ldg(sinw + (d >> 1));
+            const float ce = __uint_as_float(cw << 16), co = __uint_as_float(cw & 0xffff0000u);
+            const float se = __uint_as_float(sw << 16), so = __uint_as_float(sw & 0xffff0000u);
+            const float oe = __fadd_rn(__fmul_rn(xe, ce), __fmul_rn(xo, se));
+            const float oo = __fadd_rn(__fmul_rn(xo, co), __fmul_rn(-xe, so));
+            pk[16 * half + (j >> 1)] = pack_bf16x2(oe, oo);
+          }
+        }
+        tmem_st_32x32b_x32(tmem_base + lane_addr + kColR + 32, pk);
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(r_bar);
@@ -393,8 +440,8 @@ int launch_prolog_tc(const PrologParams& p, cudaStream_t stream) {
   if (p.t <= 0) return DSV32_OK;
   const int tiles = (p.t + 127) / 128;
   CUtensorMap qn_map, w_map, h_map, x_map, wk_map, wp_map;
-  int rc = make_tensor_map_2d_u8(&qn_map, p.q_norm, p.t, kQr, 128, 128);
-  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&w_map, p.w_qb, kQr, 8192, 128, 128);
+  int rc = make_tensor_map_2d_u8(&qn_map, p.q_norm, p.t, 1536, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&w_map, p.w_qb, 1536, 8192, 128, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&h_map, p.had_q, 128, 256, 128, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&x_map, p.x, p.t, 7168 * 2, 128, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wk_map, p.wk, 7168, 256, 64, 128);
@@ -410,8 +457,8 @@ int launch_prolog_tc(const PrologParams& p, cudaStream_t stream) {
       fk = nullptr;
     }
   }
-  cudaFuncSetAttribute(prolog_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPqSmemBytes);
-  prolog_q_tc_kernel<<<dim3(64, tiles), kPqThreads, kPqSmemBytes, q_stream>>>(qn_map, w_map, h_map, p);
+  cudaFuncSetAttribute(prolog_q_tc_kernel<kVariantV32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPqSmemBytes);
+  prolog_q_tc_kernel<kVariantV32><<<dim3(64, tiles), kPqThreads, kPqSmemBytes, q_stream>>>(qn_map, w_map, h_map, p);
   count_launch();
   rc = check_launch("prolog_q_tc_kernel");
   if (fk != nullptr && cudaEventRecord(fk->join, fk->side) != cudaSuccess) rc = check_launch("prolog side stream");
@@ -425,6 +472,79 @@ int launch_prolog_tc(const PrologParams& p, cudaStream_t stream) {
     if (rc == DSV32_OK) rc = launch_prolog_finish(p, splits, stream);
   }
   // always join, also after an error above: the caller's stream must not run ahead of the side stream
+  if (fk != nullptr && cudaStreamWaitEvent(stream, fk->join, 0) != cudaSuccess && rc == DSV32_OK)
+    rc = check_launch("prolog side stream join");
+  return rc;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// DeepSeek-V4 indexer prolog: head weights = fp16( float(bf16(x . w_proj)) * scale )
+// (lightning_indexer_prolog_quant_v4_impl.py:253-266).  One CTA per token; thread (k slice, head) walks its slice
+// of the reduction with the weight row read coalesced (64 heads = 128 bytes), the four slices are summed in a
+// fixed order.  w_proj (h x 64 bf16, 512 KB at h = 4096) stays in L2 across the CTAs.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prolog_v4_weights_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ w_proj,
+                                                                __half* __restrict__ weights, int h, float scale) {
+  extern __shared__ float xs[];  // h floats, then 4 x 64 partial sums
+  float* part = xs + h;
+  const int tok = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* xrow = x + static_cast<size_t>(tok) * h;
+  for (int k = tid; k < h; k += 256) xs[k] = __bfloat162float(xrow[k]);
+  __syncthreads();
+  const int n = tid & 63, slice = tid >> 6;
+  const int per = (h + 3) / 4;
+  const int k0 = slice * per, k1 = min(h, k0 + per);
+  float acc0 = 0.f, acc1 = 0.f;
+  int k = k0;
+  for (; k + 1 < k1; k += 2) {
+    acc0 = fmaf(xs[k], __bfloat162float(w_proj[static_cast<size_t>(k) * 64 + n]), acc0);
+    acc1 = fmaf(xs[k + 1], __bfloat162float(w_proj[static_cast<size_t>(k + 1) * 64 + n]), acc1);
+  }
+  if (k < k1) acc0 = fmaf(xs[k], __bfloat162float(w_proj[static_cast<size_t>(k) * 64 + n]), acc0);
+  part[slice * 64 + n] = acc0 + acc1;
+  __syncthreads();
+  if (tid < 64) {
+    const float sum = (part[tid] + part[64 + tid]) + (part[128 + tid] + part[192 + tid]);
+    weights[static_cast<size_t>(tok) * 64 + tid] = __float2half_rn(__fmul_rn(bf16_round(sum), scale));
+  }
+}
+
+int launch_prolog_v4(const PrologParams& p, int h, float w_scale, cudaStream_t stream) {
+  if (p.t <= 0) return DSV32_OK;
+  const int tiles = (p.t + 127) / 128;
+  CUtensorMap qn_map, w_map, h_map;
+  int rc = make_tensor_map_2d_u8(&qn_map, p.q_norm, p.t, 1024, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&w_map, p.w_qb, 1024, 8192, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&h_map, p.had_q, 128, 256, 128, 128);
+  if (rc != DSV32_OK) return rc;
+  const size_t w_smem = (static_cast<size_t>(h) + 256) * sizeof(float);
+  if (w_smem > 200 * 1024) {
+    set_error("prolog v4: hidden size %d does not fit the weights kernel's shared memory", h);
+    return DSV32_ERR_UNSUPPORTED;
+  }
+  // the Q path and the weights path are independent: fork the weights kernel onto the side stream
+  PrologFork* fk = prolog_fork_for_device();
+  cudaStream_t w_stream = stream;
+  if (fk != nullptr) {
+    if (cudaEventRecord(fk->fork, stream) == cudaSuccess && cudaStreamWaitEvent(fk->side, fk->fork, 0) == cudaSuccess) {
+      w_stream = fk->side;
+    } else {
+      (void)cudaGetLastError();
+      fk = nullptr;
+    }
+  }
+  cudaFuncSetAttribute(prolog_v4_weights_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w_smem);
+  prolog_v4_weights_kernel<<<p.t, 256, w_smem, w_stream>>>(p.x, p.w_proj, p.weights, h, w_scale);
+  count_launch();
+  rc = check_launch("prolog_v4_weights_kernel");
+  if (fk != nullptr && cudaEventRecord(fk->join, fk->side) != cudaSuccess) rc = check_launch("prolog side stream");
+  if (rc == DSV32_OK) {
+    cudaFuncSetAttribute(prolog_q_tc_kernel<kVariantV4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPqSmemBytes);
+    prolog_q_tc_kernel<kVariantV4><<<dim3(64, tiles), kPqThreads, kPqSmemBytes, stream>>>(qn_map, w_map, h_map, p);
+    count_launch();
+    rc = check_launch("prolog_q_tc_kernel (v4)");
+  }
   if (fk != nullptr && cudaStreamWaitEvent(stream, fk->join, 0) != cudaSuccess && rc == DSV32_OK)
     rc = check_launch("prolog side stream join");
   return rc;

@@ -25,6 +25,8 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
                      models/deepseek_v4/test_compress_flash_attention.py) on the caches of scfa_small.npz
   win_small.npz      the output of the DeepSeek-V4 sliding-window attention golden (win_atten_calc_tnd,
                      models/deepseek_v4/test_win_attention.py) on the inputs of scfa_small.npz
+  prolog_v4_small.npz  token count + input digests + outputs of the DeepSeek-V4 indexer prolog golden
+                     (compute_quant_lightning_indexer_prolog, models/deepseek_v4/test_lightning_indexer_prolog_quant_v4.py)
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -333,6 +335,45 @@ def make_win():
     print("win_small: out", tuple(out.shape))
 
 
+class _TolerateNpuDispatchKey:
+    """Some reference operator files register a torch.library implementation for the dispatch key "NPU" at import
+    time without guarding it; this torch build has no such key.  While such a file is imported, a registration
+    for that key is skipped (the decorated function is returned as it is); nothing else changes."""
+
+    def __enter__(self):
+        self._impl = torch.library.impl
+
+        def impl(lib, name, dispatch_key=""):
+            if dispatch_key == "NPU":
+                return lambda fn: fn
+            return self._impl(lib, name, dispatch_key)
+
+        torch.library.impl = impl
+        return self
+
+    def __exit__(self, *exc):
+        torch.library.impl = self._impl
+        return False
+
+
+def make_prolog_v4():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        with _TolerateNpuDispatchKey():
+            import test_lightning_indexer_prolog_quant_v4 as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    t = 37
+    params = {"t": t, "idx_nq": 64, "head_dim": 128, "rope_dim": 64, "q_lora_rank": 1024, "h": 4096}
+    inputs, q, weights, q_scale = ref.gen_quant_attention_post_golden(params)   # seeds torch with 42 itself
+    names = ["qr", "idx_wq_b", "x", "weights_proj", "cos", "sin", "hadamard", "qr_scale", "idx_wq_b_scale"]
+    digests = {n: digest(v) for n, v in zip(names, inputs)}
+    np.savez_compressed(os.path.join(HERE, "prolog_v4_small.npz"), t=t, digests=json.dumps(digests),
+                        q=q.reshape(t, 64, 128).numpy(), weights=bits16(weights), q_scale=bits16(q_scale))
+    print("prolog_v4_small: q", tuple(q.shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -359,3 +400,4 @@ if __name__ == "__main__":
     make_scfa()
     make_cfa()
     make_win()
+    make_prolog_v4()

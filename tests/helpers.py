@@ -213,6 +213,59 @@ def gen_sfa_inputs(seed, act_seq, s1=1, nq=128, topk=2048, block_size=128, pad_s
                 softmax_scale=576 ** -0.5, topk=topk, block_size=block_size)
 
 
+def load_prolog_v4_golden():
+    z = np.load(os.path.join(GOLDEN, "prolog_v4_small.npz"))
+    return dict(t=int(z["t"]), digests=json.loads(str(z["digests"])), q=torch.from_numpy(z["q"]),
+                weights=from_bits16(z["weights"], torch.float16), q_scale=from_bits16(z["q_scale"], torch.float16))
+
+
+def prolog_v4_reference_inputs(t):
+    """Same RNG call order and arithmetic as the reference generator of the DeepSeek-V4 indexer prolog test
+    (models/deepseek_v4/test_lightning_indexer_prolog_quant_v4.py:77-110 with gen_uniform_data and quant_golden of
+    utils/golden/common_func.py:16-35,72-82), so the tensors reproduce the digests stored in prolog_v4_small.npz."""
+    torch.manual_seed(42)
+    bf = torch.bfloat16
+
+    def uni(shape, lo, hi, dtype):
+        if dtype == torch.int8:
+            return torch.randint(low=lo, high=hi, size=shape, dtype=dtype)
+        return lo + (hi - lo) * torch.rand(shape, dtype=dtype)
+
+    def quant(x):
+        xf = x.to(torch.float32)
+        s = 127.0 / torch.amax(torch.abs(xf), dim=-1, keepdim=True)
+        y = torch.round(xf * s).to(torch.int32)
+        return torch.trunc(y.to(x.dtype)).to(torch.int8), 1.0 / s
+
+    qr_ori = uni([t, 1024], -1, 1, torch.int8)
+    wq_ori = uni([1024, 8192], -1, 1, torch.int8)
+    x = uni([t, 4096], -1, 1, bf)
+    weights_proj = uni([4096, 64], -0.1, 0.1, bf)
+    cos = uni([t, 64], -1, 1, bf)
+    sin = uni([t, 64], -1, 1, bf)
+    hadamard = uni([128, 128], -1, 1, bf)
+    qr, qr_scale = quant(qr_ori)
+    wq, wq_scale = quant(wq_ori.t())
+    return dict(qr=qr, idx_wq_b=wq.t().contiguous(), x=x, weights_proj=weights_proj, cos=cos, sin=sin, hadamard=hadamard,
+                qr_scale=qr_scale, idx_wq_b_scale=wq_scale)
+
+
+def gen_prolog_v4_inputs(seed, t, h=4096):
+    """Seeded full-range inputs of the DeepSeek-V4 indexer prolog (the reference generator only produces the int8
+    values -127 and 0): uniform int8 operands, scales of realistic size, unit-circle cos / sin, a random hadamard."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    ang = torch.rand((t, 64), generator=g) * 2 * torch.pi
+    return dict(
+        qr=torch.randint(-127, 128, (t, 1024), generator=g, dtype=torch.int8),
+        idx_wq_b=torch.randint(-127, 128, (1024, 8192), generator=g, dtype=torch.int8),
+        x=torch.randn((t, h), generator=g).to(bf), weights_proj=(torch.randn((h, 64), generator=g) * 0.02).to(bf),
+        cos=torch.cos(ang).to(bf), sin=torch.sin(ang).to(bf),
+        hadamard=(torch.rand((128, 128), generator=g) * 2 - 1).to(bf),
+        qr_scale=torch.rand((t, 1), generator=g) * 0.02 + 0.001,
+        idx_wq_b_scale=torch.rand((8192, 1), generator=g) * 0.002 + 0.0001)
+
+
 def gen_scfa_inputs(seed, ori_seq, s1_list, nq=64, topk=512, win_size=128, cmp_ratio=4, block_size=128, holes=0,
                     scale=1.0):
     """Seeded synthetic inputs of the DeepSeek-V4 sparse compress attention in the operator's layouts: queries,

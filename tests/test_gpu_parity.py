@@ -701,6 +701,85 @@ def test_prolog_config1_distributions_vs_oracle(t):
 
 
 # --------------------------------------------------------------------------------------------------
+# DeepSeek-V4 indexer prolog (query path + head weights)
+# --------------------------------------------------------------------------------------------------
+def _run_prolog_v4(inp, entry="npu"):
+    import pypto_b200
+    from pypto_b200 import lightning_indexer_prolog_quant_v4_impl as pv4
+    c = _cuda(inp)
+    args = [c[k] for k in ("qr", "idx_wq_b", "x", "weights_proj", "cos", "sin", "hadamard", "qr_scale", "idx_wq_b_scale")]
+    if entry == "npu":
+        q, w, qs = pv4.npu_quant_lightning_indexer_prolog(*args)
+    else:
+        t = inp["qr"].shape[0]
+        q = torch.zeros((t, 64 * 128), dtype=torch.int8, device=DEV)      # the operator's table lists q as 2-D
+        w = torch.zeros((t, 64), dtype=torch.float16, device=DEV)
+        qs = torch.zeros((t, 64), dtype=torch.float16, device=DEV)
+        assert pv4.quant_lightning_indexer_prolog_kernel(*args, q, w, qs, pv4.IndexerPrologQuantConfig()) is None
+        q = q.reshape(t, 64, 128)
+    pypto_b200.check_status()
+    return q.cpu(), w.cpu(), qs.cpu()
+
+
+def _assert_prolog_v4_close(got, ref):
+    q, w, qs = got
+    rq, rw, rqs = ref
+    assert (q.int() - rq.int()).abs().max() <= 1
+    assert (q != rq).float().mean() < 0.02
+    # the reference's own tolerances (test_lightning_indexer_prolog_quant_v4.py:158-160)
+    assert torch.allclose(w.float(), rw.float(), atol=1e-4, rtol=0.007825)
+    assert torch.allclose(qs.float(), rqs.float(), atol=1e-4, rtol=0.007825)
+
+
+def test_prolog_v4_reference_golden_fixture():
+    g = helpers.load_prolog_v4_golden()
+    inp = helpers.prolog_v4_reference_inputs(g["t"])
+    got = _run_prolog_v4(inp)
+    _assert_prolog_v4_close(got, (g["q"], g["weights"], g["q_scale"]))
+    again = _run_prolog_v4(inp, entry="kernel")
+    assert all(torch.equal(a, b) for a, b in zip(got, again))
+
+
+@pytest.mark.parametrize("t,h", [(1, 4096), (37, 4096), (128, 4096), (200, 4096), (16, 7168), (5, 1000)])
+def test_prolog_v4_seeded_vs_oracle(t, h):
+    inp = helpers.gen_prolog_v4_inputs(1100 + t, t, h)
+    got = _run_prolog_v4(inp)
+    ref = orc.indexer_prolog_v4(**inp)
+    _assert_prolog_v4_close(got, ref)
+    # the int32 products are exact and the order of the roundings is the reference's: expect (near) bit equality
+    assert (got[0] != ref[0]).float().mean() < 2e-3
+    assert (got[2] != ref[2]).float().mean() < 2e-3
+
+
+def test_prolog_v4_bad_arguments():
+    from pypto_b200 import lightning_indexer_prolog_quant_v4_impl as pv4
+    inp = helpers.gen_prolog_v4_inputs(1, 4)
+    c = _cuda(inp)
+    order = ("qr", "idx_wq_b", "x", "weights_proj", "cos", "sin", "hadamard", "qr_scale", "idx_wq_b_scale")
+
+    def call(**over):
+        a = dict(c, **over)
+        return pv4.npu_quant_lightning_indexer_prolog(*[a[k] for k in order])
+
+    with pytest.raises(ValueError):
+        call(qr=c["qr"][:, :512].contiguous())
+    with pytest.raises(ValueError):
+        call(idx_wq_b=c["idx_wq_b"].to(torch.int32))
+    with pytest.raises(ValueError):
+        call(x=c["x"][:3].contiguous())
+    with pytest.raises(ValueError):
+        call(weights_proj=c["weights_proj"][:100].contiguous())
+    with pytest.raises(ValueError):
+        call(cos=c["cos"].float())
+    with pytest.raises(ValueError):
+        call(idx_wq_b_scale=c["idx_wq_b_scale"].reshape(-1))
+    with pytest.raises(RuntimeError):
+        call(hadamard=inp["hadamard"])
+    call()
+
+
+# --------------------------------------------------------------------------------------------------
+# --------------------------------------------------------------------------------------------------
 # fused MLA prolog + indexer prolog
 # --------------------------------------------------------------------------------------------------
 def _run_mla(inp, ip):

@@ -69,6 +69,24 @@ def test_win_attention_oracle_matches_reference_golden():
     assert orc.reference_compare_count(out, g["out"], 1e-4, 5e-3) <= 0.005 * out.numel()
 
 
+def test_prolog_v4_oracle_matches_reference_golden():
+    g = helpers.load_prolog_v4_golden()
+    inp = helpers.prolog_v4_reference_inputs(g["t"])
+    for name, tensor in inp.items():
+        assert helpers.digest(tensor) == g["digests"][name], f"regenerated input {name} differs from the reference's"
+    q, w, qs = orc.indexer_prolog_v4(**inp)
+    assert (q.int() - g["q"].int()).abs().max() <= 1 and (q != g["q"]).float().mean() < 0.01
+    assert torch.allclose(w.float(), g["weights"].float(), atol=1e-4, rtol=0.007825)
+    assert torch.allclose(qs.float(), g["q_scale"].float(), atol=1e-4, rtol=0.007825)
+    # the interleaved inverse rotation undoes the forward one: x -> rope -> inverse rope == x (up to bf16 rounding)
+    x = torch.randn(3, 5, 64).to(torch.bfloat16)
+    ang = torch.rand(3, 64 // 2) * 6.28
+    cos = torch.cos(ang).repeat_interleave(2, -1).to(torch.bfloat16)
+    sin = torch.sin(ang).repeat_interleave(2, -1).to(torch.bfloat16)
+    fwd = orc.rope_interleaved_inverse(x, cos, -sin)
+    assert torch.allclose(orc.rope_interleaved_inverse(fwd, cos, sin).float(), x.float(), atol=0.05)
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
