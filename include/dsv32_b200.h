@@ -319,6 +319,35 @@ typedef struct {
 
 int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* args, int32_t stage, void* cuda_stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Fused element-wise stages of the DeepSeek-V4 MLA prolog (quant), between its three
+ * library GEMMs.  Replaces the vector work of mla_prolog_v4 / mla_prolog_v4_in
+ * (models/deepseek_v4/mla_prolog_quant_v4_impl.py:406-517 / 567-629):
+ *   stage 0: q_a = x.wq_a (fp32) -> RMSNorm * gamma_cq -> per-token int8 quant -> qr, qr_scale
+ *   stage 1: q_b = qr.wq_b (int32) -> * qr_scale * wq_b_scale -> per-head RMSNorm (no weight)
+ *            -> bf16 -> interleaved rotary embedding on the last 64 of 512 dims -> q
+ *   stage 2: kv_a = x.wkv (fp32) -> RMSNorm * gamma_ckv -> bf16 -> rotary on the last 64 -> kv
+ * Fixed sizes: q_lora_rank 1024, head_dim 512, rope 64; the head count is free.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const float* q_a;               /* stage 0: fp32 [t, 1024]                         */
+  const void* gamma_cq;           /* bf16 [1024]                                     */
+  int8_t* qr;                     /* stage 0 out: int8 [t, 1024]                     */
+  float* qr_scale;                /* stage 0 out / stage 1 in: fp32 [t]              */
+  const int32_t* q_b;             /* stage 1: int32 [t, q_b_ld], first heads*512 columns */
+  const float* wq_b_scale;        /* fp32 [heads*512]                                */
+  void* q_out;                    /* stage 1 out: bf16 [t, heads, 512]               */
+  const float* kv_a;              /* stage 2: fp32 [t, 512]                          */
+  const void* gamma_ckv;          /* bf16 [512]                                      */
+  void* kv_out;                   /* stage 2 out: bf16 [t, 512]                      */
+  const void* cos;                /* bf16 [t, 64]                                    */
+  const void* sin;                /* bf16 [t, 64]                                    */
+  int32_t t, heads, q_b_ld;
+  float eps;
+} Dsv32MlaV4StageArgs;
+
+int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* args, int32_t stage, void* cuda_stream);
+
 /* library-wide */
 int dsv32_abi_version(void);
 const char* dsv32_last_error(void);

@@ -46,6 +46,14 @@ class ScfaArgs(C.Structure):
     ]
 
 
+class MlaV4StageArgs(C.Structure):
+    _fields_ = [
+        ("q_a", c_void_p), ("gamma_cq", c_void_p), ("qr", c_void_p), ("qr_scale", c_void_p), ("q_b", c_void_p),
+        ("wq_b_scale", c_void_p), ("q_out", c_void_p), ("kv_a", c_void_p), ("gamma_ckv", c_void_p), ("kv_out", c_void_p),
+        ("cos", c_void_p), ("sin", c_void_p), ("t", c_i32), ("heads", c_i32), ("q_b_ld", c_i32), ("eps", c_float),
+    ]
+
+
 class PrologV4Args(C.Structure):
     _fields_ = [
         ("qr", c_void_p), ("idx_wq_b", c_void_p), ("x", c_void_p), ("weights_proj", c_void_p), ("cos", c_void_p),
@@ -109,6 +117,7 @@ EXPORTS = {
     "dsv32_indexer_topk_noalloc": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_indexer_prolog_v4": (c_i32, [C.POINTER(PrologV4Args), c_void_p]),
+    "dsv32_mla_prolog_v4_stage": (c_i32, [C.POINTER(MlaV4StageArgs), c_i32, c_void_p]),
     "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_indexer_prolog": (c_i32, [C.POINTER(PrologArgs), c_void_p]),
     "dsv32_mla_prolog_stage": (c_i32, [C.POINTER(MlaStageArgs), c_i32, c_void_p]),

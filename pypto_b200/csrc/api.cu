@@ -472,4 +472,33 @@ int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* a, int32_t stage, void* cuda
   return launch_mla_stage(p, stage, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* a, int32_t stage, void* cuda_stream) {
+  REQUIRE(a != nullptr, "mla v4: args is NULL");
+  REQUIRE(stage >= 0 && stage <= 2, "mla v4: stage=%d must be 0, 1 or 2", stage);
+  REQUIRE(a->t >= 0, "mla v4: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  if (stage == 0) REQUIRE(a->q_a && a->gamma_cq && a->qr && a->qr_scale, "mla v4 stage 0: NULL tensor pointer");
+  if (stage == 1)
+    REQUIRE(a->q_b && a->qr_scale && a->wq_b_scale && a->q_out && a->cos && a->sin && a->heads >= 1 &&
+                a->heads <= 65535 && a->q_b_ld >= a->heads * 512,
+            "mla v4 stage 1: NULL tensor pointer, bad heads=%d or q_b_ld=%d too small", a->heads, a->q_b_ld);
+  if (stage == 2) REQUIRE(a->kv_a && a->gamma_ckv && a->kv_out && a->cos && a->sin, "mla v4 stage 2: NULL tensor pointer");
+  MlaV4StageParams p{};
+  p.q_a = a->q_a;
+  p.gamma_cq = static_cast<const __nv_bfloat16*>(a->gamma_cq);
+  p.qr = a->qr;
+  p.qr_scale = a->qr_scale;
+  p.q_b = a->q_b;
+  p.wq_b_scale = a->wq_b_scale;
+  p.q_out = static_cast<__nv_bfloat16*>(a->q_out);
+  p.kv_a = a->kv_a;
+  p.gamma_ckv = static_cast<const __nv_bfloat16*>(a->gamma_ckv);
+  p.kv_out = static_cast<__nv_bfloat16*>(a->kv_out);
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos);
+  p.sin = static_cast<const __nv_bfloat16*>(a->sin);
+  p.t = a->t; p.heads = a->heads; p.q_b_ld = a->q_b_ld;
+  p.eps = a->eps;
+  return launch_mla_v4_stage(p, stage, static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

@@ -27,6 +27,8 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
                      models/deepseek_v4/test_win_attention.py) on the inputs of scfa_small.npz
   prolog_v4_small.npz  token count + input digests + outputs of the DeepSeek-V4 indexer prolog golden
                      (compute_quant_lightning_indexer_prolog, models/deepseek_v4/test_lightning_indexer_prolog_quant_v4.py)
+  mla_v4_small.npz   token count + input digests + outputs of the DeepSeek-V4 MLA prolog golden
+                     (mla_prolog_compute, models/deepseek_v4/test_mla_prolog_quant_v4.py)
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -374,6 +376,26 @@ def make_prolog_v4():
     print("prolog_v4_small: q", tuple(q.shape))
 
 
+def make_mla_v4():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        with _TolerateNpuDispatchKey():
+            import test_mla_prolog_quant_v4 as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    t = 5
+    params = {"t": t, "num_heads": 64, "h": 4096, "q_lora_rank": 1024, "head_dim": 512, "qk_rope_head_dim": 64}
+    torch.manual_seed(5)   # the reference module seeds with 5 when it is imported; repeated here for a fixed start
+    inputs, outputs = ref.gen_mla_prolog_data(params, torch.bfloat16, True, False)
+    names = ["x", "wq_a", "wq_b", "w_kv", "cos", "sin", "gamma_cq", "gamma_ckv", "wq_b_scale"]
+    digests = {n: digest(inputs[n]) for n in names}
+    np.savez_compressed(os.path.join(HERE, "mla_v4_small.npz"), t=t, digests=json.dumps(digests),
+                        q=bits16(outputs["q_golden"]), kv=bits16(outputs["kv_golden"]),
+                        qr=outputs["qr_golden"].numpy(), qr_scale=outputs["qr_scale_golden"].numpy())
+    print("mla_v4_small: q", tuple(outputs["q_golden"].shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -401,3 +423,4 @@ if __name__ == "__main__":
     make_cfa()
     make_win()
     make_prolog_v4()
+    make_mla_v4()

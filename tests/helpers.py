@@ -266,6 +266,50 @@ def gen_prolog_v4_inputs(seed, t, h=4096):
         idx_wq_b_scale=torch.rand((8192, 1), generator=g) * 0.002 + 0.0001)
 
 
+def load_mla_v4_golden():
+    z = np.load(os.path.join(GOLDEN, "mla_v4_small.npz"))
+    bf = torch.bfloat16
+    return dict(t=int(z["t"]), digests=json.loads(str(z["digests"])), q=from_bits16(z["q"], bf),
+                kv=from_bits16(z["kv"], bf), qr=torch.from_numpy(z["qr"]), qr_scale=torch.from_numpy(z["qr_scale"]))
+
+
+def mla_v4_reference_inputs(t, heads=64, h=4096):
+    """Same RNG call order as the reference generator of the DeepSeek-V4 MLA prolog test
+    (models/deepseek_v4/test_mla_prolog_quant_v4.py:192-233, seed 5), so the tensors reproduce the digests stored in
+    mla_v4_small.npz."""
+    torch.manual_seed(5)
+    bf = torch.bfloat16
+    x = torch.empty([t, h], dtype=bf).uniform_(-1, 1)
+    wq_a = torch.empty([h, 1024], dtype=bf).uniform_(-0.1, 0.1)
+    wq_b = torch.empty([1024, heads * 512], dtype=bf).uniform_(-0.1, 0.1)
+    w_kv = torch.empty([h, 512], dtype=bf).uniform_(-0.1, 0.1)
+    wf = wq_b.to(torch.float32)                       # per-column int8 quantisation of wq_b
+    s = 127 / torch.max(torch.abs(wf), dim=-2, keepdim=True)[0]
+    wq_b_i8 = torch.trunc(torch.round(wf * s).to(torch.int32).to(torch.float16)).to(torch.int8)
+    gamma_cq = torch.empty([1024], dtype=bf).uniform_(-1, 1)
+    gamma_ckv = torch.empty([512], dtype=bf).uniform_(-1, 1)
+    cos = torch.empty([t, 64], dtype=bf).uniform_(-1, 1)
+    sin = torch.empty([t, 64], dtype=bf).uniform_(-1, 1)
+    return dict(x=x, wq_a=wq_a, wq_b=wq_b_i8, w_kv=w_kv, cos=cos, sin=sin, gamma_cq=gamma_cq, gamma_ckv=gamma_ckv,
+                wq_b_scale=1 / s)
+
+
+def gen_mla_v4_inputs(seed, t, heads=64, h=4096):
+    """Seeded inputs of the DeepSeek-V4 MLA prolog with realistic distributions: normal activations and weights,
+    gamma near one, unit-circle cos / sin repeated per rotary pair."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    wq = torch.randn((1024, heads * 512), generator=g) * 0.03
+    s = 127 / wq.abs().amax(0, keepdim=True)
+    ang = torch.rand((t, 32), generator=g) * 2 * torch.pi
+    return dict(
+        x=torch.randn((t, h), generator=g).to(bf), wq_a=(torch.randn((h, 1024), generator=g) * 0.02).to(bf),
+        wq_b=torch.round(wq * s).to(torch.int8), w_kv=(torch.randn((h, 512), generator=g) * 0.02).to(bf),
+        cos=torch.cos(ang).repeat_interleave(2, -1).to(bf), sin=torch.sin(ang).repeat_interleave(2, -1).to(bf),
+        gamma_cq=(1 + 0.1 * torch.randn(1024, generator=g)).to(bf),
+        gamma_ckv=(1 + 0.1 * torch.randn(512, generator=g)).to(bf), wq_b_scale=(1 / s).float())
+
+
 def gen_scfa_inputs(seed, ori_seq, s1_list, nq=64, topk=512, win_size=128, cmp_ratio=4, block_size=128, holes=0,
                     scale=1.0):
     """Seeded synthetic inputs of the DeepSeek-V4 sparse compress attention in the operator's layouts: queries,

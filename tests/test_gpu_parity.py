@@ -780,6 +780,109 @@ def test_prolog_v4_bad_arguments():
 
 # --------------------------------------------------------------------------------------------------
 # --------------------------------------------------------------------------------------------------
+# DeepSeek-V4 MLA prolog (q / kv / qr) and its hand-over to the V4 indexer prolog
+# --------------------------------------------------------------------------------------------------
+def _run_mla_v4(inp, entry="in"):
+    import pypto_b200
+    from pypto_b200 import mla_prolog_quant_v4_impl as m4
+    c = _cuda(inp)
+    if entry == "in":
+        out = m4.mla_prolog_v4_in(c["x"], c["wq_a"], c["wq_b"], c["w_kv"], c["cos"], c["sin"], c["gamma_cq"],
+                                  c["gamma_ckv"], c["wq_b_scale"])
+    else:
+        t, heads = inp["x"].shape[0], inp["wq_b"].shape[1] // 512
+        q = torch.zeros((t, heads, 512), dtype=torch.bfloat16, device=DEV)
+        kv = torch.zeros((t, 512), dtype=torch.bfloat16, device=DEV)
+        qr = torch.zeros((t, 1024), dtype=torch.int8, device=DEV)
+        qs = torch.zeros((t, 1), dtype=torch.float32, device=DEV)
+        assert m4.mla_prolog_v4(c["x"], c["wq_a"], c["wq_b"], c["w_kv"], c["gamma_cq"], c["gamma_ckv"], c["cos"], c["sin"],
+                                c["wq_b_scale"], q, kv, qr, qs, m4.MlaPrologV4Attrs(eps=1e-6), m4.MlaPrologV4Configs(),
+                                m4.MlaTileConfigs()) is None
+        out = (q, kv, qr, qs)
+    pypto_b200.check_status()
+    return tuple(o.cpu() for o in out)
+
+
+def _mla_v4_oracle(inp, qr_override=None):
+    return orc.mla_prolog_v4(inp["x"], inp["wq_a"], inp["wq_b"], inp["w_kv"], inp["gamma_cq"], inp["gamma_ckv"],
+                             inp["cos"], inp["sin"], inp["wq_b_scale"])
+
+
+def _assert_mla_v4_close(got, ref, inp):
+    q, kv, qr, qs = got
+    rq, rkv, rqr, rqs = ref
+    # the reference's own tolerances (test_mla_prolog_quant_v4.py:344-350): q / kv atol 1e-4 rtol 2^-7 with 0.5 % of
+    # the elements allowed outside, qr within one step, qr_scale atol 2.5e-5 rtol 5e-3
+    assert (qr.int() - rqr.int()).abs().max() <= 1
+    assert (qr != rqr).float().mean() < 0.02
+    assert torch.allclose(qs, rqs, atol=2.5e-5, rtol=0.005)
+    assert torch.allclose(kv.float(), rkv.float(), atol=1e-4, rtol=0.0078125) or \
+        orc.reference_compare_count(kv, rkv, 1e-4, 0.0078125) <= 0.005 * kv.numel()
+    # q depends on qr: where the library GEMM's summation order flips a last bit of qr, q moves by up to the weight
+    # of one quantisation step; judge q against the oracle run on the device's own qr (tight), and against the
+    # reference value with the reference's outlier allowance
+    x, heads = inp["x"], inp["wq_b"].shape[1] // 512
+    q_b = torch.matmul(qr.to(torch.int32), inp["wq_b"].to(torch.int32)).to(torch.float32) * qs
+    q_b = (q_b * inp["wq_b_scale"].reshape(1, -1)).reshape(x.shape[0], heads, 512)
+    qn = (q_b / torch.sqrt((q_b * q_b * (1.0 / 512)).sum(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    q_own = torch.cat([qn[:, :, :-64], orc.rope_interleaved_inverse(qn[:, :, -64:], inp["cos"], -inp["sin"])], dim=-1)
+    assert orc.reference_compare_count(q, q_own, 1e-4, 0.0078125) <= 0.001 * q.numel()
+    assert orc.reference_compare_count(q, rq, 1e-4, 0.0078125) <= 0.02 * q.numel()
+
+
+def test_mla_v4_reference_golden_fixture():
+    g = helpers.load_mla_v4_golden()
+    inp = helpers.mla_v4_reference_inputs(g["t"])
+    got = _run_mla_v4(inp)
+    _assert_mla_v4_close(got, (g["q"], g["kv"], g["qr"], g["qr_scale"]), inp)
+    again = _run_mla_v4(inp, entry="kernel")
+    assert all(torch.equal(a, b) for a, b in zip(got, again))
+
+
+@pytest.mark.parametrize("t,heads,h", [(1, 64, 4096), (37, 64, 4096), (128, 64, 4096), (20, 8, 1024)])
+def test_mla_v4_seeded_vs_oracle(t, heads, h):
+    inp = helpers.gen_mla_v4_inputs(1200 + t, t, heads, h)
+    _assert_mla_v4_close(_run_mla_v4(inp), _mla_v4_oracle(inp), inp)
+
+
+def test_mla_v4_feeds_the_v4_indexer_prolog():
+    """qr / qr_scale of the MLA prolog are the first inputs of the indexer prolog: chain both on the device and compare
+    with the oracle chain run on the device's qr."""
+    t = 9
+    m = helpers.gen_mla_v4_inputs(1300, t)
+    p = helpers.gen_prolog_v4_inputs(1301, t)
+    q, kv, qr, qs = _run_mla_v4(m)
+    p = dict(p, qr=qr, qr_scale=qs, x=m["x"], cos=m["cos"], sin=m["sin"])
+    _assert_prolog_v4_close(_run_prolog_v4(p), orc.indexer_prolog_v4(**p))
+
+
+def test_mla_v4_bad_arguments():
+    from pypto_b200 import mla_prolog_quant_v4_impl as m4
+    inp = helpers.gen_mla_v4_inputs(5, 3, heads=4, h=512)
+    c = _cuda(inp)
+    order = ("x", "wq_a", "wq_b", "w_kv", "cos", "sin", "gamma_cq", "gamma_ckv", "wq_b_scale")
+
+    def call(**over):
+        a = dict(c, **over)
+        return m4.mla_prolog_v4_in(*[a[k] for k in order])
+
+    with pytest.raises(ValueError):
+        call(x=c["x"].float())
+    with pytest.raises(ValueError):
+        call(wq_a=c["wq_a"][:, :512].contiguous())
+    with pytest.raises(ValueError):
+        call(wq_b=c["wq_b"][:, :700].contiguous())
+    with pytest.raises(ValueError):
+        call(cos=c["cos"][:2].contiguous())
+    with pytest.raises(ValueError):
+        call(wq_b_scale=c["wq_b_scale"][:, :100].contiguous())
+    with pytest.raises(RuntimeError):
+        call(gamma_cq=inp["gamma_cq"])
+    q, kv, qr, qs = call()
+    assert q.shape == (3, 4, 512) and kv.shape == (3, 512) and qr.shape == (3, 1024) and qs.shape == (3, 1)
+
+
+# --------------------------------------------------------------------------------------------------
 # fused MLA prolog + indexer prolog
 # --------------------------------------------------------------------------------------------------
 def _run_mla(inp, ip):

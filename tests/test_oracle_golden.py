@@ -87,6 +87,20 @@ def test_prolog_v4_oracle_matches_reference_golden():
     assert torch.allclose(orc.rope_interleaved_inverse(fwd, cos, sin).float(), x.float(), atol=0.05)
 
 
+def test_mla_v4_oracle_matches_reference_golden():
+    g = helpers.load_mla_v4_golden()
+    inp = helpers.mla_v4_reference_inputs(g["t"])
+    for name, tensor in inp.items():
+        assert helpers.digest(tensor) == g["digests"][name], f"regenerated input {name} differs from the reference's"
+    q, kv, qr, qs = orc.mla_prolog_v4(inp["x"], inp["wq_a"], inp["wq_b"], inp["w_kv"], inp["gamma_cq"], inp["gamma_ckv"],
+                                      inp["cos"], inp["sin"], inp["wq_b_scale"])
+    # the reference's own tolerances (test_mla_prolog_quant_v4.py:344-350)
+    assert torch.allclose(q.float(), g["q"].float(), atol=1e-4, rtol=0.0078125)
+    assert torch.allclose(kv.float(), g["kv"].float(), atol=1e-4, rtol=0.0078125)
+    assert (qr.int() - g["qr"].int()).abs().max() <= 1
+    assert torch.allclose(qs, g["qr_scale"], atol=2.5e-5, rtol=0.005)
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
