@@ -328,21 +328,25 @@ int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* args, int32_t stage, void* c
  *            -> bf16 -> interleaved rotary embedding on the last 64 of 512 dims -> q
  *   stage 2: kv_a = x.wkv (fp32) -> RMSNorm * gamma_ckv -> bf16 -> rotary on the last 64 -> kv
  * Fixed sizes: q_lora_rank 1024, head_dim 512, rope 64; the head count is free.
+ * quant == 0 selects the operator without quantisation (models/deepseek_v4/mla_prolog_v4_impl.py:
+ * 310-390, 415-455): the GEMM results q_a / q_b / kv_a are bf16, qr is written as bf16 and
+ * qr_scale / wq_b_scale are not used.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
-  const float* q_a;               /* stage 0: fp32 [t, 1024]                         */
+  const void* q_a;                /* stage 0: fp32 (quant == 0: bf16) [t, 1024]      */
   const void* gamma_cq;           /* bf16 [1024]                                     */
-  int8_t* qr;                     /* stage 0 out: int8 [t, 1024]                     */
+  void* qr;                       /* stage 0 out: int8 (bf16) [t, 1024]              */
   float* qr_scale;                /* stage 0 out / stage 1 in: fp32 [t]              */
-  const int32_t* q_b;             /* stage 1: int32 [t, q_b_ld], first heads*512 columns */
+  const void* q_b;                /* stage 1: int32 (bf16) [t, q_b_ld], first heads*512 columns */
   const float* wq_b_scale;        /* fp32 [heads*512]                                */
   void* q_out;                    /* stage 1 out: bf16 [t, heads, 512]               */
-  const float* kv_a;              /* stage 2: fp32 [t, 512]                          */
+  const void* kv_a;               /* stage 2: fp32 (bf16) [t, 512]                   */
   const void* gamma_ckv;          /* bf16 [512]                                      */
   void* kv_out;                   /* stage 2 out: bf16 [t, 512]                      */
   const void* cos;                /* bf16 [t, 64]                                    */
   const void* sin;                /* bf16 [t, 64]                                    */
   int32_t t, heads, q_b_ld;
+  int32_t quant;                  /* 1: quantised operator, 0: bf16 operator         */
   float eps;
 } Dsv32MlaV4StageArgs;
 

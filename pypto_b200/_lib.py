@@ -50,7 +50,8 @@ class MlaV4StageArgs(C.Structure):
     _fields_ = [
         ("q_a", c_void_p), ("gamma_cq", c_void_p), ("qr", c_void_p), ("qr_scale", c_void_p), ("q_b", c_void_p),
         ("wq_b_scale", c_void_p), ("q_out", c_void_p), ("kv_a", c_void_p), ("gamma_ckv", c_void_p), ("kv_out", c_void_p),
-        ("cos", c_void_p), ("sin", c_void_p), ("t", c_i32), ("heads", c_i32), ("q_b_ld", c_i32), ("eps", c_float),
+        ("cos", c_void_p), ("sin", c_void_p), ("t", c_i32), ("heads", c_i32), ("q_b_ld", c_i32), ("quant", c_i32),
+        ("eps", c_float),
     ]
 
 

@@ -477,9 +477,11 @@ int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* a, int32_t stage, void*
   REQUIRE(stage >= 0 && stage <= 2, "mla v4: stage=%d must be 0, 1 or 2", stage);
   REQUIRE(a->t >= 0, "mla v4: bad t=%d", a->t);
   if (a->t == 0) return DSV32_OK;
-  if (stage == 0) REQUIRE(a->q_a && a->gamma_cq && a->qr && a->qr_scale, "mla v4 stage 0: NULL tensor pointer");
+  REQUIRE(a->quant == 0 || a->quant == 1, "mla v4: quant=%d must be 0 or 1", a->quant);
+  if (stage == 0)
+    REQUIRE(a->q_a && a->gamma_cq && a->qr && (a->qr_scale || !a->quant), "mla v4 stage 0: NULL tensor pointer");
   if (stage == 1)
-    REQUIRE(a->q_b && a->qr_scale && a->wq_b_scale && a->q_out && a->cos && a->sin && a->heads >= 1 &&
+    REQUIRE(a->q_b && ((a->qr_scale && a->wq_b_scale) || !a->quant) && a->q_out && a->cos && a->sin && a->heads >= 1 &&
                 a->heads <= 65535 && a->q_b_ld >= a->heads * 512,
             "mla v4 stage 1: NULL tensor pointer, bad heads=%d or q_b_ld=%d too small", a->heads, a->q_b_ld);
   if (stage == 2) REQUIRE(a->kv_a && a->gamma_ckv && a->kv_out && a->cos && a->sin, "mla v4 stage 2: NULL tensor pointer");
@@ -496,7 +498,7 @@ int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* a, int32_t stage, void*
   p.kv_out = static_cast<__nv_bfloat16*>(a->kv_out);
   p.cos = static_cast<const __nv_bfloat16*>(a->cos);
   p.sin = static_cast<const __nv_bfloat16*>(a->sin);
-  p.t = a->t; p.heads = a->heads; p.q_b_ld = a->q_b_ld;
+  p.t = a->t; p.heads = a->heads; p.q_b_ld = a->q_b_ld; p.quant = a->quant;
   p.eps = a->eps;
   return launch_mla_v4_stage(p, stage, static_cast<cudaStream_t>(cuda_stream));
 }

@@ -132,19 +132,20 @@ struct MlaStageParams {
 int launch_mla_stage(const MlaStageParams& p, int stage, cudaStream_t stream);
 
 struct MlaV4StageParams {
-  const float* q_a;               // stage 0: fp32 [t, 1024]
+  // quant != 0: the quantised operator (fp32 / int32 GEMM results, int8 qr); 0: the bf16 operator (bf16 throughout)
+  const void* q_a;                // stage 0: fp32 (bf16) [t, 1024]
   const __nv_bfloat16* gamma_cq;  // bf16 [1024]
-  int8_t* qr;                     // stage 0 out: int8 [t, 1024]
-  float* qr_scale;                // stage 0 out / stage 1 in: fp32 [t]
-  const int32_t* q_b;             // stage 1: int32 [t, q_b_ld], first heads*512 columns
+  void* qr;                       // stage 0 out: int8 (bf16) [t, 1024]
+  float* qr_scale;                // stage 0 out / stage 1 in: fp32 [t] (quantised operator only)
+  const void* q_b;                // stage 1: int32 (bf16) [t, q_b_ld], first heads*512 columns
   const float* wq_b_scale;        // fp32 [heads*512]
   __nv_bfloat16* q_out;           // stage 1 out: bf16 [t, heads, 512]
-  const float* kv_a;              // stage 2: fp32 [t, 512]
+  const void* kv_a;               // stage 2: fp32 (bf16) [t, 512]
   const __nv_bfloat16* gamma_ckv; // bf16 [512]
   __nv_bfloat16* kv_out;          // stage 2 out: bf16 [t, 512]
   const __nv_bfloat16* cos;       // bf16 [t, 64]
   const __nv_bfloat16* sin;
-  int t, heads, q_b_ld;
+  int t, heads, q_b_ld, quant;
   float eps;
 };
 int launch_mla_v4_stage(const MlaV4StageParams& p, int stage, cudaStream_t stream);

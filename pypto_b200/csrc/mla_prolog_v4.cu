@@ -6,6 +6,9 @@
 //   stage 1: q_b (int32 [t, heads*512]) -> * qr_scale * wq_b_scale -> per-head RMSNorm without weight -> bf16;
 //            last 64 dims of a head: interleaved rotary embedding -> q [t, heads, 512]
 //   stage 2: kv_a (fp32 [t, 512]) -> RMSNorm * gamma_ckv -> bf16; last 64 dims: interleaved rotary -> kv [t, 512]
+// The operator without quantisation (models/deepseek_v4/mla_prolog_v4_impl.py:310-390; golden
+// models/deepseek_v4/test_mla_prolog_v4.py:117-158) is the kQuant = false instantiation of the same kernels: its
+// three GEMMs return bf16, stage 0 writes qr as bf16 without quantising and stage 1 has nothing to dequantise.
 // Rotary form (apply_rotary_pos_emb_v2, test_mla_prolog_quant_v4.py:84-106): pairs (2i, 2i+1),
 //   out[2i] = x[2i] cos[2i] - x[2i+1] sin[2i],  out[2i+1] = x[2i+1] cos[2i+1] + x[2i] sin[2i+1]   (fp32, then bf16).
 #include "kernels.cuh"
@@ -50,14 +53,15 @@ __device__ __forceinline__ float v4_rope(const float* x, int j, const __nv_bfloa
 }  // namespace
 
 // ---- stage 0: one CTA per token, 256 threads, 4 elements each ---------------------------------------------
+template <bool kQuant>
 __global__ void __launch_bounds__(256) mla_v4_rmsnorm_quant_kernel(MlaV4StageParams p) {
   __shared__ float red[8];
   const int tok = blockIdx.x, tid = threadIdx.x;
-  const float* row = p.q_a + static_cast<size_t>(tok) * 1024;
   float x[4], ss = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    x[i] = row[tid + i * 256];
+    const size_t at = static_cast<size_t>(tok) * 1024 + tid + i * 256;
+    x[i] = kQuant ? static_cast<const float*>(p.q_a)[at] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.q_a)[at]);
     ss += __fmul_rn(__fmul_rn(x[i], x[i]), 1.0f / 1024.0f);
   }
   const float rms = sqrtf(v4_block_sum<256>(ss, red) + p.eps);
@@ -67,27 +71,39 @@ __global__ void __launch_bounds__(256) mla_v4_rmsnorm_quant_kernel(MlaV4StagePar
     x[i] = __fmul_rn(__fdiv_rn(x[i], rms), __bfloat162float(p.gamma_cq[tid + i * 256]));
     amax = fmaxf(amax, fabsf(x[i]));
   }
+  if constexpr (!kQuant) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      static_cast<__nv_bfloat16*>(p.qr)[static_cast<size_t>(tok) * 1024 + tid + i * 256] = __float2bfloat16_rn(x[i]);
+    return;
+  }
   amax = v4_block_max<256>(amax, red);
   const float sq = __fdiv_rn(127.0f, amax);
 #pragma unroll
   for (int i = 0; i < 4; ++i)
-    p.qr[static_cast<size_t>(tok) * 1024 + tid + i * 256] = static_cast<int8_t>(static_cast<int>(rintf(__fmul_rn(x[i], sq))));
+    static_cast<int8_t*>(p.qr)[static_cast<size_t>(tok) * 1024 + tid + i * 256] =
+        static_cast<int8_t>(static_cast<int>(rintf(__fmul_rn(x[i], sq))));
   if (tid == 0) p.qr_scale[tok] = __fdiv_rn(1.0f, sq);
 }
 
 // ---- stage 1: one CTA per (token, head), 256 threads, 2 elements each ---------------------------------------
+template <bool kQuant>
 __global__ void __launch_bounds__(256) mla_v4_q_finish_kernel(MlaV4StageParams p) {
   __shared__ float red[8];
   __shared__ float rope_s[64];
   const int tok = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
   const size_t col0 = static_cast<size_t>(head) * 512;
-  const int32_t* row = p.q_b + static_cast<size_t>(tok) * p.q_b_ld + col0;
-  const float qs = p.qr_scale[tok];
+  const size_t row0 = static_cast<size_t>(tok) * p.q_b_ld + col0;
+  float qs = 0.f;
+  if constexpr (kQuant) qs = p.qr_scale[tok];
   float x[2], ss = 0.f;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int d = tid + i * 256;
-    x[i] = __fmul_rn(__fmul_rn(__int2float_rn(row[d]), qs), p.wq_b_scale[col0 + d]);
+    if constexpr (kQuant)
+      x[i] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<const int32_t*>(p.q_b)[row0 + d]), qs), p.wq_b_scale[col0 + d]);
+    else
+      x[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.q_b)[row0 + d]);
     ss += __fmul_rn(__fmul_rn(x[i], x[i]), 1.0f / 512.0f);
   }
   const float rms = sqrtf(v4_block_sum<256>(ss, red) + p.eps);
@@ -106,11 +122,13 @@ __global__ void __launch_bounds__(256) mla_v4_q_finish_kernel(MlaV4StageParams p
 }
 
 // ---- stage 2: one CTA per token, 512 threads ------------------------------------------------------------------
+template <bool kQuant>
 __global__ void __launch_bounds__(512) mla_v4_kv_finish_kernel(MlaV4StageParams p) {
   __shared__ float red[16];
   __shared__ float rope_s[64];
   const int tok = blockIdx.x, tid = threadIdx.x;
-  const float x = p.kv_a[static_cast<size_t>(tok) * 512 + tid];
+  const size_t at = static_cast<size_t>(tok) * 512 + tid;
+  const float x = kQuant ? static_cast<const float*>(p.kv_a)[at] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.kv_a)[at]);
   const float rms = sqrtf(v4_block_sum<512>(__fmul_rn(__fmul_rn(x, x), 1.0f / 512.0f), red) + p.eps);
   const float y = v4_bf16r(__fmul_rn(__fdiv_rn(x, rms), __bfloat162float(p.gamma_ckv[tid])));
   __nv_bfloat16* out = p.kv_out + static_cast<size_t>(tok) * 512;
@@ -125,11 +143,14 @@ __global__ void __launch_bounds__(512) mla_v4_kv_finish_kernel(MlaV4StageParams 
 int launch_mla_v4_stage(const MlaV4StageParams& p, int stage, cudaStream_t stream) {
   if (p.t <= 0) return DSV32_OK;
   if (stage == 0) {
-    mla_v4_rmsnorm_quant_kernel<<<p.t, 256, 0, stream>>>(p);
+    if (p.quant) mla_v4_rmsnorm_quant_kernel<true><<<p.t, 256, 0, stream>>>(p);
+    else mla_v4_rmsnorm_quant_kernel<false><<<p.t, 256, 0, stream>>>(p);
   } else if (stage == 1) {
-    mla_v4_q_finish_kernel<<<dim3(p.t, p.heads), 256, 0, stream>>>(p);
+    if (p.quant) mla_v4_q_finish_kernel<true><<<dim3(p.t, p.heads), 256, 0, stream>>>(p);
+    else mla_v4_q_finish_kernel<false><<<dim3(p.t, p.heads), 256, 0, stream>>>(p);
   } else {
-    mla_v4_kv_finish_kernel<<<p.t, 512, 0, stream>>>(p);
+    if (p.quant) mla_v4_kv_finish_kernel<true><<<p.t, 512, 0, stream>>>(p);
+    else mla_v4_kv_finish_kernel<false><<<p.t, 512, 0, stream>>>(p);
   }
   count_launch();
   return check_launch("mla v4 prolog stage kernel");

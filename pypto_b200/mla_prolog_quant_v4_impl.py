@@ -95,7 +95,7 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
         q_a = _fp32_gemm(token_x, wq_a)                                   # [t, 1024] fp32
         a = _lib.MlaV4StageArgs(rt.ptr(q_a), rt.ptr(gamma_cq), rt.ptr(qr_out), rt.ptr(qr_scale_out), None,
                                 rt.ptr(wq_b_scale), rt.ptr(q_out), None, rt.ptr(gamma_ckv), rt.ptr(kv_out),
-                                rt.ptr(rope_cos), rt.ptr(rope_sin), t, heads, 0, eps)
+                                rt.ptr(rope_cos), rt.ptr(rope_sin), t, heads, 0, 1, eps)
         rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 0, stream), "mla_prolog_v4 (q norm + quant)")
         q_b = _int8_gemm(qr_out, wq_b)                                    # [>= t, heads * 512] int32
         a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]

@@ -29,6 +29,8 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
                      (compute_quant_lightning_indexer_prolog, models/deepseek_v4/test_lightning_indexer_prolog_quant_v4.py)
   mla_v4_small.npz   token count + input digests + outputs of the DeepSeek-V4 MLA prolog golden
                      (mla_prolog_compute, models/deepseek_v4/test_mla_prolog_quant_v4.py)
+  mla_v4_bf16_small.npz  outputs of the DeepSeek-V4 MLA prolog golden without quantisation (mla_prolog_compute,
+                     models/deepseek_v4/test_mla_prolog_v4.py) on the un-quantised inputs of mla_v4_small.npz
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -396,6 +398,27 @@ def make_mla_v4():
     print("mla_v4_small: q", tuple(outputs["q_golden"].shape))
 
 
+def make_mla_v4_bf16():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        with _TolerateNpuDispatchKey():
+            import test_mla_prolog_v4 as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    t = 5
+    params = {"t": t, "num_heads": 64, "h": 4096, "q_lora_rank": 1024, "head_dim": 512, "qk_rope_head_dim": 64}
+    torch.manual_seed(5)   # as the reference module does when it is imported
+    x, wq_a, wq_b, w_kv, gamma_cq, gamma_ckv, cos, sin = ref.gen_mla_prolog_input_data(params, torch.bfloat16)
+    inputs = {"x": x, "wq_a": wq_a, "wq_b": wq_b, "w_kv": w_kv, "cos": cos, "sin": sin, "gamma_cq": gamma_cq,
+              "gamma_ckv": gamma_ckv}
+    q, kv, qr = ref.mla_prolog_compute(inputs)
+    digests = {n: digest(v) for n, v in inputs.items()}
+    np.savez_compressed(os.path.join(HERE, "mla_v4_bf16_small.npz"), t=t, digests=json.dumps(digests), q=bits16(q),
+                        kv=bits16(kv), qr=bits16(qr))
+    print("mla_v4_bf16_small: q", tuple(q.shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -424,3 +447,4 @@ if __name__ == "__main__":
     make_win()
     make_prolog_v4()
     make_mla_v4()
+    make_mla_v4_bf16()

@@ -294,6 +294,30 @@ def mla_v4_reference_inputs(t, heads=64, h=4096):
                 wq_b_scale=1 / s)
 
 
+def load_mla_v4_bf16_golden():
+    z = np.load(os.path.join(GOLDEN, "mla_v4_bf16_small.npz"))
+    bf = torch.bfloat16
+    return dict(t=int(z["t"]), digests=json.loads(str(z["digests"])), q=from_bits16(z["q"], bf),
+                kv=from_bits16(z["kv"], bf), qr=from_bits16(z["qr"], bf))
+
+
+def mla_v4_bf16_reference_inputs(t, heads=64, h=4096):
+    """The reference generator of the MLA prolog test without quantisation
+    (models/deepseek_v4/test_mla_prolog_v4.py:161-199, seed 5): the same draws as mla_v4_reference_inputs, with
+    wq_b kept in bf16."""
+    torch.manual_seed(5)
+    bf = torch.bfloat16
+    x = torch.empty([t, h], dtype=bf).uniform_(-1, 1)
+    wq_a = torch.empty([h, 1024], dtype=bf).uniform_(-0.1, 0.1)
+    wq_b = torch.empty([1024, heads * 512], dtype=bf).uniform_(-0.1, 0.1)
+    w_kv = torch.empty([h, 512], dtype=bf).uniform_(-0.1, 0.1)
+    gamma_cq = torch.empty([1024], dtype=bf).uniform_(-1, 1)
+    gamma_ckv = torch.empty([512], dtype=bf).uniform_(-1, 1)
+    cos = torch.empty([t, 64], dtype=bf).uniform_(-1, 1)
+    sin = torch.empty([t, 64], dtype=bf).uniform_(-1, 1)
+    return dict(x=x, wq_a=wq_a, wq_b=wq_b, w_kv=w_kv, cos=cos, sin=sin, gamma_cq=gamma_cq, gamma_ckv=gamma_ckv)
+
+
 def gen_mla_v4_inputs(seed, t, heads=64, h=4096):
     """Seeded inputs of the DeepSeek-V4 MLA prolog with realistic distributions: normal activations and weights,
     gamma near one, unit-circle cos / sin repeated per rotary pair."""

@@ -856,6 +856,60 @@ def test_mla_v4_feeds_the_v4_indexer_prolog():
     _assert_prolog_v4_close(_run_prolog_v4(p), orc.indexer_prolog_v4(**p))
 
 
+def _run_mla_v4_bf16(inp, entry="in"):
+    import pypto_b200
+    from pypto_b200 import mla_prolog_v4_impl as m4
+    c = _cuda(inp)
+    if entry == "in":
+        out = m4.mla_prolog_v4_in(c["x"], c["wq_a"], c["wq_b"], c["w_kv"], c["cos"], c["sin"], c["gamma_cq"], c["gamma_ckv"])
+    else:
+        t, heads = inp["x"].shape[0], inp["wq_b"].shape[1] // 512
+        q = torch.zeros((t, heads, 512), dtype=torch.bfloat16, device=DEV)
+        kv = torch.zeros((t, 512), dtype=torch.bfloat16, device=DEV)
+        qr = torch.zeros((t, 1024), dtype=torch.bfloat16, device=DEV)
+        assert m4.mla_prolog_v4(c["x"], c["wq_a"], c["wq_b"], c["w_kv"], c["gamma_cq"], c["gamma_ckv"], c["cos"], c["sin"],
+                                q, kv, qr, m4.MlaPrologV4Attrs(), m4.MlaPrologV4Configs()) is None
+        out = (q, kv, qr)
+    pypto_b200.check_status()
+    return tuple(o.cpu() for o in out)
+
+
+def _assert_mla_v4_bf16_close(got, ref, inp):
+    q, kv, qr = got
+    rq, rkv, rqr = ref
+    # the reference's rule for all three outputs (test_mla_prolog_v4.py:309-313): atol 1e-4, rtol 2^-7, 0.5 % of the
+    # elements may fall outside.  A last-bit difference of the bf16 GEMM results (another summation order) is one
+    # bf16 step = 2^-8 relative, inside the rule; q is two GEMMs deep, so it is also judged from the device's own qr.
+    for name, a, b in (("kv", kv, rkv), ("qr", qr, rqr)):
+        bad = orc.reference_compare_count(a, b, 1e-4, 0.0078125)
+        assert bad <= 0.005 * a.numel(), f"{name}: {bad} of {a.numel()} outside the reference's rule"
+    heads = inp["wq_b"].shape[1] // 512
+    qb = torch.matmul(qr, inp["wq_b"]).reshape(qr.shape[0], heads, 512).float()
+    qn = (qb / torch.sqrt((qb * qb * (1.0 / 512)).sum(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    q_own = torch.cat([qn[:, :, :-64], orc.rope_interleaved_inverse(qn[:, :, -64:], inp["cos"], -inp["sin"])], dim=-1)
+    assert orc.reference_compare_count(q, q_own, 1e-4, 0.0078125) <= 0.005 * q.numel()
+    assert orc.reference_compare_count(q, rq, 1e-4, 0.0078125) <= 0.03 * q.numel()
+    assert torch.allclose(q.float(), rq.float(), atol=0.02, rtol=0.05)
+
+
+def test_mla_v4_bf16_reference_golden_fixture():
+    g = helpers.load_mla_v4_bf16_golden()
+    inp = helpers.mla_v4_bf16_reference_inputs(g["t"])
+    got = _run_mla_v4_bf16(inp)
+    _assert_mla_v4_bf16_close(got, (g["q"], g["kv"], g["qr"]), inp)
+    again = _run_mla_v4_bf16(inp, entry="kernel")
+    assert all(torch.equal(a, b) for a, b in zip(got, again))
+
+
+@pytest.mark.parametrize("t,heads,h", [(1, 64, 4096), (37, 64, 4096), (128, 64, 4096), (20, 8, 1024)])
+def test_mla_v4_bf16_seeded_vs_oracle(t, heads, h):
+    inp = helpers.gen_mla_v4_inputs(1400 + t, t, heads, h)
+    inp = dict(inp, wq_b=(inp["wq_b"].float() * inp["wq_b_scale"]).to(torch.bfloat16))
+    ref = orc.mla_prolog_v4_bf16(inp["x"], inp["wq_a"], inp["wq_b"], inp["w_kv"], inp["gamma_cq"], inp["gamma_ckv"],
+                                 inp["cos"], inp["sin"])
+    _assert_mla_v4_bf16_close(_run_mla_v4_bf16(inp), ref, inp)
+
+
 def test_mla_v4_bad_arguments():
     from pypto_b200 import mla_prolog_quant_v4_impl as m4
     inp = helpers.gen_mla_v4_inputs(5, 3, heads=4, h=512)

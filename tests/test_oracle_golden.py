@@ -101,6 +101,17 @@ def test_mla_v4_oracle_matches_reference_golden():
     assert torch.allclose(qs, g["qr_scale"], atol=2.5e-5, rtol=0.005)
 
 
+def test_mla_v4_bf16_oracle_matches_reference_golden():
+    g = helpers.load_mla_v4_bf16_golden()
+    inp = helpers.mla_v4_bf16_reference_inputs(g["t"])
+    for name, tensor in inp.items():
+        assert helpers.digest(tensor) == g["digests"][name], f"regenerated input {name} differs from the reference's"
+    q, kv, qr = orc.mla_prolog_v4_bf16(inp["x"], inp["wq_a"], inp["wq_b"], inp["w_kv"], inp["gamma_cq"], inp["gamma_ckv"],
+                                       inp["cos"], inp["sin"])
+    for got, ref in ((q, g["q"]), (kv, g["kv"]), (qr, g["qr"])):   # the reference's own tolerance for all three
+        assert torch.allclose(got.float(), ref.float(), atol=1e-4, rtol=0.0078125)
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
