@@ -352,6 +352,33 @@ typedef struct {
 
 int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* args, int32_t stage, void* cuda_stream);
 
+/* ---------------------------------------------------------------------------------------
+ * DeepSeek-V4 hyper-connection pre-mix.  Replaces hc_pre_kernel / hc_pre_kernel_prefill /
+ * npu_hc_pre (models/deepseek_v4/hc_pre_impl.py:100-206 / 216-309 / 371-392):
+ *   mix = (x as [t, 16384]) . hc_fn^T / sqrt(mean(x^2) + norm_eps)                  [t, 24]
+ *   pre = sigmoid(mix[0:4] * hc_scale[0] + hc_base[0:4]) + hc_eps
+ *   post = 2 * sigmoid(mix[4:8] * hc_scale[1] + hc_base[4:8])
+ *   comb = Sinkhorn(mix[8:24] * hc_scale[2] + hc_base[8:24], iters, hc_eps)        [t, 4, 4]
+ *   y = bf16(sum_h pre[h] * x[:, h, :])                                            [t, 4096]
+ * Fixed sizes: 4 streams of 4096.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;                  /* bf16 [t, 4, 4096]                    */
+  const float* hc_fn;             /* fp32 [24, 16384]                     */
+  const float* hc_scale;          /* fp32 [3]                             */
+  const float* hc_base;           /* fp32 [24]                            */
+  void* y;                        /* out bf16 [t, 4096]                   */
+  float* post;                    /* out fp32 [t, 4]                      */
+  float* comb;                    /* out fp32 [t, 4, 4]                   */
+  void* workspace;                /* >= dsv32_hc_pre_workspace_bytes(t), 16-byte aligned */
+  size_t workspace_bytes;
+  int32_t t, hc_mult, d, iters;   /* hc_mult must be 4, d 4096, iters >= 1 */
+  float norm_eps, hc_eps;
+} Dsv32HcPreArgs;
+
+int dsv32_hc_pre(const Dsv32HcPreArgs* args, void* cuda_stream);
+size_t dsv32_hc_pre_workspace_bytes(int32_t t);
+
 /* library-wide */
 int dsv32_abi_version(void);
 const char* dsv32_last_error(void);

@@ -55,6 +55,15 @@ class MlaV4StageArgs(C.Structure):
     ]
 
 
+class HcPreArgs(C.Structure):
+    _fields_ = [
+        ("x", c_void_p), ("hc_fn", c_void_p), ("hc_scale", c_void_p), ("hc_base", c_void_p), ("y", c_void_p),
+        ("post", c_void_p), ("comb", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("t", c_i32),
+        ("hc_mult", c_i32), ("d", c_i32), ("iters", c_i32),
+        ("norm_eps", c_float), ("hc_eps", c_float),
+    ]
+
+
 class PrologV4Args(C.Structure):
     _fields_ = [
         ("qr", c_void_p), ("idx_wq_b", c_void_p), ("x", c_void_p), ("weights_proj", c_void_p), ("cos", c_void_p),
@@ -119,6 +128,8 @@ EXPORTS = {
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_indexer_prolog_v4": (c_i32, [C.POINTER(PrologV4Args), c_void_p]),
     "dsv32_mla_prolog_v4_stage": (c_i32, [C.POINTER(MlaV4StageArgs), c_i32, c_void_p]),
+    "dsv32_hc_pre": (c_i32, [C.POINTER(HcPreArgs), c_void_p]),
+    "dsv32_hc_pre_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_indexer_prolog": (c_i32, [C.POINTER(PrologArgs), c_void_p]),
     "dsv32_mla_prolog_stage": (c_i32, [C.POINTER(MlaStageArgs), c_i32, c_void_p]),

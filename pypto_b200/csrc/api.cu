@@ -503,4 +503,36 @@ int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* a, int32_t stage, void*
   return launch_mla_v4_stage(p, stage, static_cast<cudaStream_t>(cuda_stream));
 }
 
+size_t dsv32_hc_pre_workspace_bytes(int32_t t) { return align_up(hc_pre_workspace_bytes(t), 256); }
+
+int dsv32_hc_pre(const Dsv32HcPreArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "hc_pre: args is NULL");
+  REQUIRE(a->t >= 0, "hc_pre: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  REQUIRE(a->hc_mult == 4 && a->d == 4096, "hc_pre: only 4 streams of 4096 are supported (got %d x %d)", a->hc_mult, a->d);
+  REQUIRE(a->iters >= 1, "hc_pre: iters=%d must be >= 1", a->iters);
+  REQUIRE(a->x && a->hc_fn && a->hc_scale && a->hc_base && a->y && a->post && a->comb, "hc_pre: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->x) % 16 == 0 && reinterpret_cast<uintptr_t>(a->y) % 16 == 0,
+          "hc_pre: x and y must be 16-byte aligned");
+  const size_t need = hc_pre_workspace_bytes(a->t);
+  if (a->workspace == nullptr || a->workspace_bytes < need || reinterpret_cast<uintptr_t>(a->workspace) % 16 != 0) {
+    set_error("hc_pre: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
+  HcPreParams p{};
+  p.partial = static_cast<float*>(a->workspace);
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.hc_fn = a->hc_fn;
+  p.hc_scale = a->hc_scale;
+  p.hc_base = a->hc_base;
+  p.y = static_cast<__nv_bfloat16*>(a->y);
+  p.post = a->post;
+  p.comb = a->comb;
+  p.t = a->t;
+  p.iters = a->iters;
+  p.norm_eps = a->norm_eps;
+  p.hc_eps = a->hc_eps;
+  return launch_hc_pre(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

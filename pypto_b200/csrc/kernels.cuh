@@ -150,4 +150,19 @@ struct MlaV4StageParams {
 };
 int launch_mla_v4_stage(const MlaV4StageParams& p, int stage, cudaStream_t stream);
 
+struct HcPreParams {
+  const __nv_bfloat16* x;   // [t, 4, 4096]
+  const float* hc_fn;       // [24, 16384]
+  const float* hc_scale;    // [3]
+  const float* hc_base;     // [24]
+  __nv_bfloat16* y;         // [t, 4096]
+  float* post;              // [t, 4]
+  float* comb;              // [t, 4, 4]
+  float* partial;           // workspace: [groups, t, 24] partial dot products
+  int t, iters;
+  float norm_eps, hc_eps;
+};
+int launch_hc_pre(const HcPreParams& p, cudaStream_t stream);
+size_t hc_pre_workspace_bytes(int t);
+
 }  // namespace dsv32

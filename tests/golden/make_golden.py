@@ -31,6 +31,8 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
                      (mla_prolog_compute, models/deepseek_v4/test_mla_prolog_quant_v4.py)
   mla_v4_bf16_small.npz  outputs of the DeepSeek-V4 MLA prolog golden without quantisation (mla_prolog_compute,
                      models/deepseek_v4/test_mla_prolog_v4.py) on the un-quantised inputs of mla_v4_small.npz
+  hc_pre_small.npz   token count + input digests + outputs of the DeepSeek-V4 hyper-connection pre-mix golden
+                     (gen_hc_pre, models/deepseek_v4/test_hc_pre.py)
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -419,6 +421,22 @@ def make_mla_v4_bf16():
     print("mla_v4_bf16_small: q", tuple(q.shape))
 
 
+def make_hc_pre():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        with _TolerateNpuDispatchKey():
+            import test_hc_pre as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    t = 16
+    x, hc_fn, hc_scale, hc_base, y, post, comb, _ = ref.gen_hc_pre_data(t)    # seeds torch with 42 itself
+    digests = {"x": digest(x), "hc_fn": digest(hc_fn), "hc_scale": digest(hc_scale), "hc_base": digest(hc_base)}
+    np.savez_compressed(os.path.join(HERE, "hc_pre_small.npz"), t=t, digests=json.dumps(digests), y=bits16(y),
+                        post=post.numpy(), comb=comb.numpy())
+    print("hc_pre_small: y", tuple(y.shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -448,3 +466,4 @@ if __name__ == "__main__":
     make_prolog_v4()
     make_mla_v4()
     make_mla_v4_bf16()
+    make_hc_pre()

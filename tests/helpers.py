@@ -318,6 +318,31 @@ def mla_v4_bf16_reference_inputs(t, heads=64, h=4096):
     return dict(x=x, wq_a=wq_a, wq_b=wq_b, w_kv=w_kv, cos=cos, sin=sin, gamma_cq=gamma_cq, gamma_ckv=gamma_ckv)
 
 
+def load_hc_pre_golden():
+    z = np.load(os.path.join(GOLDEN, "hc_pre_small.npz"))
+    return dict(t=int(z["t"]), digests=json.loads(str(z["digests"])), y=from_bits16(z["y"], torch.bfloat16),
+                post=torch.from_numpy(z["post"]), comb=torch.from_numpy(z["comb"]))
+
+
+def hc_pre_reference_inputs(t):
+    """The reference generator of the hyper-connection pre-mix test (models/deepseek_v4/test_hc_pre.py:141-149,
+    seed 42): reproduces the digests stored in hc_pre_small.npz."""
+    torch.manual_seed(42)
+    x = torch.empty((t, 4, 4096), dtype=torch.bfloat16).uniform_(-1, 1)
+    hc_fn = torch.empty((24, 4 * 4096), dtype=torch.float32).uniform_(-1, 1)
+    hc_scale = torch.empty((3,), dtype=torch.float32).uniform_(-1, 1)
+    hc_base = torch.empty((24,), dtype=torch.float32).uniform_(-1, 1)
+    return dict(x=x, hc_fn=hc_fn, hc_scale=hc_scale, hc_base=hc_base)
+
+
+def gen_hc_pre_inputs(seed, t, fn_scale=0.02):
+    """Seeded inputs with mixing logits of order one (the reference generator's saturate every sigmoid)."""
+    g = torch.Generator().manual_seed(seed)
+    return dict(x=torch.randn((t, 4, 4096), generator=g).to(torch.bfloat16),
+                hc_fn=torch.randn((24, 4 * 4096), generator=g) * fn_scale,
+                hc_scale=torch.rand((3,), generator=g) + 0.5, hc_base=torch.randn((24,), generator=g) * 0.5)
+
+
 def gen_mla_v4_inputs(seed, t, heads=64, h=4096):
     """Seeded inputs of the DeepSeek-V4 MLA prolog with realistic distributions: normal activations and weights,
     gamma near one, unit-circle cos / sin repeated per rotary pair."""

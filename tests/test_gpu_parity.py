@@ -937,6 +937,74 @@ def test_mla_v4_bad_arguments():
 
 
 # --------------------------------------------------------------------------------------------------
+# DeepSeek-V4 hyper-connection pre-mix
+# --------------------------------------------------------------------------------------------------
+def _run_hc_pre(inp, entry="npu", iters=20, eps=1e-6):
+    import pypto_b200
+    from pypto_b200 import hc_pre_impl as hp
+    c = _cuda(inp)
+    if entry == "npu":
+        out = hp.npu_hc_pre(c["x"], c["hc_fn"], c["hc_scale"], c["hc_base"], 4, iters, eps)
+    else:
+        t = inp["x"].shape[0]
+        y = torch.zeros((t, 4096), dtype=torch.bfloat16, device=DEV)
+        post = torch.zeros((t, 4), dtype=torch.float32, device=DEV)
+        comb = torch.zeros((t, 4, 4), dtype=torch.float32, device=DEV)
+        fn = hp.hc_pre_kernel if entry == "kernel" else hp.hc_pre_kernel_prefill
+        assert fn(c["x"], c["hc_fn"], c["hc_scale"], c["hc_base"], y, post, comb, 4, iters, eps) is None
+        out = (y, post, comb)
+    pypto_b200.check_status()
+    return tuple(o.cpu() for o in out)
+
+
+def _assert_hc_pre_close(got, ref):
+    # the reference's own tolerances (test_hc_pre.py:203-208)
+    y, post, comb = got
+    ry, rpost, rcomb = ref
+    assert orc.reference_compare_count(y, ry, 1e-4, 0.0078125) <= 0.005 * y.numel()
+    assert torch.allclose(post, rpost, atol=2.5e-5, rtol=0.005)
+    assert torch.allclose(comb, rcomb, atol=2.5e-5, rtol=0.005)
+
+
+def test_hc_pre_reference_golden_fixture():
+    g = helpers.load_hc_pre_golden()
+    inp = helpers.hc_pre_reference_inputs(g["t"])
+    got = _run_hc_pre(inp)
+    _assert_hc_pre_close(got, (g["y"], g["post"], g["comb"]))
+    for entry in ("kernel", "prefill"):
+        assert all(torch.equal(a, b) for a, b in zip(got, _run_hc_pre(inp, entry)))
+
+
+@pytest.mark.parametrize("t,iters,eps", [(1, 20, 1e-6), (37, 20, 1e-6), (512, 20, 1e-6), (9, 1, 1e-6), (9, 3, 1e-3)])
+def test_hc_pre_seeded_vs_oracle(t, iters, eps):
+    inp = helpers.gen_hc_pre_inputs(1500 + t + iters, t)
+    got = _run_hc_pre(inp, iters=iters, eps=eps)
+    _assert_hc_pre_close(got, orc.hc_pre(**inp, iters=iters, hc_eps=eps))
+    if iters == 20:  # converged Sinkhorn: doubly stochastic
+        assert torch.allclose(got[2].sum(-2), torch.ones(t, 4), atol=1e-4)
+
+
+def test_hc_pre_bad_arguments():
+    from pypto_b200 import hc_pre_impl as hp
+    inp = helpers.gen_hc_pre_inputs(7, 2)
+    c = _cuda(inp)
+    with pytest.raises(ValueError):
+        hp.npu_hc_pre(c["x"][:, :2].contiguous(), c["hc_fn"], c["hc_scale"], c["hc_base"])
+    with pytest.raises(ValueError):
+        hp.npu_hc_pre(c["x"], c["hc_fn"].to(torch.bfloat16), c["hc_scale"], c["hc_base"])
+    with pytest.raises(ValueError):
+        hp.npu_hc_pre(c["x"], c["hc_fn"], c["hc_scale"][:2].contiguous(), c["hc_base"])
+    with pytest.raises(ValueError):
+        hp.npu_hc_pre(c["x"], c["hc_fn"], c["hc_scale"], c["hc_base"], 8)
+    with pytest.raises(ValueError):
+        hp.npu_hc_pre(c["x"], c["hc_fn"], c["hc_scale"], c["hc_base"], 4, 0)
+    with pytest.raises(RuntimeError):
+        hp.npu_hc_pre(inp["x"], c["hc_fn"], c["hc_scale"], c["hc_base"])
+    y, post, comb = hp.npu_hc_pre(c["x"], c["hc_fn"], c["hc_scale"], c["hc_base"])
+    assert y.shape == (2, 4096) and post.shape == (2, 4) and comb.shape == (2, 4, 4)
+
+
+# --------------------------------------------------------------------------------------------------
 # fused MLA prolog + indexer prolog
 # --------------------------------------------------------------------------------------------------
 def _run_mla(inp, ip):

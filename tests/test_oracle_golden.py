@@ -112,6 +112,21 @@ def test_mla_v4_bf16_oracle_matches_reference_golden():
         assert torch.allclose(got.float(), ref.float(), atol=1e-4, rtol=0.0078125)
 
 
+def test_hc_pre_oracle_matches_reference_golden():
+    g = helpers.load_hc_pre_golden()
+    inp = helpers.hc_pre_reference_inputs(g["t"])
+    for name, tensor in inp.items():
+        assert helpers.digest(tensor) == g["digests"][name], f"regenerated input {name} differs from the reference's"
+    y, post, comb = orc.hc_pre(**inp)
+    # the reference's own tolerances (test_hc_pre.py:203-208)
+    assert torch.allclose(y.float(), g["y"].float(), atol=1e-4, rtol=0.0078125)
+    assert torch.allclose(post, g["post"], atol=2.5e-5, rtol=0.005)
+    assert torch.allclose(comb, g["comb"], atol=2.5e-5, rtol=0.005)
+    # Sinkhorn leaves a (nearly) doubly stochastic matrix
+    y, post, comb = orc.hc_pre(**helpers.gen_hc_pre_inputs(3, 5))
+    assert torch.allclose(comb.sum(-2), torch.ones(5, 4), atol=1e-4) and torch.allclose(comb.sum(-1), torch.ones(5, 4), atol=1e-3)
+
+
 def test_sa_antiquant_oracle_matches_reference_golden():
     g = helpers.load_sa_antiquant_golden()
     out = orc.sa_antiquant(g["q_nope"], g["q_rope"], g["nope_cache"], g["topk_indices"], g["block_table"], g["act_seq"],
