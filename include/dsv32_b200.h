@@ -379,6 +379,40 @@ typedef struct {
 int dsv32_hc_pre(const Dsv32HcPreArgs* args, void* cuda_stream);
 size_t dsv32_hc_pre_workspace_bytes(int32_t t);
 
+/* ---------------------------------------------------------------------------------------
+ * DeepSeek-V4 KV compressor: state update + compression, between the operator's GEMMs.
+ * Replaces the vector work of compressor_ratio_4_kernel / compressor_ratio_4_rotate_kernel /
+ * compressor_ratio_128_kernel (models/deepseek_v4/compressor_impl.py:421-923; entry
+ * npu_compressor :139-226).  For token i of request r at position pos = start_pos[r] + i:
+ * the rows kv_total / score_total (+ ape[pos % ratio]) are stored into the paged states at
+ * pos; when (pos + 1) % ratio == 0 the window ending at pos is compressed (softmax over its
+ * score rows per column, weighted sum of its kv rows; ratio 4 uses the first halves of the
+ * previous window and the second halves of this one), RMS-normalised with `weight`, rotated
+ * (interleaved rotary on the last 64 dims, row r of sin / cos) and written to out[r].
+ * Rows of `out` of requests that did not compress are left untouched.
+ * coff = 2 with ratio 4 (overlapping windows), 1 with ratio 128; d <= 512.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const float* kv_total;          /* fp32 [b*s1, coff*d]                  */
+  const float* score_total;       /* fp32 [b*s1, coff*d]                  */
+  const float* ape;               /* fp32 [ratio, coff*d]                 */
+  const float* weight;            /* fp32 [d]                             */
+  float* kv_state;                /* in/out fp32 [kv_blocks, 128, coff*d] */
+  float* score_state;             /* in/out fp32 [score_blocks, 128, coff*d] */
+  const int32_t* kv_block_table;  /* int32 [b, kv_cols]                   */
+  const int32_t* score_block_table; /* int32 [b, score_cols]              */
+  const void* sin;                /* bf16 [>= b, 64]                      */
+  const void* cos;                /* bf16 [>= b, 64]                      */
+  const int32_t* start_pos;       /* int32 [b]                            */
+  void* out;                      /* out bf16 [>= b, d]                   */
+  uint32_t* status;
+  int64_t kv_blocks, score_blocks;
+  int32_t b, s1, d, ratio, kv_cols, score_cols;
+  float eps;
+} Dsv32CompressorArgs;
+
+int dsv32_compressor_update(const Dsv32CompressorArgs* args, void* cuda_stream);
+
 /* library-wide */
 int dsv32_abi_version(void);
 const char* dsv32_last_error(void);

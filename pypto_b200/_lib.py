@@ -55,6 +55,16 @@ class MlaV4StageArgs(C.Structure):
     ]
 
 
+class CompressorArgs(C.Structure):
+    _fields_ = [
+        ("kv_total", c_void_p), ("score_total", c_void_p), ("ape", c_void_p), ("weight", c_void_p),
+        ("kv_state", c_void_p), ("score_state", c_void_p), ("kv_block_table", c_void_p),
+        ("score_block_table", c_void_p), ("sin", c_void_p), ("cos", c_void_p), ("start_pos", c_void_p),
+        ("out", c_void_p), ("status", c_void_p), ("kv_blocks", c_i64), ("score_blocks", c_i64), ("b", c_i32),
+        ("s1", c_i32), ("d", c_i32), ("ratio", c_i32), ("kv_cols", c_i32), ("score_cols", c_i32), ("eps", c_float),
+    ]
+
+
 class HcPreArgs(C.Structure):
     _fields_ = [
         ("x", c_void_p), ("hc_fn", c_void_p), ("hc_scale", c_void_p), ("hc_base", c_void_p), ("y", c_void_p),
@@ -128,6 +138,7 @@ EXPORTS = {
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_indexer_prolog_v4": (c_i32, [C.POINTER(PrologV4Args), c_void_p]),
     "dsv32_mla_prolog_v4_stage": (c_i32, [C.POINTER(MlaV4StageArgs), c_i32, c_void_p]),
+    "dsv32_compressor_update": (c_i32, [C.POINTER(CompressorArgs), c_void_p]),
     "dsv32_hc_pre": (c_i32, [C.POINTER(HcPreArgs), c_void_p]),
     "dsv32_hc_pre_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),

@@ -535,4 +535,38 @@ int dsv32_hc_pre(const Dsv32HcPreArgs* a, void* cuda_stream) {
   return launch_hc_pre(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int dsv32_compressor_update(const Dsv32CompressorArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "compressor: args is NULL");
+  REQUIRE(a->b >= 0 && a->s1 >= 0, "compressor: bad b=%d s1=%d", a->b, a->s1);
+  if (a->b == 0 || a->s1 == 0) return DSV32_OK;
+  REQUIRE(a->ratio == 4 || a->ratio == 128, "compressor: ratio=%d must be 4 or 128", a->ratio);
+  REQUIRE(a->d >= 64 && a->d <= 512 && a->d % 2 == 0, "compressor: d=%d must be even and in [64, 512]", a->d);
+  REQUIRE(a->kv_cols >= 1 && a->score_cols >= 1 && a->kv_blocks >= 1 && a->score_blocks >= 1,
+          "compressor: empty block table or state");
+  REQUIRE(a->kv_total && a->score_total && a->ape && a->weight && a->kv_state && a->score_state &&
+              a->kv_block_table && a->score_block_table && a->sin && a->cos && a->start_pos && a->out,
+          "compressor: NULL tensor pointer");
+  CompressorParams p{};
+  p.kv_total = a->kv_total;
+  p.score_total = a->score_total;
+  p.ape = a->ape;
+  p.weight = a->weight;
+  p.kv_state = a->kv_state;
+  p.score_state = a->score_state;
+  p.kv_table = a->kv_block_table;
+  p.score_table = a->score_block_table;
+  p.sin = static_cast<const __nv_bfloat16*>(a->sin);
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos);
+  p.start_pos = a->start_pos;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.status = a->status;
+  p.kv_blocks = a->kv_blocks;
+  p.score_blocks = a->score_blocks;
+  p.b = a->b; p.s1 = a->s1; p.d = a->d; p.ratio = a->ratio;
+  p.coff = a->ratio == 4 ? 2 : 1;
+  p.kv_cols = a->kv_cols; p.score_cols = a->score_cols;
+  p.eps = a->eps;
+  return launch_compressor(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

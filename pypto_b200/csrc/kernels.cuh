@@ -150,6 +150,26 @@ struct MlaV4StageParams {
 };
 int launch_mla_v4_stage(const MlaV4StageParams& p, int stage, cudaStream_t stream);
 
+struct CompressorParams {
+  const float* kv_total;       // [b*s1, coff*d]  x . wkv^T
+  const float* score_total;    // [b*s1, coff*d]  x . wgate^T
+  const float* ape;            // [ratio, coff*d]
+  const float* weight;         // [d]
+  float* kv_state;             // [kv_blocks, 128, coff*d]
+  float* score_state;          // [score_blocks, 128, coff*d]
+  const int32_t* kv_table;     // [b, kv_cols]
+  const int32_t* score_table;  // [b, score_cols]
+  const __nv_bfloat16* sin;    // [>= b, 64]
+  const __nv_bfloat16* cos;
+  const int32_t* start_pos;    // [b]
+  __nv_bfloat16* out;          // [>= b, d]
+  uint32_t* status;
+  long long kv_blocks, score_blocks;
+  int b, s1, d, coff, ratio, kv_cols, score_cols;
+  float eps;
+};
+int launch_compressor(const CompressorParams& p, cudaStream_t stream);
+
 struct HcPreParams {
   const __nv_bfloat16* x;   // [t, 4, 4096]
   const float* hc_fn;       // [24, 16384]

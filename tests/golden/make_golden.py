@@ -33,6 +33,8 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
                      models/deepseek_v4/test_mla_prolog_v4.py) on the un-quantised inputs of mla_v4_small.npz
   hc_pre_small.npz   token count + input digests + outputs of the DeepSeek-V4 hyper-connection pre-mix golden
                      (gen_hc_pre, models/deepseek_v4/test_hc_pre.py)
+  compressor_small.npz  outputs and touched state rows of the DeepSeek-V4 compressor golden (golden_compress,
+                     models/deepseek_v4/test_compressor.py) for three cases: ratio 128, ratio 4, ratio 4 + hadamard
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -437,6 +439,43 @@ def make_hc_pre():
     print("hc_pre_small: y", tuple(y.shape))
 
 
+COMPRESSOR_CASES = {   # name: (ratio, rotate, d, batch, tokens per request, start positions)
+    "r128": (128, False, 512, 3, 2, [254, 126, 300]),
+    "r4": (4, False, 512, 4, 2, [255, 2, 6, 9]),
+    "r4_rot": (4, True, 128, 4, 2, [255, 3, 10, 1]),
+}
+
+
+def make_compressor():
+    v4_dir = os.path.join(REF, "models", "deepseek_v4")
+    sys.path.insert(0, v4_dir)
+    try:
+        with _TolerateNpuDispatchKey():
+            import test_compressor as ref  # noqa: reference module
+    finally:
+        sys.path.remove(v4_dir)
+    saved = {}
+    for name, (ratio, rotate, d, bsz, seq, starts) in COMPRESSOR_CASES.items():
+        x, sin, cos, wkv, wgate, ape, weight, kv_state, score_state, table, hadamard = ref.gen_inputs(
+            bsz, seq, 4096, d, 64, ratio, "cpu")          # seeds torch with 42 itself
+        # the generator leaves the states zero; give them history so that the rows of earlier positions matter
+        g = torch.Generator().manual_seed(7)
+        kv_state.copy_(torch.rand(kv_state.shape, generator=g))
+        score_state.copy_(torch.rand(score_state.shape, generator=g))
+        st = torch.tensor(starts, dtype=torch.int32)
+        digests = {n: digest(v) for n, v in (("x", x), ("sin", sin), ("cos", cos), ("wkv", wkv), ("wgate", wgate),
+                                             ("ape", ape), ("hadamard", hadamard), ("kv_state", kv_state),
+                                             ("score_state", score_state), ("table", table))}
+        out = ref.golden_compress(x, sin, cos, wkv, wgate, ape, weight, kv_state, score_state, table, table, hadamard,
+                                  ratio, st, 64, rotate)
+        saved[name + "_digests"] = json.dumps(digests)
+        saved[name + "_out"] = bits16(out)
+        saved[name + "_kv_state_sum"] = kv_state.double().sum(-1).numpy()       # [blocks, 128] row checksums
+        saved[name + "_score_state_sum"] = score_state.double().sum(-1).numpy()
+        print("compressor", name, "out", tuple(out.shape))
+    np.savez_compressed(os.path.join(HERE, "compressor_small.npz"), **saved)
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -467,3 +506,4 @@ if __name__ == "__main__":
     make_mla_v4()
     make_mla_v4_bf16()
     make_hc_pre()
+    make_compressor()

@@ -343,6 +343,49 @@ def gen_hc_pre_inputs(seed, t, fn_scale=0.02):
                 hc_scale=torch.rand((3,), generator=g) + 0.5, hc_base=torch.randn((24,), generator=g) * 0.5)
 
 
+COMPRESSOR_CASES = {   # name: (ratio, rotate, d, batch, tokens per request, start positions) -- as in make_golden.py
+    "r128": (128, False, 512, 3, 2, [254, 126, 300]),
+    "r4": (4, False, 512, 4, 2, [255, 2, 6, 9]),
+    "r4_rot": (4, True, 128, 4, 2, [255, 3, 10, 1]),
+}
+
+
+def compressor_reference_inputs(name):
+    """The reference generator of the compressor test (models/deepseek_v4/test_compressor.py:190-236, seed 42) with
+    the state history make_golden.py adds (seed 7); reproduces the digests stored in compressor_small.npz."""
+    ratio, rotate, d, bsz, seq, starts = COMPRESSOR_CASES[name]
+    torch.manual_seed(42)
+    bf = torch.bfloat16
+    coff = 2 if ratio == 4 else 1
+    x = torch.rand((bsz, seq, 4096), dtype=bf)
+    rows = min(bsz * seq, bsz * seq // ratio + bsz)
+    sin = torch.rand((rows, 64), dtype=bf)
+    cos = torch.rand((rows, 64), dtype=bf)
+    wkv = torch.rand((coff * d, 4096), dtype=bf)
+    wgate = torch.rand((coff * d, 4096), dtype=bf)
+    ape = torch.rand((ratio, coff * d), dtype=torch.float32)
+    weight = torch.ones(d, dtype=torch.float32)
+    if ratio == 4:
+        table = torch.ones(bsz, 100, dtype=torch.int32) + torch.arange(bsz, dtype=torch.int32).view(-1, 1) * 2
+    else:
+        table = torch.arange(100, dtype=torch.int32) % 2 + 1 + torch.arange(bsz, dtype=torch.int32).view(-1, 1) * 2
+    nblk = int(table.max()) + 1
+    hadamard = torch.rand((d, d), dtype=bf) * (d ** -0.5)
+    g = torch.Generator().manual_seed(7)
+    kv_state = torch.rand((nblk, 128, coff * d), generator=g)
+    score_state = torch.rand((nblk, 128, coff * d), generator=g)
+    return dict(x=x, sin=sin, cos=cos, wkv=wkv, wgate=wgate, ape=ape, weight=weight, kv_state=kv_state,
+                score_state=score_state, table=table, hadamard=hadamard,
+                start_pos=torch.tensor(starts, dtype=torch.int32), ratio=ratio, rotate=rotate, d=d)
+
+
+def load_compressor_golden(name):
+    z = np.load(os.path.join(GOLDEN, "compressor_small.npz"))
+    return dict(digests=json.loads(str(z[name + "_digests"])), out=from_bits16(z[name + "_out"], torch.bfloat16),
+                kv_state_sum=torch.from_numpy(z[name + "_kv_state_sum"]),
+                score_state_sum=torch.from_numpy(z[name + "_score_state_sum"]))
+
+
 def gen_mla_v4_inputs(seed, t, heads=64, h=4096):
     """Seeded inputs of the DeepSeek-V4 MLA prolog with realistic distributions: normal activations and weights,
     gamma near one, unit-circle cos / sin repeated per rotary pair."""

@@ -1005,6 +1005,117 @@ def test_hc_pre_bad_arguments():
 
 
 # --------------------------------------------------------------------------------------------------
+# DeepSeek-V4 KV compressor
+# --------------------------------------------------------------------------------------------------
+def _run_compressor(inp, kv_table=None, score_table=None):
+    import pypto_b200
+    from pypto_b200 import compressor_impl as cp
+    c = _cuda(inp)
+    kv_state, score_state = c["kv_state"].clone(), c["score_state"].clone()
+    out, kv2, sc2 = cp.npu_compressor(c["x"], kv_state, score_state, c["table"] if kv_table is None else kv_table.to(DEV),
+                                      c["table"] if score_table is None else score_table.to(DEV), c["sin"], c["cos"],
+                                      c["wkv"], c["wgate"], c["ape"], c["weight"], c["hadamard"], c["start_pos"],
+                                      inp["ratio"], 64, inp["rotate"])
+    pypto_b200.check_status()
+    assert kv2 is kv_state and sc2 is score_state          # updated in place and handed back
+    return out.cpu(), kv_state.cpu(), score_state.cpu()
+
+
+def _compressor_oracle(inp):
+    kv_state, score_state = inp["kv_state"].clone(), inp["score_state"].clone()
+    out = orc.compressor(inp["x"], kv_state, score_state, inp["table"], inp["table"], inp["sin"], inp["cos"], inp["wkv"],
+                         inp["wgate"], inp["ape"], inp["weight"], inp["hadamard"], inp["start_pos"], inp["ratio"], 64,
+                         inp["rotate"])
+    return out, kv_state, score_state
+
+
+def _assert_compressor_close(got, ref):
+    out, kv_state, score_state = got
+    rout, rkv, rsc = ref
+    # states: fp32 GEMM rows (another summation order than the CPU's) -- relative 1e-4 of the row scale
+    assert torch.allclose(kv_state, rkv, rtol=1e-4, atol=1e-4 * float(rkv.abs().max()))
+    assert torch.allclose(score_state, rsc, rtol=1e-4, atol=1e-4 * float(rsc.abs().max()))
+    # out: the reference's own rule (test_compressor.py: atol 1e-4, rtol 2^-7, 0.5 % of the elements may fall outside)
+    assert orc.reference_compare_count(out, rout, 1e-4, 0.0078125) <= 0.005 * out.numel()
+    assert torch.equal(out.float().abs().sum(-1) == 0, rout.float().abs().sum(-1) == 0)   # rows that did not compress
+
+
+@pytest.mark.parametrize("name", list(helpers.COMPRESSOR_CASES))
+def test_compressor_reference_golden_fixture(name):
+    g = helpers.load_compressor_golden(name)
+    inp = helpers.compressor_reference_inputs(name)
+    out, kv_state, score_state = _run_compressor(inp)
+    assert orc.reference_compare_count(out, g["out"], 1e-4, 0.0078125) <= 0.005 * out.numel()
+    assert torch.allclose(kv_state.double().sum(-1), g["kv_state_sum"], rtol=1e-5, atol=1e-2)
+    assert torch.allclose(score_state.double().sum(-1), g["score_state_sum"], rtol=1e-5, atol=1e-2)
+    _assert_compressor_close((out, kv_state, score_state), _compressor_oracle(inp))
+
+
+@pytest.mark.parametrize("ratio,rotate,d,starts,s1", [
+    (4, False, 512, [3, 4, 7, 8, 123, 124, 127, 128, 0], 1),       # every residue; windows that span two pages
+    (4, False, 512, [0, 1, 5, 250], 4),                             # four tokens per request: two compressions in one call
+    (128, False, 512, [127, 255, 383, 100], 1),
+    (128, False, 512, [125, 126, 254], 3),
+    (4, True, 128, [255, 3, 4, 11], 2),
+])
+def test_compressor_seeded_vs_oracle(ratio, rotate, d, starts, s1):
+    g = torch.Generator().manual_seed(1600 + ratio + d + s1)
+    bf = torch.bfloat16
+    b, coff, h = len(starts), (2 if ratio == 4 else 1), 4096
+    pages = 4
+    perm = torch.randperm(b * pages, generator=g).to(torch.int32).reshape(b, pages)
+    rows = min(b * s1, b * s1 // ratio + b)
+    ang = torch.rand((rows, 32), generator=g) * 6.2831853
+    inp = dict(
+        x=torch.randn((b, s1, h), generator=g).to(bf), sin=torch.sin(ang).repeat_interleave(2, -1).to(bf),
+        cos=torch.cos(ang).repeat_interleave(2, -1).to(bf), wkv=(torch.randn((coff * d, h), generator=g) * 0.02).to(bf),
+        wgate=(torch.randn((coff * d, h), generator=g) * 0.02).to(bf), ape=torch.randn((ratio, coff * d), generator=g) * 0.5,
+        weight=1 + 0.1 * torch.randn(d, generator=g), kv_state=torch.randn((b * pages, 128, coff * d), generator=g),
+        score_state=torch.randn((b * pages, 128, coff * d), generator=g), table=perm,
+        hadamard=(torch.randn((d, d), generator=g) * d ** -0.5).to(bf), start_pos=torch.tensor(starts, dtype=torch.int32),
+        ratio=ratio, rotate=rotate, d=d)
+    _assert_compressor_close(_run_compressor(inp), _compressor_oracle(inp))
+
+
+def test_compressor_bad_arguments_and_bad_pages():
+    import pypto_b200
+    from pypto_b200 import compressor_impl as cp
+    inp = helpers.compressor_reference_inputs("r4")
+    c = _cuda(inp)
+
+    def call(**over):
+        a = dict(c, **over)
+        return cp.npu_compressor(a["x"], a["kv_state"].clone(), a["score_state"].clone(), a["table"], a["table"], a["sin"],
+                                 a["cos"], a["wkv"], a["wgate"], a["ape"], a["weight"], a["hadamard"], a["start_pos"],
+                                 over.get("ratio", 4), over.get("rope", 64), over.get("rotate", False))
+
+    with pytest.raises(ValueError):
+        call(ratio=8)
+    with pytest.raises(ValueError):
+        call(rope=32)
+    with pytest.raises(ValueError):
+        call(rotate=1)
+    with pytest.raises(ValueError):
+        call(x=c["x"].float())
+    with pytest.raises(ValueError):
+        call(ape=c["ape"][:2].contiguous())
+    with pytest.raises(ValueError):
+        call(start_pos=c["start_pos"].long())
+    with pytest.raises(RuntimeError):
+        call(weight=inp["weight"])
+    bad = c["table"].clone()
+    bad[0, 1] = 10 ** 6                                   # request 0 writes position 255 -> page slot 1
+    call(table=bad)
+    with pytest.raises(RuntimeError):
+        pypto_b200.check_status()
+    call(start_pos=torch.tensor([128 * 100, 2, 6, 9], dtype=torch.int32, device=DEV))   # past the table's last column
+    with pytest.raises(RuntimeError):
+        pypto_b200.check_status()
+    call()
+    pypto_b200.check_status()
+
+
+# --------------------------------------------------------------------------------------------------
 # fused MLA prolog + indexer prolog
 # --------------------------------------------------------------------------------------------------
 def _run_mla(inp, ip):

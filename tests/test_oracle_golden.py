@@ -1,4 +1,5 @@
 """The CPU oracle against the fixtures produced by the unmodified reference goldens."""
+import pytest
 import torch
 
 import helpers
@@ -125,6 +126,21 @@ def test_hc_pre_oracle_matches_reference_golden():
     # Sinkhorn leaves a (nearly) doubly stochastic matrix
     y, post, comb = orc.hc_pre(**helpers.gen_hc_pre_inputs(3, 5))
     assert torch.allclose(comb.sum(-2), torch.ones(5, 4), atol=1e-4) and torch.allclose(comb.sum(-1), torch.ones(5, 4), atol=1e-3)
+
+
+@pytest.mark.parametrize("name", list(helpers.COMPRESSOR_CASES))
+def test_compressor_oracle_matches_reference_golden(name):
+    g = helpers.load_compressor_golden(name)
+    inp = helpers.compressor_reference_inputs(name)
+    for key, want in g["digests"].items():
+        assert helpers.digest(inp[key]) == want, f"regenerated input {key} differs from the reference's"
+    out = orc.compressor(inp["x"], inp["kv_state"], inp["score_state"], inp["table"], inp["table"], inp["sin"], inp["cos"],
+                         inp["wkv"], inp["wgate"], inp["ape"], inp["weight"], inp["hadamard"], inp["start_pos"],
+                         inp["ratio"], 64, inp["rotate"])
+    assert torch.allclose(out.float(), g["out"].float(), atol=1e-4, rtol=0.0078125)
+    # the state rows written by this call (row checksums of every page position)
+    assert torch.allclose(inp["kv_state"].double().sum(-1), g["kv_state_sum"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(inp["score_state"].double().sum(-1), g["score_state_sum"], rtol=1e-6, atol=1e-6)
 
 
 def test_sa_antiquant_oracle_matches_reference_golden():
