@@ -163,7 +163,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    _emit_json(line)
 
 
 def workload_config(args, world):
@@ -332,10 +332,34 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "stages": stage_info,
             "cpu_baseline": cpu,
         }
-        print(json.dumps(line), flush=True)
+        _emit_json(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+_JSON_FD = None
+
+
+def _reserve_stdout_for_json():
+    """stdout carries the one JSON line only.  Native libraries write to file descriptor 1 directly (NCCL prints its
+    version banner there when NCCL_DEBUG is set), so descriptor 1 is pointed at stderr for the rest of the run and
+    the JSON line goes out through a saved copy of the original descriptor."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit_json(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_JSON_FD, data)
 
 
 def main():
@@ -355,6 +379,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    _reserve_stdout_for_json()
     if args.cpu_requests is None:
         args.cpu_requests = min(args.batch, 64) if args.impl == "ours" else 4
     if args.impl == "reference":
