@@ -293,6 +293,8 @@ def test_scfa_reference_golden_fixture():
     (4, [2100, 4000], [2, 1], 128, {"holes": 37}),                             # 128 heads; -1 entries among the selected
     (5, [5000, 300], [1, 2], 32, {"topk": 200, "win_size": 64, "cmp_ratio": 8, "scale": 3.0}),   # other sizes, peaked softmax
     (6, [900], [5], 64, {"topk": 64, "win_size": 300, "cmp_ratio": 2}),        # window longer than two pages
+    (7, [5000], [1], 64, {}),                                                  # one token: fewer query rows than the 128-row tile
+    (8, [300], [1], 32, {"topk": 64}),
 ])
 def test_scfa_seeded_cases(seed, ori_seq, s1_list, nq, kw):
     d = helpers.gen_scfa_inputs(700 + seed, ori_seq, s1_list, nq=nq, **kw)
