@@ -307,6 +307,25 @@ def test_scfa_seeded_cases(seed, ori_seq, s1_list, nq, kw):
     assert torch.equal(out.float().abs().sum(-1) == 0, ref.float().abs().sum(-1) == 0)
 
 
+def test_scfa_reference_decode_shape_sampled_tokens():
+    """The reference's decode case (64 requests x 2 tokens, context 8192, 64 heads, 128 + 512 keys): sampled tokens
+    against the oracle, every row finite, and the result independent of the order of the selected indices up to
+    the rounding of another summation order."""
+    d = helpers.gen_scfa_inputs(760, [8192] * 64, [2] * 64)
+    out = _run_scfa(d)
+    assert torch.isfinite(out.float()).all() and (out.float().abs().sum(-1) > 0).all()
+    sample = [0, 1, 37, 64, 126, 127]
+    ref = orc.scfa(d["q"], d["actual_seq_q"], d["ori_kv"], d["cmp_kv"], d["ori_block_table"], d["cmp_block_table"],
+                   d["atten_sink"], d["seqused_kv"], d["cmp_sparse_indices"], d["nq"], d["softmax_scale"], d["win_size"],
+                   d["cmp_ratio"], d["block_size"], tokens=sample)
+    rows = torch.cat([torch.arange(t * 64, (t + 1) * 64) for t in sample])
+    _assert_attention_close(out[rows], ref[rows])
+    g = torch.Generator().manual_seed(1)
+    shuffled = dict(d, cmp_sparse_indices=d["cmp_sparse_indices"][:, torch.randperm(512, generator=g)].contiguous())
+    out2 = _run_scfa(shuffled)
+    assert torch.allclose(out2.float(), out.float(), rtol=2e-2, atol=2e-3)
+
+
 def test_scfa_sink_and_window_matter():
     """The sink only enters the denominator; dropping it, or the window, must change the result."""
     d = helpers.gen_scfa_inputs(770, [1000, 600], [1, 2])
