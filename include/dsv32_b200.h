@@ -276,11 +276,14 @@ typedef struct {
   int8_t* q;                      /* out int8 [t, 64, 128]                */
   void* weights;                  /* out fp16 [t, 64]                     */
   void* q_scale;                  /* out fp16 [t, 64]                     */
+  void* workspace;                /* >= dsv32_prolog_v4_workspace_bytes(t, h), 16-byte aligned */
+  size_t workspace_bytes;
   uint32_t* status;
   int32_t t, h;
 } Dsv32PrologV4Args;
 
 int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* args, void* cuda_stream);
+size_t dsv32_prolog_v4_workspace_bytes(int32_t t, int32_t h);
 
 /* ---------------------------------------------------------------------------------------
  * Fused element-wise stages of the MLA prolog (quant), the MLA half of

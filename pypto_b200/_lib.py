@@ -78,7 +78,8 @@ class PrologV4Args(C.Structure):
     _fields_ = [
         ("qr", c_void_p), ("idx_wq_b", c_void_p), ("x", c_void_p), ("weights_proj", c_void_p), ("cos", c_void_p),
         ("sin", c_void_p), ("hadamard", c_void_p), ("qr_scale", c_void_p), ("idx_wq_b_scale", c_void_p),
-        ("q", c_void_p), ("weights", c_void_p), ("q_scale", c_void_p), ("status", c_void_p), ("t", c_i32), ("h", c_i32),
+        ("q", c_void_p), ("weights", c_void_p), ("q_scale", c_void_p), ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t), ("status", c_void_p), ("t", c_i32), ("h", c_i32),
     ]
 
 
@@ -137,6 +138,7 @@ EXPORTS = {
     "dsv32_indexer_topk_noalloc": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_indexer_prolog_v4": (c_i32, [C.POINTER(PrologV4Args), c_void_p]),
+    "dsv32_prolog_v4_workspace_bytes": (c_size_t, [c_i32, c_i32]),
     "dsv32_mla_prolog_v4_stage": (c_i32, [C.POINTER(MlaV4StageArgs), c_i32, c_void_p]),
     "dsv32_compressor_update": (c_i32, [C.POINTER(CompressorArgs), c_void_p]),
     "dsv32_hc_pre": (c_i32, [C.POINTER(HcPreArgs), c_void_p]),

@@ -41,6 +41,13 @@ def same_device(*tensors):
     return dev
 
 
+def gemm_bf16_fp32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """bf16 [m, k] x bf16 [k, n] -> fp32 [m, n] on the tensor cores (library GEMM): the products of bf16 numbers
+    are exact in fp32 and the accumulation is fp32, so this is the fp32 product of the widened operands up to
+    the order of the summation, without materialising fp32 copies of the weights.  `b` may be a transposed view."""
+    return torch.mm(a, b, out_dtype=torch.float32)
+
+
 def ptr(t):
     return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
 

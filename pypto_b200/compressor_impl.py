@@ -7,8 +7,8 @@ cache row: per token kv = x @ wkv.T and score = x @ wgate.T + ape[pos % ratio] a
 when a window is complete its kv rows are summed with softmax(score rows) weights per column (ratio 4 mixes the
 first halves of the previous window with the second halves of the current one), RMS-normalised, given the
 interleaved rotary embedding on the last 64 dims and, with `rotate`, multiplied by a hadamard matrix.
-The two projections and the hadamard product are library GEMMs (cuBLAS through torch, fp32 operands as in the
-reference golden); the state update and the compression are one CUDA kernel.  `kv_state` and `score_state` are
+The two projections and the hadamard product are library GEMMs (cuBLAS through torch; bf16 operands with fp32
+accumulation and fp32 results, i.e. the reference golden's fp32 product up to summation order); the state update and the compression are one CUDA kernel.  `kv_state` and `score_state` are
 updated in place and returned with the new rows, as the reference does.  Work is only enqueued on the current stream.
 """
 from __future__ import annotations
@@ -61,9 +61,9 @@ def npu_compressor(x, kv_state, score_state, kv_block_table, score_block_table, 
                          hadamard, start_pos)
     lib = _lib.load()
     with torch.cuda.device(dev):
-        xf = x.reshape(b * s1, h).to(f32)
-        kv_total = torch.matmul(xf, wkv.to(f32).t())          # [b*s1, coff*d] fp32
-        score_total = torch.matmul(xf, wgate.to(f32).t())
+        x2 = x.reshape(b * s1, h)
+        kv_total = rt.gemm_bf16_fp32(x2, wkv.t())              # [b*s1, coff*d] fp32
+        score_total = rt.gemm_bf16_fp32(x2, wgate.t())
         a = _lib.CompressorArgs(rt.ptr(kv_total), rt.ptr(score_total), rt.ptr(ape), rt.ptr(weight), rt.ptr(kv_state),
                                 rt.ptr(score_state), rt.ptr(kv_block_table), rt.ptr(score_block_table), rt.ptr(sin),
                                 rt.ptr(cos), rt.ptr(start_pos), rt.ptr(out), rt.ptr(rt.status_word(dev)),

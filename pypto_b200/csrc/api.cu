@@ -344,6 +344,8 @@ int dsv32_topk_select(const Dsv32TopkArgs* a, void* cuda_stream) {
 }
 
 // ---- indexer prolog -----------------------------------------------------------------------------------
+size_t dsv32_prolog_v4_workspace_bytes(int32_t t, int32_t h) { return align_up(prolog_v4_workspace_bytes(t, h), 256); }
+
 int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* a, void* cuda_stream) {
   REQUIRE(a != nullptr, "prolog v4: args is NULL");
   REQUIRE(a->t >= 0, "prolog v4: bad t=%d", a->t);
@@ -356,7 +358,13 @@ int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* a, void* cuda_stream) {
               reinterpret_cast<uintptr_t>(a->hadamard) % 16 == 0 && reinterpret_cast<uintptr_t>(a->q) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(a->cos) % 4 == 0 && reinterpret_cast<uintptr_t>(a->sin) % 4 == 0,
           "prolog v4: qr / idx_wq_b / hadamard / q must be 16-byte aligned, cos / sin 4-byte aligned");
+  const size_t need_v4 = prolog_v4_workspace_bytes(a->t, a->h);
+  if (a->workspace == nullptr || a->workspace_bytes < need_v4 || reinterpret_cast<uintptr_t>(a->workspace) % 16 != 0) {
+    set_error("prolog v4: workspace of %zu bytes (16-byte aligned) required, got %zu", need_v4, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
   PrologParams p{};
+  p.partial = static_cast<float*>(a->workspace);
   p.x = static_cast<const __nv_bfloat16*>(a->x);
   p.q_norm = a->qr;
   p.q_norm_scale = a->qr_scale;

@@ -104,6 +104,7 @@ struct PrologParams {
 int launch_prolog(const PrologParams& p, cudaStream_t stream);
 int launch_prolog_tc(const PrologParams& p, cudaStream_t stream);
 int launch_prolog_v4(const PrologParams& p, int h, float w_scale, cudaStream_t stream);
+size_t prolog_v4_workspace_bytes(int t, int h);
 size_t prolog_workspace_bytes(int t);
 
 

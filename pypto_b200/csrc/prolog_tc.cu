@@ -17,7 +17,7 @@
 // (models/deepseek_v4/lightning_indexer_prolog_quant_v4_impl.py:118-266): reduction length 1024 instead of 1536
 // and, in epilogue 1, the rotary embedding on dims 64..127 in its interleaved, inverse form
 // (out[2i] = x[2i] cos[2i] + x[2i+1] sin[2i], out[2i+1] = x[2i+1] cos[2i+1] - x[2i] sin[2i+1]).  That operator has
-// no K path; its head weights come from prolog_v4_weights_kernel.
+// no K path; its head weights come from prolog_v4_weights_partial_kernel / _finish_kernel.
 #include <mutex>
 
 #include "kernels.cuh"
@@ -479,35 +479,79 @@ int launch_prolog_tc(const PrologParams& p, cudaStream_t stream) {
 
 // ---------------------------------------------------------------------------------------------------------
 // DeepSeek-V4 indexer prolog: head weights = fp16( float(bf16(x . w_proj)) * scale )
-// (lightning_indexer_prolog_quant_v4_impl.py:253-266).  One CTA per token; thread (k slice, head) walks its slice
-// of the reduction with the weight row read coalesced (64 heads = 128 bytes), the four slices are summed in a
-// fixed order.  w_proj (h x 64 bf16, 512 KB at h = 4096) stays in L2 across the CTAs.
+// (lightning_indexer_prolog_quant_v4_impl.py:253-266).  The reduction over the hidden size is split into slices of
+// 512 and the tokens into tiles of 16: a CTA stages its 16 x 512 piece of x in shared memory (as floats) and
+// thread (k group, head) walks a quarter of the slice, reading one weight (coalesced over the 64 heads) for 16
+// fused multiply-adds with broadcast x values.  Partial sums [slice][token][head] are added in a fixed order by
+// the finish kernel, which rounds to bf16, scales and writes fp16.
 // ---------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) prolog_v4_weights_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                const __nv_bfloat16* __restrict__ w_proj,
-                                                                __half* __restrict__ weights, int h, float scale) {
-  extern __shared__ float xs[];  // h floats, then 4 x 64 partial sums
-  float* part = xs + h;
-  const int tok = blockIdx.x, tid = threadIdx.x;
-  const __nv_bfloat16* xrow = x + static_cast<size_t>(tok) * h;
-  for (int k = tid; k < h; k += 256) xs[k] = __bfloat162float(xrow[k]);
-  __syncthreads();
-  const int n = tid & 63, slice = tid >> 6;
-  const int per = (h + 3) / 4;
-  const int k0 = slice * per, k1 = min(h, k0 + per);
-  float acc0 = 0.f, acc1 = 0.f;
-  int k = k0;
-  for (; k + 1 < k1; k += 2) {
-    acc0 = fmaf(xs[k], __bfloat162float(w_proj[static_cast<size_t>(k) * 64 + n]), acc0);
-    acc1 = fmaf(xs[k + 1], __bfloat162float(w_proj[static_cast<size_t>(k + 1) * 64 + n]), acc1);
+constexpr int kW4Tok = 16, kW4Slice = 512, kW4Threads = 256;
+
+__global__ void __launch_bounds__(kW4Threads) prolog_v4_weights_partial_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                               const __nv_bfloat16* __restrict__ w_proj,
+                                                                               float* __restrict__ partial, int t, int h) {
+  __shared__ __align__(16) float x_s[kW4Tok * kW4Slice];   // 32 KB
+  __shared__ float red_s[3 * kW4Tok * 64];                 // 12 KB
+  const int tid = threadIdx.x;
+  const int t0 = blockIdx.x * kW4Tok, k0 = blockIdx.y * kW4Slice;
+  const int klen = min(kW4Slice, h - k0);
+  for (int i = tid; i < kW4Tok * kW4Slice; i += kW4Threads) {
+    const int tok = i / kW4Slice, k = i % kW4Slice;
+    x_s[i] = (t0 + tok < t && k < klen) ? __bfloat162float(x[static_cast<size_t>(t0 + tok) * h + k0 + k]) : 0.f;
   }
-  if (k < k1) acc0 = fmaf(xs[k], __bfloat162float(w_proj[static_cast<size_t>(k) * 64 + n]), acc0);
-  part[slice * 64 + n] = acc0 + acc1;
   __syncthreads();
-  if (tid < 64) {
-    const float sum = (part[tid] + part[64 + tid]) + (part[128 + tid] + part[192 + tid]);
-    weights[static_cast<size_t>(tok) * 64 + tid] = __float2half_rn(__fmul_rn(bf16_round(sum), scale));
+  const int n = tid & 63, kg = tid >> 6;
+  float acc[kW4Tok];
+#pragma unroll
+  for (int i = 0; i < kW4Tok; ++i) acc[i] = 0.f;
+  const int kb = kg * (kW4Slice / 4), ke = min(kb + kW4Slice / 4, klen);
+  const __nv_bfloat16* wp = w_proj + static_cast<size_t>(k0) * 64 + n;
+  int k = kb;
+  for (; k + 4 <= ke; k += 4) {
+    const float w0 = __bfloat162float(wp[static_cast<size_t>(k) * 64]), w1 = __bfloat162float(wp[static_cast<size_t>(k + 1) * 64]);
+    const float w2 = __bfloat162float(wp[static_cast<size_t>(k + 2) * 64]), w3 = __bfloat162float(wp[static_cast<size_t>(k + 3) * 64]);
+#pragma unroll
+    for (int i = 0; i < kW4Tok; ++i) {
+      const float4 xv = *reinterpret_cast<const float4*>(&x_s[i * kW4Slice + k]);   // broadcast
+      acc[i] = fmaf(xv.x, w0, acc[i]);
+      acc[i] = fmaf(xv.y, w1, acc[i]);
+      acc[i] = fmaf(xv.z, w2, acc[i]);
+      acc[i] = fmaf(xv.w, w3, acc[i]);
+    }
   }
+  for (; k < ke; ++k) {
+    const float w0 = __bfloat162float(wp[static_cast<size_t>(k) * 64]);
+#pragma unroll
+    for (int i = 0; i < kW4Tok; ++i) acc[i] = fmaf(x_s[i * kW4Slice + k], w0, acc[i]);
+  }
+  if (kg > 0) {
+#pragma unroll
+    for (int i = 0; i < kW4Tok; ++i) red_s[((kg - 1) * kW4Tok + i) * 64 + n] = acc[i];
+  }
+  __syncthreads();
+  if (kg == 0) {
+#pragma unroll
+    for (int i = 0; i < kW4Tok; ++i) {
+      if (t0 + i < t) {
+        const float s = ((acc[i] + red_s[i * 64 + n]) + red_s[(kW4Tok + i) * 64 + n]) + red_s[(2 * kW4Tok + i) * 64 + n];
+        partial[(static_cast<size_t>(blockIdx.y) * t + t0 + i) * 64 + n] = s;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(64) prolog_v4_weights_finish_kernel(const float* __restrict__ partial,
+                                                                      __half* __restrict__ weights, int t, int slices,
+                                                                      float scale) {
+  const int tok = blockIdx.x, n = threadIdx.x;
+  float s = 0.f;
+  for (int g = 0; g < slices; ++g) s += partial[(static_cast<size_t>(g) * t + tok) * 64 + n];
+  weights[static_cast<size_t>(tok) * 64 + n] = __float2half_rn(__fmul_rn(bf16_round(s), scale));
+}
+
+size_t prolog_v4_workspace_bytes(int t, int h) {
+  if (t <= 0 || h <= 0) return 0;
+  return static_cast<size_t>((h + kW4Slice - 1) / kW4Slice) * t * 64 * sizeof(float);
 }
 
 int launch_prolog_v4(const PrologParams& p, int h, float w_scale, cudaStream_t stream) {
@@ -518,11 +562,6 @@ int launch_prolog_v4(const PrologParams& p, int h, float w_scale, cudaStream_t s
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&w_map, p.w_qb, 1024, 8192, 128, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&h_map, p.had_q, 128, 256, 128, 128);
   if (rc != DSV32_OK) return rc;
-  const size_t w_smem = (static_cast<size_t>(h) + 256) * sizeof(float);
-  if (w_smem > 200 * 1024) {
-    set_error("prolog v4: hidden size %d does not fit the weights kernel's shared memory", h);
-    return DSV32_ERR_UNSUPPORTED;
-  }
   // the Q path and the weights path are independent: fork the weights kernel onto the side stream
   PrologFork* fk = prolog_fork_for_device();
   cudaStream_t w_stream = stream;
@@ -534,10 +573,16 @@ int launch_prolog_v4(const PrologParams& p, int h, float w_scale, cudaStream_t s
       fk = nullptr;
     }
   }
-  cudaFuncSetAttribute(prolog_v4_weights_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w_smem);
-  prolog_v4_weights_kernel<<<p.t, 256, w_smem, w_stream>>>(p.x, p.w_proj, p.weights, h, w_scale);
+  const int slices = (h + kW4Slice - 1) / kW4Slice;
+  prolog_v4_weights_partial_kernel<<<dim3((p.t + kW4Tok - 1) / kW4Tok, slices), kW4Threads, 0, w_stream>>>(
+      p.x, p.w_proj, p.partial, p.t, h);
   count_launch();
-  rc = check_launch("prolog_v4_weights_kernel");
+  rc = check_launch("prolog_v4_weights_partial_kernel");
+  if (rc == DSV32_OK) {
+    prolog_v4_weights_finish_kernel<<<p.t, 64, 0, w_stream>>>(p.partial, p.weights, p.t, slices, w_scale);
+    count_launch();
+    rc = check_launch("prolog_v4_weights_finish_kernel");
+  }
   if (fk != nullptr && cudaEventRecord(fk->join, fk->side) != cudaSuccess) rc = check_launch("prolog side stream");
   if (rc == DSV32_OK) {
     cudaFuncSetAttribute(prolog_q_tc_kernel<kVariantV4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPqSmemBytes);

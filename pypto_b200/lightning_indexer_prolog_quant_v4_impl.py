@@ -59,9 +59,11 @@ def quant_lightning_indexer_prolog_kernel(qr, idx_wq_b, x, weights_proj, cos, si
     dev = rt.same_device(qr, idx_wq_b, x, weights_proj, cos, sin, hadamard, qr_scale, idx_wq_b_scale, q, weights, q_scale)
     lib = _lib.load()
     with torch.cuda.device(dev):
+        ws_bytes = lib.dsv32_prolog_v4_workspace_bytes(t, h)
+        ws = rt.workspace(ws_bytes, dev)
         a = _lib.PrologV4Args(rt.ptr(qr), rt.ptr(idx_wq_b), rt.ptr(x), rt.ptr(weights_proj), rt.ptr(cos), rt.ptr(sin),
                               rt.ptr(hadamard), rt.ptr(qr_scale), rt.ptr(idx_wq_b_scale), rt.ptr(q), rt.ptr(weights),
-                              rt.ptr(q_scale), rt.ptr(rt.status_word(dev)), t, h)
+                              rt.ptr(q_scale), rt.ptr(ws), int(ws_bytes), rt.ptr(rt.status_word(dev)), t, h)
         rt.check(lib.dsv32_indexer_prolog_v4(C.byref(a), rt.stream_ptr(dev)), "quant_lightning_indexer_prolog")
     return None
 

@@ -6,8 +6,8 @@ mla_prolog_v4_in :567-629, mla_prolog_quant_pypto :655-658; compute mla_prolog_v
   q            = bf16(RMSNorm_per_head(int32(qr @ wq_b) * qr_scale * wq_b_scale)), heads of 512 dims, interleaved
                  rotary embedding on the last 64 dims of each head                (the query of the V4 attention)
   kv           = bf16(RMSNorm(x @ wkv) * gamma_ckv), rotary embedding on its last 64 dims   (the new cache row)
-The three projections are library GEMMs (cuBLAS through torch: bf16 inputs widened to fp32 as in the reference
-golden; int8 with int32 accumulation); everything between them is one fused CUDA kernel per stage.  Weights are
+The three projections are library GEMMs (cuBLAS through torch: bf16 operands with fp32 accumulation and fp32 results, which is
+the reference golden's fp32 product of the widened operands up to summation order; int8 with int32 accumulation); everything between them is one fused CUDA kernel per stage.  Weights are
 plain row-major [K, N].  Work is only enqueued on the current CUDA stream.
 """
 from __future__ import annotations
@@ -51,11 +51,6 @@ class MlaPrologV4Configs:
     chunk_size: int = 2
 
 
-def _fp32_gemm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """bf16 [m,k] x bf16 [k,n] -> fp32 [m,n], operands widened to fp32 as the reference golden does."""
-    return torch.matmul(a.to(torch.float32), b.to(torch.float32))
-
-
 def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_sin, wq_b_scale, q_out, kv_out, qr_out,
                   qr_scale_out, attrs=None, configs=None, tile_configs=None):
     """mla_prolog_quant_v4_impl.py:528-564: 9 inputs (note gamma before cos / sin here), 4 outputs written in place,
@@ -92,7 +87,7 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
     lib = _lib.load()
     with torch.cuda.device(dev):
         stream = rt.stream_ptr(dev)
-        q_a = _fp32_gemm(token_x, wq_a)                                   # [t, 1024] fp32
+        q_a = rt.gemm_bf16_fp32(token_x, wq_a)                                   # [t, 1024] fp32
         a = _lib.MlaV4StageArgs(rt.ptr(q_a), rt.ptr(gamma_cq), rt.ptr(qr_out), rt.ptr(qr_scale_out), None,
                                 rt.ptr(wq_b_scale), rt.ptr(q_out), None, rt.ptr(gamma_ckv), rt.ptr(kv_out),
                                 rt.ptr(rope_cos), rt.ptr(rope_sin), t, heads, 0, 1, eps)
@@ -100,7 +95,7 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
         q_b = _int8_gemm(qr_out, wq_b)                                    # [>= t, heads * 512] int32
         a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]
         rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 1, stream), "mla_prolog_v4 (q dequant + norm + rope)")
-        kv_a = _fp32_gemm(token_x, wkv)                                   # [t, 512] fp32
+        kv_a = rt.gemm_bf16_fp32(token_x, wkv)                                   # [t, 512] fp32
         a.kv_a = rt.ptr(kv_a)
         rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 2, stream), "mla_prolog_v4 (kv norm + rope)")
     return None
