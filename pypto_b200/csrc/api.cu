@@ -554,6 +554,8 @@ int dsv32_compressor_update(const Dsv32CompressorArgs* a, void* cuda_stream) {
   REQUIRE(a->kv_total && a->score_total && a->ape && a->weight && a->kv_state && a->score_state &&
               a->kv_block_table && a->score_block_table && a->sin && a->cos && a->start_pos && a->out,
           "compressor: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->kv_state) % 16 == 0 && reinterpret_cast<uintptr_t>(a->score_state) % 16 == 0,
+          "compressor: the states must be 16-byte aligned");
   CompressorParams p{};
   p.kv_total = a->kv_total;
   p.score_total = a->score_total;

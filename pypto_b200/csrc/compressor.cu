@@ -10,8 +10,9 @@
 //       request whose start position is below the ratio has no previous window (weight 0)
 //     then bf16 -> RMSNorm * weight -> bf16 -> interleaved rotary embedding on the last 64 dims -> out[b]
 // One CTA per request; its tokens are handled in order because a later token's compression reads the rows an
-// earlier one wrote.  Columns are spread over the threads, so the softmax over rows needs no communication;
-// only the RMSNorm sum and the rotary partner go through shared memory.
+// earlier one wrote.  With ratio 4 a thread owns a column and walks its 8 rows; with ratio 128 the threads are
+// (four columns) x (a group of the 128 rows), each keeps a running maximum / sum / weighted sum with 16-byte loads
+// and the row groups are merged through shared memory, as are the RMSNorm sum and the rotary partner.
 #include "kernels.cuh"
 
 namespace dsv32 {
@@ -25,6 +26,7 @@ __device__ __forceinline__ float comp_bf16r(float x) { return __bfloat162float(_
 __global__ void __launch_bounds__(kCompThreads) compressor_update_kernel(CompressorParams p) {
   __shared__ float val_s[kCompMaxD];
   __shared__ float red_s[kCompThreads / 32];
+  __shared__ float merge_s[kCompThreads * 4 * 3];   // (maximum, sum, weighted sum) of the row groups 1.. per column
   const int b = blockIdx.x, tid = threadIdx.x;
   const int d = p.d, cd = p.coff * p.d, ratio = p.ratio;
   const int start = p.start_pos[b];
@@ -82,21 +84,71 @@ __global__ void __launch_bounds__(kCompThreads) compressor_update_kernel(Compres
     }
     // ---- per column: softmax over the rows, weighted sum ------------------------------------------------------
     float sq = 0.f;
-    for (int c = tid; c < d; c += kCompThreads) {
-      float m = -INFINITY;
-      for (int r = 0; r < pre_rows; ++r) m = fmaxf(m, sc0[static_cast<size_t>(r) * cd + c]);
-      for (int r = 0; r < nrows; ++r) m = fmaxf(m, sc1[static_cast<size_t>(r) * cd + c]);
-      float sum = 0.f;
-      for (int r = 0; r < pre_rows; ++r) sum += expf(sc0[static_cast<size_t>(r) * cd + c] - m);
-      for (int r = 0; r < nrows; ++r) sum += expf(sc1[static_cast<size_t>(r) * cd + c] - m);
-      float acc = 0.f;
-      for (int r = 0; r < pre_rows; ++r)
-        acc += kv0[static_cast<size_t>(r) * cd + c] * __fdiv_rn(expf(sc0[static_cast<size_t>(r) * cd + c] - m), sum);
-      for (int r = 0; r < nrows; ++r)
-        acc += kv1[static_cast<size_t>(r) * cd + c] * __fdiv_rn(expf(sc1[static_cast<size_t>(r) * cd + c] - m), sum);
-      const float v = comp_bf16r(acc);
-      val_s[c] = v;
-      sq += v * v;
+    if (!overlap && (d & 3) == 0 && (kCompThreads % (d / 4)) == 0) {
+      // 128 rows: threads = (group of four columns) x (group of rows); each walks its rows once with 16-byte
+      // loads, keeping a running maximum, sum and weighted sum per column; the row groups are then merged.
+      const int ncg = d / 4, nrg = kCompThreads / ncg;
+      const int cg = tid % ncg, rg = tid / ncg;
+      const int rows_per = (kCompPage + nrg - 1) / nrg;
+      const int r0 = rg * rows_per, r1 = min(kCompPage, r0 + rows_per);
+      float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, sm[4] = {0.f, 0.f, 0.f, 0.f}, ac[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int r = r0; r < r1; ++r) {
+        const float4 s4 = *reinterpret_cast<const float4*>(sc1 + static_cast<size_t>(r) * cd + 4 * cg);
+        const float4 k4 = *reinterpret_cast<const float4*>(kv1 + static_cast<size_t>(r) * cd + 4 * cg);
+        const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float mn = fmaxf(m[j], sv[j]);
+          const float f = expf(m[j] - mn), e = expf(sv[j] - mn);   // exp(-inf) = 0 on the first row
+          sm[j] = sm[j] * f + e;
+          ac[j] = ac[j] * f + kv[j] * e;
+          m[j] = mn;
+        }
+      }
+      if (rg > 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          merge_s[((rg - 1) * d + 4 * cg + j) * 3 + 0] = m[j];
+          merge_s[((rg - 1) * d + 4 * cg + j) * 3 + 1] = sm[j];
+          merge_s[((rg - 1) * d + 4 * cg + j) * 3 + 2] = ac[j];
+        }
+      }
+      __syncthreads();
+      if (rg == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float mm = m[j];
+          for (int g = 1; g < nrg; ++g) mm = fmaxf(mm, merge_s[((g - 1) * d + 4 * cg + j) * 3]);
+          float f = expf(m[j] - mm);
+          float st = sm[j] * f, at = ac[j] * f;
+          for (int g = 1; g < nrg; ++g) {
+            const float* q = &merge_s[((g - 1) * d + 4 * cg + j) * 3];
+            f = expf(q[0] - mm);
+            st += q[1] * f;
+            at += q[2] * f;
+          }
+          const float v = comp_bf16r(__fdiv_rn(at, st));
+          val_s[4 * cg + j] = v;
+          sq += v * v;
+        }
+      }
+    } else {
+      for (int c = tid; c < d; c += kCompThreads) {
+        float m = -INFINITY;
+        for (int r = 0; r < pre_rows; ++r) m = fmaxf(m, sc0[static_cast<size_t>(r) * cd + c]);
+        for (int r = 0; r < nrows; ++r) m = fmaxf(m, sc1[static_cast<size_t>(r) * cd + c]);
+        float sum = 0.f;
+        for (int r = 0; r < pre_rows; ++r) sum += expf(sc0[static_cast<size_t>(r) * cd + c] - m);
+        for (int r = 0; r < nrows; ++r) sum += expf(sc1[static_cast<size_t>(r) * cd + c] - m);
+        float acc = 0.f;
+        for (int r = 0; r < pre_rows; ++r)
+          acc += kv0[static_cast<size_t>(r) * cd + c] * __fdiv_rn(expf(sc0[static_cast<size_t>(r) * cd + c] - m), sum);
+        for (int r = 0; r < nrows; ++r)
+          acc += kv1[static_cast<size_t>(r) * cd + c] * __fdiv_rn(expf(sc1[static_cast<size_t>(r) * cd + c] - m), sum);
+        const float v = comp_bf16r(acc);
+        val_s[c] = v;
+        sq += v * v;
+      }
     }
     // ---- RMSNorm * weight -> bf16 ---------------------------------------------------------------------------
 #pragma unroll
