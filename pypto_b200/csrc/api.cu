@@ -181,8 +181,8 @@ int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* a, void* cuda_s
 // ---- DeepSeek-V4 sparse compress attention ------------------------------------------------------------------
 size_t dsv32_scfa_workspace_bytes(int32_t t, int32_t topk, int32_t win_size) {
   if (t <= 0 || topk < 0 || win_size < 0) return 0;
-  // cache row of every listed key + the length of every token's list
-  return align_up(static_cast<size_t>(t) * (static_cast<size_t>(topk) + win_size) * sizeof(int32_t), 256) +
+  // cache row of every listed key (one more slot: the union window of two paired tokens) + the length of every list
+  return align_up(static_cast<size_t>(t) * (static_cast<size_t>(topk) + win_size + 1) * sizeof(int32_t), 256) +
          align_up(static_cast<size_t>(t) * sizeof(int32_t), 256);
 }
 
@@ -227,7 +227,10 @@ int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
   p.rows = a->ori_rows;
   p.rows2 = a->cmp_rows;
   p.b = a->b; p.s1 = 1; p.t_total = a->t; p.nq = a->n_q;
-  p.topk = a->topk + a->win_size;  // length of a token's key list
+  p.topk = a->topk + a->win_size + 1;  // slots of a key list (the union window of two paired tokens is one longer)
+  // tokens 2k, 2k+1 of a request share a CTA when the key lists do not come from an index tensor and the heads
+  // of both fit the 128-row tile
+  p.pair = (a->n_q <= 64 && (a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED || a->topk == 0)) ? 1 : 0;
   p.sel_topk = a->topk; p.win_size = a->win_size; p.cmp_ratio = a->cmp_ratio;
   p.cmp_dense = a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED ? 1 : 0;
   p.block_size = a->block_size;
@@ -244,7 +247,7 @@ int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
   char* ws = static_cast<char*>(a->workspace);
   p.row_ids = reinterpret_cast<int32_t*>(ws);
   p.key_counts = reinterpret_cast<int32_t*>(
-      ws + align_up(static_cast<size_t>(a->t) * (static_cast<size_t>(a->topk) + a->win_size) * sizeof(int32_t), 256));
+      ws + align_up(static_cast<size_t>(a->t) * (static_cast<size_t>(a->topk) + a->win_size + 1) * sizeof(int32_t), 256));
   return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 

@@ -127,7 +127,13 @@ __global__ void __launch_bounds__(256) sfa_row_ids_kernel(SfaParams p) {
 // rows of the compressed cache named by the first min(max(seq / cmp_ratio - s1 + 1 + i, 0), sel_topk) entries of
 // the token's index row (paged by block_table2)  (sparse_compress_flash_attention_impl.py:83-131) -- or, with
 // cmp_dense, every compressed position below cur_len / cmp_ratio (compress_flash_attention_impl.py:160-186).
-// An entry is row + 1, with bit 31 set for a row of the compressed cache; 0 = no key.
+// An entry is row + 1 in bits 0..28, bit 29 = "a key of this token", bit 31 = row of the compressed cache;
+// 0 = no key.
+// With p.pair (at most 64 heads, key lists that do not depend on an index tensor) the tokens 2k and 2k+1 of a
+// request share one CTA: lanes 0..63 of the M = 128 tile are the heads of the first, lanes 64..127 those of the
+// second.  The list is then the union of both lists -- they differ in one window position and at most one
+// compressed position -- with bit 29 / bit 30 = member of the first / second token's list; it is stored in the
+// first token's slot, and the second token's count is -1 ("done by the partner").
 __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
   const int tok = blockIdx.y;
   const int j = blockIdx.x * 256 + threadIdx.x;
@@ -140,18 +146,29 @@ __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
   }
   const int bi = lo;
   const int q0 = __ldg(p.seq_q + bi), q1 = __ldg(p.seq_q + bi + 1);
-  int out = 0, win = 0, sel = 0;
+  uint32_t out = 0;
+  int count = 0;
   if (tok < q0 || tok >= q1) {
     if (j == 0) report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, bi);
+  } else if (p.pair && ((tok - q0) & 1)) {
+    count = -1;  // second token of a pair
   } else {
     const int s1 = q1 - q0, si = tok - q0;
     const int seq = __ldg(p.act_seq + bi);
-    const int cur_len = max(seq - s1 + 1 + si, 0);
-    win = min(cur_len, p.win_size);
-    sel = p.cmp_dense ? min(cur_len / p.cmp_ratio, p.sel_topk)
-                      : min(max(seq / p.cmp_ratio - s1 + 1 + si, 0), p.sel_topk);
-    if (j < win) {
-      const int pos = cur_len - win + j;
+    const bool has_b = p.pair && si + 1 < s1;
+    // first token (a), second token (b = a + 1 position) of the pair; without pairing only a
+    const int len_a = max(seq - s1 + 1 + si, 0), len_b = has_b ? max(seq - s1 + 2 + si, 0) : len_a;
+    const int win_a = min(len_a, p.win_size), win_b = min(len_b, p.win_size);
+    const int sel_a = p.cmp_dense ? min(len_a / p.cmp_ratio, p.sel_topk)
+                                  : min(max(seq / p.cmp_ratio - s1 + 1 + si, 0), p.sel_topk);
+    const int sel_b = has_b ? min(len_b / p.cmp_ratio, p.sel_topk) : sel_a;   // pairs only exist with cmp_dense / no index
+    const int w_start = len_a - win_a;              // first window position of the union (b's window starts later or equal)
+    const int w_len = len_b - w_start;              // union window: [w_start, len_b)
+    const int sel_u = max(sel_a, sel_b);
+    count = w_len + sel_u;
+    if (j < w_len) {
+      const int pos = w_start + j;
+      const uint32_t mem = (pos < len_a ? 1u : 0u) | ((has_b && pos >= len_b - win_b) ? 2u : 0u);
       const int lb = pos / p.block_size;
       if (lb >= p.max_blocks) {
         report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, pos);
@@ -159,10 +176,12 @@ __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
         const int pb = __ldg(p.block_table + static_cast<size_t>(bi) * p.max_blocks + lb);
         const long long row = static_cast<long long>(pb) * p.block_size + pos % p.block_size;
         if (pb < 0 || row >= p.rows) report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, pos);
-        else out = static_cast<int>(row) + 1;
+        else out = (static_cast<uint32_t>(row) + 1u) | (mem << 29);
       }
-    } else if (j < win + sel) {
-      const int idx = p.cmp_dense ? j - win : __ldg(p.topk_idx + static_cast<size_t>(tok) * p.sel_topk + (j - win));
+    } else if (j < count) {
+      const int e = j - w_len;
+      const int idx = (p.cmp_dense || p.topk_idx == nullptr) ? e : __ldg(p.topk_idx + static_cast<size_t>(tok) * p.sel_topk + e);
+      const uint32_t mem = (e < sel_a ? 1u : 0u) | ((has_b && e < sel_b) ? 2u : 0u);
       if (idx >= 0) {
         const int lb = idx / p.block_size;
         if (lb >= p.max_blocks2) {
@@ -171,13 +190,13 @@ __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
           const int pb = __ldg(p.block_table2 + static_cast<size_t>(bi) * p.max_blocks2 + lb);
           const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
           if (pb < 0 || row >= p.rows2) report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, idx);
-          else out = static_cast<int>((static_cast<uint32_t>(row) + 1u) | 0x80000000u);
+          else out = (static_cast<uint32_t>(row) + 1u) | (mem << 29) | 0x80000000u;
         }
       }
     }
   }
-  p.row_ids[static_cast<size_t>(tok) * p.topk + j] = out;
-  if (j == 0) p.key_counts[tok] = win + sel;
+  p.row_ids[static_cast<size_t>(tok) * p.topk + j] = static_cast<int>(out);
+  if (j == 0) p.key_counts[tok] = count;
 }
 
 template <int kMode>
@@ -206,8 +225,12 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
   constexpr bool kCompress = kMode == kModeCompress;
   constexpr int kSteps = kCompress ? 32 : 36;  // 16-dim MMA steps of one S tile (no rope dims in mode 2)
   int cnt;
+  int live_rows = p.nq;   // lanes (query rows) of the M = 128 tile that belong to this CTA's token(s)
   if constexpr (kCompress) {
-    cnt = min(max(p.key_counts[tok], 0), p.topk);
+    const int raw = p.key_counts[tok];
+    if (raw < 0) return;  // second token of a pair: its heads are lanes 64.. of the partner's CTA
+    cnt = min(raw, p.topk);
+    if (p.pair && tok + 1 < p.t_total && p.key_counts[tok + 1] < 0) live_rows = 2 * p.nq;
   } else {
     const int bi = tok / p.s1, si = tok % p.s1;
     cnt = min(max(p.act_seq[bi] - p.s1 + 1 + si, 0), p.topk);
@@ -220,7 +243,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
   if (ntiles == 0) {  // nothing to attend to: zero row block (uniform for the CTA)
     for (int i = tid; i < 128 * 64; i += kStThreads) {
       const int h = i >> 6, c = i & 63;  // 64 chunks of 4 dims
-      if (h >= p.nq) continue;
+      if (h >= live_rows) continue;
       if (p.splits == 1) {
         *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(tok) * p.nq + h) * kKvLora + half * 256 + c * 4) =
             make_uint2(0u, 0u);
@@ -322,7 +345,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (!kCompress || head < p.nq) v = __ldg(qrow + c * 8 + j);
+          if (!kCompress || head < live_rows) v = __ldg(qrow + c * 8 + j);
           r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
         }
         tmem_st_32x32b_x32(tmem_base + lane_addr + kColQ + c * 32, r);
@@ -344,13 +367,16 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       tmem_ld_32x32b_x32(s_addr + 32, r1);
       tmem_ld_wait();
       // Masking is only needed when the tile holds an invalid key (tail of the list, or a -1 entry).
+      // A flag holds membership bits: bit 0 = a key of the token in lanes 0..63 (the only token unless two share
+      // the CTA), bit 1 = a key of the token in lanes 64..127; this warp's lanes all belong to one of them.
       const int* vm = valid_s + s * kStTile;
-      const bool all_valid = __all_sync(0xffffffffu, (vm[lane] & vm[32 + lane]) != 0);
+      const int hb = !kCompress ? 1 : (head < p.nq ? 1 : (head < live_rows ? 2 : 3));   // idle lanes take every key
+      const bool all_valid = __all_sync(0xffffffffu, (vm[lane] & vm[32 + lane] & hb) != 0);
       if (!all_valid) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          if (!vm[j]) r0[j] = 0xff800000u;       // -inf
-          if (!vm[32 + j]) r1[j] = 0xff800000u;
+          if (!(vm[j] & hb)) r0[j] = 0xff800000u;       // -inf
+          if (!(vm[32 + j] & hb)) r1[j] = 0xff800000u;
         }
       }
       float m_raw = -INFINITY;  // row maximum of the raw scores (the softmax scale is positive)
@@ -428,10 +454,11 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     if (ok) {
       tc_fence_after();
       if constexpr (kCompress) {  // the sink joins the denominator only: + exp(sink - max), in the units of m_run
-        if (head < p.nq && m_run != -INFINITY) l_run += exp2f(fmaf(__ldg(p.sinks + head), 1.4426950408889634f, -m_run));
+        if (head < live_rows && m_run != -INFINITY)
+          l_run += exp2f(fmaf(__ldg(p.sinks + (head >= p.nq ? head - p.nq : head)), 1.4426950408889634f, -m_run));
       }
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      if (kCompress && head >= p.nq) {
+      if (kCompress && head >= live_rows) {
         // idle lane of the M = 128 tile: nothing to store
       } else if (p.splits == 1) {
         __nv_bfloat16* orow = p.out + (static_cast<size_t>(tok) * p.nq + head) * kKvLora + half * 256;
@@ -510,7 +537,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         const int v = static_cast<int>(row);
         if (v != 0) {
           const unsigned char* base = v < 0 ? reinterpret_cast<const unsigned char*>(p.k_nope2) : nope_b;
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<long long>((v & 0x7fffffff) - 1) * 1024 + gpart * 128));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<long long>((v & 0x1fffffff) - 1) * 1024 + gpart * 128));
         }
         return;
       }
@@ -542,7 +569,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         const int v = static_cast<int>(row);
         pf.valid = v != 0;
         const unsigned char* base = v < 0 ? reinterpret_cast<const unsigned char*>(p.k_nope2) : nope_b;
-        src = reinterpret_cast<const int4*>(base + static_cast<long long>((v & 0x7fffffff) - 1) * 1024);
+        src = reinterpret_cast<const int4*>(base + static_cast<long long>((v & 0x1fffffff) - 1) * 1024);
       } else {
         pf.valid = row >= 0;
         src = reinterpret_cast<const int4*>(nope_b + row * p.nope_stride);
@@ -613,7 +640,10 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       const int r = pass * 32 + gkey;
       store_group(stage, r, q_own, 0, pf);
       store_group(stage, r, q_own + 1, 1, pf);
-      if (gpart == 0) valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
+      if (gpart == 0) {  // membership bits for the softmax; the tile's ids are still in the ring (mode 2 keeps them raw)
+        if constexpr (kCompress) valid_s[s * kStTile + r] = (static_cast<int>(row_of(tile, pass)) >> 29) & 3;
+        else valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
+      }
     };
 
     StPrefetch pf0, pf1;
@@ -688,6 +718,15 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
   cudaFuncSetAttribute(sfa_tc_kernel<kModeInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
   cudaFuncSetAttribute(sfa_tc_kernel<kModeBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
   cudaFuncSetAttribute(sfa_tc_kernel<kModeCompress>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStSmemBytes);
+  if (p.compress && (p.rows > 0x1ffffffeLL || p.rows2 > 0x1ffffffeLL)) {
+    set_error("sfa: the compress variant addresses at most 2^29-2 rows per cache (got %lld / %lld)",
+              static_cast<long long>(p.rows), static_cast<long long>(p.rows2));
+    return DSV32_ERR_UNSUPPORTED;
+  }
+  if (p.pair && p.nq > 64) {
+    set_error("sfa: two tokens per CTA need n_q <= 64 (got %d)", p.nq);
+    return DSV32_ERR_UNSUPPORTED;
+  }
   if (p.rows > 0x7ffffffeLL || (p.compress && p.rows2 > 0x7ffffffeLL)) {
     set_error("sfa: the tcgen05 kernel addresses at most 2^31-2 cache rows (got %lld)", static_cast<long long>(p.rows));
     return DSV32_ERR_UNSUPPORTED;

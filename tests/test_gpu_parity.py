@@ -457,6 +457,8 @@ def test_win_attention_reference_golden_fixture():
     (1, [8192] * 4, [2, 2, 2, 2], 64, 128),         # the reference's decode shape, 4 requests
     (2, [300, 129, 128, 7, 1], [5, 4, 1, 9, 3], 64, 128),   # ragged query counts; windows cut by the start of the context
     (3, [1000, 40], [2, 1], 128, 300),              # 128 heads; a window over more than two pages
+    (4, [1, 2, 3, 200], [2, 2, 2, 7], 64, 128),     # paired tokens: the first of a pair without any key; an odd count
+    (5, [500, 600], [2, 4], 32, 128),               # 32 heads, two tokens per CTA
 ])
 def test_win_attention_seeded_cases(seed, ori_seq, s1_list, nq, win):
     d = helpers.gen_scfa_inputs(900 + seed, ori_seq, s1_list, nq=nq, win_size=win)
