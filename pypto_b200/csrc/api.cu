@@ -182,7 +182,7 @@ int dsv32_sparse_attention_antiquant(const Dsv32SaAntiquantArgs* a, void* cuda_s
 size_t dsv32_scfa_workspace_bytes(int32_t t, int32_t topk, int32_t win_size) {
   if (t <= 0 || topk < 0 || win_size < 0) return 0;
   // cache row of every listed key (one more slot: the union window of two paired tokens) + the length of every list
-  return align_up(static_cast<size_t>(t) * (static_cast<size_t>(topk) + win_size + 1) * sizeof(int32_t), 256) +
+  return align_up(static_cast<size_t>(t) * (2 * static_cast<size_t>(topk) + win_size + 1) * sizeof(int32_t), 256) +
          align_up(static_cast<size_t>(t) * sizeof(int32_t), 256);
 }
 
@@ -227,10 +227,16 @@ int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
   p.rows = a->ori_rows;
   p.rows2 = a->cmp_rows;
   p.b = a->b; p.s1 = 1; p.t_total = a->t; p.nq = a->n_q;
-  p.topk = a->topk + a->win_size + 1;  // slots of a key list (the union window of two paired tokens is one longer)
-  // tokens 2k, 2k+1 of a request share a CTA when the key lists do not come from an index tensor and the heads
-  // of both fit the 128-row tile
-  p.pair = (a->n_q <= 64 && (a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED || a->topk == 0)) ? 1 : 0;
+  // Tokens 2k, 2k+1 of a request share a CTA when the heads of both fit the 128-row tile: their window differs in one
+  // position; the compressed keys are the same but one (all-compressed) or the union of both selections (selected,
+  // as long as a request's compressed positions fit the pre-pass' bitmaps).
+  p.pair = 0;
+  if (a->n_q <= 64) {
+    if (a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED || a->topk == 0) p.pair = 1;
+    else if (static_cast<long long>(a->cmp_max_blocks) * a->block_size <= 131072 && a->t >= 2) p.pair = 2;
+  }
+  // slots of a key list: the union window of two paired tokens is one longer, the union of two selections up to twice
+  p.topk = a->win_size + 1 + (p.pair == 2 ? 2 * a->topk : a->topk);
   p.sel_topk = a->topk; p.win_size = a->win_size; p.cmp_ratio = a->cmp_ratio;
   p.cmp_dense = a->cmp_mode == DSV32_SCFA_ALL_COMPRESSED ? 1 : 0;
   p.block_size = a->block_size;
@@ -247,7 +253,7 @@ int dsv32_sparse_compress_attention(const Dsv32ScfaArgs* a, void* cuda_stream) {
   char* ws = static_cast<char*>(a->workspace);
   p.row_ids = reinterpret_cast<int32_t*>(ws);
   p.key_counts = reinterpret_cast<int32_t*>(
-      ws + align_up(static_cast<size_t>(a->t) * (static_cast<size_t>(a->topk) + a->win_size + 1) * sizeof(int32_t), 256));
+      ws + align_up(static_cast<size_t>(a->t) * (2 * static_cast<size_t>(a->topk) + a->win_size + 1) * sizeof(int32_t), 256));
   return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 

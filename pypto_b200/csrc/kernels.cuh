@@ -69,7 +69,8 @@ struct SfaParams {
   int32_t* key_counts;      // [t] scratch: keys in each token's list
   long long rows2;
   int max_blocks2, win_size, sel_topk, cmp_ratio, t_total;
-  int pair;       // 1: tokens 2k, 2k+1 of a request share a CTA (<= 64 heads; key lists without an index tensor)
+  int pair;       // tokens 2k, 2k+1 of a request share a CTA (<= 64 heads): 1 = key lists without an index tensor,
+                  // 2 = selected compressed keys (the union of both selections is built by scfa_pair_ids_kernel)
   int cmp_dense;  // 1: every compressed position [0, cur_len / cmp_ratio) instead of the rows topk_idx selects
 };
 int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);

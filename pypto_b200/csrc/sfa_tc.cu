@@ -199,6 +199,120 @@ __global__ void __launch_bounds__(256) scfa_row_ids_kernel(SfaParams p) {
   if (j == 0) p.key_counts[tok] = count;
 }
 
+// The same for the operator whose compressed keys come from an index tensor (p.pair == 2): one CTA per token.
+// The CTA of the first token of a pair builds the union of both tokens' selections: two bitmaps over the compressed
+// positions (shared memory) say which token selected what; the list is the union window, then the first token's
+// entries (bit 30 set as well where the second token selected the same position), then the second token's
+// entries that the first did not select, compacted in their original order by a block-wide scan (deterministic).
+constexpr int kPairBitmapWords = 4096;   // 131,072 compressed positions per request at most
+
+__global__ void __launch_bounds__(256) scfa_pair_ids_kernel(SfaParams p) {
+  __shared__ uint32_t bm_a[kPairBitmapWords], bm_b[kPairBitmapWords];
+  __shared__ int warp_cnt[8];
+  __shared__ int base_s;
+  const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int lo = 0, hi = p.b;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(p.seq_q + mid) <= tok) lo = mid; else hi = mid;
+  }
+  const int bi = lo;
+  const int q0 = __ldg(p.seq_q + bi), q1 = __ldg(p.seq_q + bi + 1);
+  int32_t* list = p.row_ids + static_cast<size_t>(tok) * p.topk;
+  if (tok < q0 || tok >= q1) {
+    if (tid == 0) {
+      report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, bi);
+      p.key_counts[tok] = 0;
+    }
+    return;
+  }
+  const int s1 = q1 - q0, si = tok - q0;
+  if (si & 1) {
+    if (tid == 0) p.key_counts[tok] = -1;  // second token of a pair
+    return;
+  }
+  const int seq = __ldg(p.act_seq + bi);
+  const bool has_b = si + 1 < s1;
+  const int len_a = max(seq - s1 + 1 + si, 0), len_b = has_b ? max(seq - s1 + 2 + si, 0) : len_a;
+  const int win_a = min(len_a, p.win_size), win_b = min(len_b, p.win_size);
+  const int sel_a = min(max(seq / p.cmp_ratio - s1 + 1 + si, 0), p.sel_topk);
+  const int sel_b = has_b ? min(max(seq / p.cmp_ratio - s1 + 2 + si, 0), p.sel_topk) : 0;
+  const int w_start = len_a - win_a, w_len = len_b - w_start;
+  const int cap = p.max_blocks2 * p.block_size;   // compressed positions of a request (<= 32 * kPairBitmapWords)
+  auto resolve = [&](int idx, uint32_t mem) -> uint32_t {   // entry of compressed position idx, 0 if it cannot be used
+    if (idx < 0) return 0u;
+    if (idx >= cap) {
+      report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, idx);
+      return 0u;
+    }
+    const int pb = __ldg(p.block_table2 + static_cast<size_t>(bi) * p.max_blocks2 + idx / p.block_size);
+    const long long row = static_cast<long long>(pb) * p.block_size + idx % p.block_size;
+    if (pb < 0 || row >= p.rows2) {
+      report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, idx);
+      return 0u;
+    }
+    return (static_cast<uint32_t>(row) + 1u) | (mem << 29) | 0x80000000u;
+  };
+  // window
+  for (int j = tid; j < w_len; j += 256) {
+    const int pos = w_start + j;
+    const uint32_t mem = (pos < len_a ? 1u : 0u) | ((has_b && pos >= len_b - win_b) ? 2u : 0u);
+    uint32_t out = 0;
+    const int lb = pos / p.block_size;
+    if (lb >= p.max_blocks) {
+      report_status(p.status, DSV32_STATUS_BAD_INDEX, tok, pos);
+    } else {
+      const int pb = __ldg(p.block_table + static_cast<size_t>(bi) * p.max_blocks + lb);
+      const long long row = static_cast<long long>(pb) * p.block_size + pos % p.block_size;
+      if (pb < 0 || row >= p.rows) report_status(p.status, DSV32_STATUS_BAD_PAGE, tok, pos);
+      else out = (static_cast<uint32_t>(row) + 1u) | (mem << 29);
+    }
+    list[j] = static_cast<int>(out);
+  }
+  // bitmaps of both selections
+  const int words = (cap + 31) / 32;
+  for (int i = tid; i < words; i += 256) { bm_a[i] = 0u; bm_b[i] = 0u; }
+  __syncthreads();
+  const int32_t* ia = p.topk_idx + static_cast<size_t>(tok) * p.sel_topk;
+  const int32_t* ib = ia + p.sel_topk;   // the next token's index row
+  for (int e = tid; e < sel_a; e += 256) {
+    const int idx = __ldg(ia + e);
+    if (idx >= 0 && idx < cap) atomicOr(&bm_a[idx >> 5], 1u << (idx & 31));
+  }
+  for (int e = tid; e < sel_b; e += 256) {
+    const int idx = __ldg(ib + e);
+    if (idx >= 0 && idx < cap) atomicOr(&bm_b[idx >> 5], 1u << (idx & 31));
+  }
+  __syncthreads();
+  // the first token's entries, in place
+  for (int e = tid; e < sel_a; e += 256) {
+    const int idx = __ldg(ia + e);
+    const bool in_b = idx >= 0 && idx < cap && ((bm_b[idx >> 5] >> (idx & 31)) & 1u);
+    list[w_len + e] = static_cast<int>(resolve(idx, in_b ? 3u : 1u));
+  }
+  // the second token's entries that the first did not select, compacted in order
+  int base = w_len + sel_a;
+  for (int e0 = 0; e0 < sel_b; e0 += 256) {
+    const int e = e0 + tid;
+    int idx = -1;
+    if (e < sel_b) idx = __ldg(ib + e);
+    const bool take = idx >= 0 && !(idx < cap && ((bm_a[idx >> 5] >> (idx & 31)) & 1u));
+    const uint32_t ballot = __ballot_sync(0xffffffffu, take);
+    if (lane == 0) warp_cnt[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) before += warp_cnt[w];
+      total += warp_cnt[w];
+    }
+    if (take) list[base + before + __popc(ballot & ((1u << lane) - 1u))] = static_cast<int>(resolve(idx, 2u));
+    base += total;
+    __syncthreads();
+  }
+  if (tid == 0) p.key_counts[tok] = base;
+}
+
 template <int kMode>
 __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
                                                                const __grid_constant__ CUtensorMap qr_map,
@@ -731,7 +845,11 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
     set_error("sfa: the tcgen05 kernel addresses at most 2^31-2 cache rows (got %lld)", static_cast<long long>(p.rows));
     return DSV32_ERR_UNSUPPORTED;
   }
-  if (p.compress) {
+  if (p.compress && p.pair == 2) {
+    scfa_pair_ids_kernel<<<t, 256, 0, stream>>>(p);
+    count_launch();
+    rc = check_launch("scfa_pair_ids_kernel");
+  } else if (p.compress) {
     scfa_row_ids_kernel<<<dim3((p.topk + 255) / 256, t), 256, 0, stream>>>(p);
     count_launch();
     rc = check_launch("scfa_row_ids_kernel");

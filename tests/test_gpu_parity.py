@@ -295,6 +295,7 @@ def test_scfa_reference_golden_fixture():
     (6, [900], [5], 64, {"topk": 64, "win_size": 300, "cmp_ratio": 2}),        # window longer than two pages
     (7, [5000], [1], 64, {}),                                                  # one token: fewer query rows than the 128-row tile
     (8, [300], [1], 32, {"topk": 64}),
+    (9, [2100, 900, 3000], [2, 3, 4], 64, {"holes": 37}),                      # paired tokens with -1 entries among the selected
 ])
 def test_scfa_seeded_cases(seed, ori_seq, s1_list, nq, kw):
     d = helpers.gen_scfa_inputs(700 + seed, ori_seq, s1_list, nq=nq, **kw)
@@ -324,6 +325,23 @@ def test_scfa_reference_decode_shape_sampled_tokens():
     shuffled = dict(d, cmp_sparse_indices=d["cmp_sparse_indices"][:, torch.randperm(512, generator=g)].contiguous())
     out2 = _run_scfa(shuffled)
     assert torch.allclose(out2.float(), out.float(), rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("shared", [512, 460, 1])
+def test_scfa_paired_tokens_with_overlapping_selections(shared):
+    """With at most 64 heads the two tokens of a request share a CTA and its key list is the union of both selections:
+    identical, mostly identical and nearly disjoint selections must all match the oracle."""
+    d = helpers.gen_scfa_inputs(790 + shared, [8192] * 6, [2] * 6)
+    idx = d["cmp_sparse_indices"].clone()
+    idx[1::2, :shared] = idx[0::2, :shared]
+    if shared < 512:   # keep every row free of duplicates: the rest of the odd rows comes from the unused positions
+        g = torch.Generator().manual_seed(shared)
+        for t in range(1, idx.shape[0], 2):
+            used = set(idx[t - 1].tolist())
+            rest = [v for v in torch.randperm(2048, generator=g).tolist() if v not in used][:512 - shared]
+            idx[t, shared:] = torch.tensor(rest, dtype=torch.int32)
+    d = dict(d, cmp_sparse_indices=idx)
+    _assert_attention_close(_run_scfa(d), _scfa_oracle(d))
 
 
 def test_scfa_sink_and_window_matter():
