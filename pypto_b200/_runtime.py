@@ -48,6 +48,39 @@ def gemm_bf16_fp32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return torch.mm(a, b, out_dtype=torch.float32)
 
 
+_SIDE_STREAMS = {}
+
+
+class side_stream:
+    """Run an independent branch of an operator on a second stream of the device: `with fork:` makes the side
+    stream wait for the work already enqueued on the current stream and makes it current inside the block; the
+    caller then enqueues the other branch on the original stream and calls `fork.join()`, after which the original
+    stream waits for the side branch (events only, so the pattern can be captured in a CUDA graph).  Tensors
+    created inside the block belong to the side stream's allocator pool; keep them referenced until the join."""
+
+    def __init__(self, device):
+        key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+        if key not in _SIDE_STREAMS:
+            _SIDE_STREAMS[key] = torch.cuda.Stream(device=key)
+        self.side = _SIDE_STREAMS[key]
+        self.main = None
+        self.ctx = None
+
+    def __enter__(self):
+        self.main = torch.cuda.current_stream(self.side.device)
+        self.side.wait_stream(self.main)
+        self.ctx = torch.cuda.stream(self.side)
+        self.ctx.__enter__()
+        return self.side
+
+    def __exit__(self, *exc):
+        self.ctx.__exit__(*exc)
+        return False
+
+    def join(self):
+        self.main.wait_stream(self.side)
+
+
 def ptr(t):
     return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
 

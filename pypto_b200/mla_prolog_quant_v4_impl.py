@@ -86,18 +86,23 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
                          qr_out, qr_scale_out)
     lib = _lib.load()
     with torch.cuda.device(dev):
-        stream = rt.stream_ptr(dev)
-        q_a = rt.gemm_bf16_fp32(token_x, wq_a)                                   # [t, 1024] fp32
-        a = _lib.MlaV4StageArgs(rt.ptr(q_a), rt.ptr(gamma_cq), rt.ptr(qr_out), rt.ptr(qr_scale_out), None,
+        a = _lib.MlaV4StageArgs(None, rt.ptr(gamma_cq), rt.ptr(qr_out), rt.ptr(qr_scale_out), None,
                                 rt.ptr(wq_b_scale), rt.ptr(q_out), None, rt.ptr(gamma_ckv), rt.ptr(kv_out),
                                 rt.ptr(rope_cos), rt.ptr(rope_sin), t, heads, 0, 1, eps)
+        # the kv branch (one GEMM + one stage kernel) is independent of the q branch: it runs on a second stream
+        fork = rt.side_stream(dev)
+        with fork:
+            kv_a = rt.gemm_bf16_fp32(token_x, wkv)                               # [t, 512] fp32
+            a.kv_a = rt.ptr(kv_a)
+            rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 2, rt.stream_ptr(dev)), "mla_prolog_v4 (kv norm + rope)")
+        stream = rt.stream_ptr(dev)
+        q_a = rt.gemm_bf16_fp32(token_x, wq_a)                                   # [t, 1024] fp32
+        a.q_a = rt.ptr(q_a)
         rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 0, stream), "mla_prolog_v4 (q norm + quant)")
         q_b = _int8_gemm(qr_out, wq_b)                                    # [>= t, heads * 512] int32
         a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]
         rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 1, stream), "mla_prolog_v4 (q dequant + norm + rope)")
-        kv_a = rt.gemm_bf16_fp32(token_x, wkv)                                   # [t, 512] fp32
-        a.kv_a = rt.ptr(kv_a)
-        rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 2, stream), "mla_prolog_v4 (kv norm + rope)")
+        fork.join()
     return None
 
 
