@@ -529,8 +529,9 @@ int dsv32_hc_pre(const Dsv32HcPreArgs* a, void* cuda_stream) {
   REQUIRE(a->hc_mult == 4 && a->d == 4096, "hc_pre: only 4 streams of 4096 are supported (got %d x %d)", a->hc_mult, a->d);
   REQUIRE(a->iters >= 1, "hc_pre: iters=%d must be >= 1", a->iters);
   REQUIRE(a->x && a->hc_fn && a->hc_scale && a->hc_base && a->y && a->post && a->comb, "hc_pre: NULL tensor pointer");
-  REQUIRE(reinterpret_cast<uintptr_t>(a->x) % 16 == 0 && reinterpret_cast<uintptr_t>(a->y) % 16 == 0,
-          "hc_pre: x and y must be 16-byte aligned");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->x) % 16 == 0 && reinterpret_cast<uintptr_t>(a->y) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->hc_fn) % 16 == 0,
+          "hc_pre: x, y and hc_fn must be 16-byte aligned");
   const size_t need = hc_pre_workspace_bytes(a->t);
   if (a->workspace == nullptr || a->workspace_bytes < need || reinterpret_cast<uintptr_t>(a->workspace) % 16 != 0) {
     set_error("hc_pre: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);

@@ -8,9 +8,9 @@
 //              (iters - 1) x (row normalisation, column normalisation), every divisor with + hc_eps
 //   y[4096]  = bf16( sum_h pre[h] * x[h, :] )
 // Two kernels.  hc_pre_dots_kernel splits the 16384-long reduction into 128 slices of 128 columns: a CTA holds
-// the 24 x 128 slice of hc_fn in shared memory and applies it to a tile of up to 64 tokens, so hc_fn (1.5 MB) is
-// read once per token tile instead of once per token; lane m of a warp owns output m, x values are shared-memory
-// broadcasts, so there are no shuffles in the loop.  Partial sums go to a workspace [group][token][24]; with
+// the 24 x 128 slice of hc_fn in shared memory and applies it to a tile of up to 128 tokens, so hc_fn (1.5 MB) is
+// read once per token tile instead of once per token; a lane owns 6 outputs x 2 tokens, so every lane works and
+// there are no shuffles in the loop.  Partial sums go to a workspace [group][token][24]; with
 // many tokens a CTA walks several slices and adds them up in registers first.
 // hc_pre_finish_kernel (one CTA per token) reads the token's x with 16-byte loads, takes its sum of squares, adds
 // the partials in a fixed order, runs the 4x4 Sinkhorn on 16 lanes of a warp (row / column sums by shuffles)
@@ -23,60 +23,76 @@ namespace dsv32 {
 namespace {
 constexpr int kHc = 4, kHcD = 4096, kHcK = kHc * kHcD, kHcMix = (2 + kHc) * kHc, kHcOut = kHcMix + 1;
 constexpr int kHcSlice = 128, kHcSlices = kHcK / kHcSlice;   // 128 slices of 128 columns
-constexpr int kHcTokTile = 64, kHcDotThreads = 256, kHcFinThreads = 512;
-constexpr int kHcWStride = kHcOut;                            // odd: conflict-free transposed stores
+constexpr int kHcTokTile = 128, kHcDotThreads = 256, kHcFinThreads = 512;
+constexpr int kHcPad = kHcSlice + 4;                          // padded row stride of the shared-memory tiles
+constexpr size_t kHcDotSmem = static_cast<size_t>(kHcMix + kHcTokTile) * kHcPad * sizeof(float);   // 80,256 bytes
 
 __device__ __forceinline__ float hc_sigmoid(float v) { return __fdiv_rn(1.0f, 1.0f + expf(-v)); }
 }  // namespace
 
-// grid (groups, token tiles); a group = slices_per_cta consecutive slices
+// grid (groups, token tiles); a group = slices_per_cta consecutive slices.  Dynamic shared memory:
+// w_s[24][132] (a slice of hc_fn, row stride padded so that the four output groups of a warp hit different banks)
+// and x_s[128][132] (the token tile's slice of x as floats, padded so that the eight token groups do).
+// Lane = (output group og = lane / 8: outputs 6 og .. 6 og + 5) x (token group tg = lane % 8: tokens tg, tg + 8 of
+// the warp's 16): per four columns 6 + 2 sixteen-byte shared-memory loads (broadcast within a group) feed 48 FMAs.
 __global__ void __launch_bounds__(kHcDotThreads) hc_pre_dots_kernel(HcPreParams p, int slices_per_cta) {
-  __shared__ float w_s[kHcSlice * kHcWStride];          // [col][m], m = 0..23; column 24 unused
-  __shared__ __align__(16) float x_s[kHcTokTile * kHcSlice];   // [token][col]
+  extern __shared__ __align__(16) float hc_smem[];
+  float* w_s = hc_smem;                               // [kHcMix][kHcPad]
+  float* x_s = hc_smem + kHcMix * kHcPad;             // [kHcTokTile][kHcPad]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = blockIdx.x, t0 = blockIdx.y * kHcTokTile;
   const int ntok = min(kHcTokTile, p.t - t0);
-  constexpr int kTokPerWarp = kHcTokTile / (kHcDotThreads / 32);   // 8
-  float acc[kTokPerWarp];
+  const int og = lane >> 3, tg = lane & 7;
+  const int tok_a = warp * 16 + tg, tok_b = tok_a + 8;
+  float acc_a[6], acc_b[6];
 #pragma unroll
-  for (int i = 0; i < kTokPerWarp; ++i) acc[i] = 0.f;
+  for (int i = 0; i < 6; ++i) acc_a[i] = acc_b[i] = 0.f;
   for (int s = 0; s < slices_per_cta; ++s) {
     const int k0 = (group * slices_per_cta + s) * kHcSlice;
     __syncthreads();  // the previous slice has been consumed
-    for (int i = tid; i < kHcMix * kHcSlice; i += kHcDotThreads) {
-      const int m = i / kHcSlice, col = i % kHcSlice;
-      w_s[col * kHcWStride + m] = __ldg(p.hc_fn + static_cast<size_t>(m) * kHcK + k0 + col);
+    for (int i = tid; i < kHcMix * (kHcSlice / 4); i += kHcDotThreads) {
+      const int m = i / (kHcSlice / 4), c4 = i % (kHcSlice / 4);
+      *reinterpret_cast<float4*>(&w_s[m * kHcPad + 4 * c4]) =
+          __ldg(reinterpret_cast<const float4*>(p.hc_fn + static_cast<size_t>(m) * kHcK + k0 + 4 * c4));
     }
-    for (int i = tid; i < ntok * (kHcSlice / 4); i += kHcDotThreads) {
+    for (int i = tid; i < kHcTokTile * (kHcSlice / 4); i += kHcDotThreads) {
       const int tok = i / (kHcSlice / 4), c4 = i % (kHcSlice / 4);
-      const uint2 v = __ldg(reinterpret_cast<const uint2*>(p.x + static_cast<size_t>(t0 + tok) * kHcK + k0 + 4 * c4));
-      *reinterpret_cast<float4*>(&x_s[tok * kHcSlice + 4 * c4]) =
-          make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
-                      __uint_as_float(v.y & 0xffff0000u));
+      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tok < ntok) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(p.x + static_cast<size_t>(t0 + tok) * kHcK + k0 + 4 * c4));
+        f = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                        __uint_as_float(v.y & 0xffff0000u));
+      }
+      *reinterpret_cast<float4*>(&x_s[tok * kHcPad + 4 * c4]) = f;
     }
     __syncthreads();
-    // lane m < 24: dot with row m of hc_fn; lanes 24..31 idle copies of lane 0
-    const float* wl = w_s + (lane < kHcMix ? lane : 0);
+    if (warp * 16 < ntok) {
+      const float* wl = w_s + og * 6 * kHcPad;
+      const float* xa = x_s + tok_a * kHcPad;
+      const float* xb = x_s + tok_b * kHcPad;
 #pragma unroll 2
-    for (int col = 0; col < kHcSlice; col += 4) {
-      const float w0 = wl[col * kHcWStride], w1 = wl[(col + 1) * kHcWStride];
-      const float w2 = wl[(col + 2) * kHcWStride], w3 = wl[(col + 3) * kHcWStride];
+      for (int col = 0; col < kHcSlice; col += 4) {
+        const float4 va = *reinterpret_cast<const float4*>(xa + col);
+        const float4 vb = *reinterpret_cast<const float4*>(xb + col);
 #pragma unroll
-      for (int i = 0; i < kTokPerWarp; ++i) {
-        const float4 xv = *reinterpret_cast<const float4*>(&x_s[(warp + 8 * i) * kHcSlice + col]);   // broadcast
-        acc[i] = fmaf(xv.x, w0, acc[i]);
-        acc[i] = fmaf(xv.y, w1, acc[i]);
-        acc[i] = fmaf(xv.z, w2, acc[i]);
-        acc[i] = fmaf(xv.w, w3, acc[i]);
+        for (int i = 0; i < 6; ++i) {
+          const float4 w = *reinterpret_cast<const float4*>(wl + i * kHcPad + col);
+          acc_a[i] = fmaf(va.x, w.x, acc_a[i]);
+          acc_a[i] = fmaf(va.y, w.y, acc_a[i]);
+          acc_a[i] = fmaf(va.z, w.z, acc_a[i]);
+          acc_a[i] = fmaf(va.w, w.w, acc_a[i]);
+          acc_b[i] = fmaf(vb.x, w.x, acc_b[i]);
+          acc_b[i] = fmaf(vb.y, w.y, acc_b[i]);
+          acc_b[i] = fmaf(vb.z, w.z, acc_b[i]);
+          acc_b[i] = fmaf(vb.w, w.w, acc_b[i]);
+        }
       }
     }
   }
-  if (lane < kHcMix) {
 #pragma unroll
-    for (int i = 0; i < kTokPerWarp; ++i) {
-      const int tok = warp + 8 * i;
-      if (tok < ntok) p.partial[(static_cast<size_t>(group) * p.t + t0 + tok) * kHcMix + lane] = acc[i];
-    }
+  for (int i = 0; i < 6; ++i) {
+    if (tok_a < ntok) p.partial[(static_cast<size_t>(group) * p.t + t0 + tok_a) * kHcMix + og * 6 + i] = acc_a[i];
+    if (tok_b < ntok) p.partial[(static_cast<size_t>(group) * p.t + t0 + tok_b) * kHcMix + og * 6 + i] = acc_b[i];
   }
 }
 
@@ -184,7 +200,8 @@ int launch_hc_pre(const HcPreParams& p, cudaStream_t stream) {
   const int spc = hc_pre_slices_per_cta(p.t);
   const int groups = kHcSlices / spc;
   const int tiles = (p.t + kHcTokTile - 1) / kHcTokTile;
-  hc_pre_dots_kernel<<<dim3(groups, tiles), kHcDotThreads, 0, stream>>>(p, spc);
+  cudaFuncSetAttribute(hc_pre_dots_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kHcDotSmem));
+  hc_pre_dots_kernel<<<dim3(groups, tiles), kHcDotThreads, kHcDotSmem, stream>>>(p, spc);
   count_launch();
   int rc = check_launch("hc_pre_dots_kernel");
   if (rc != DSV32_OK) return rc;
