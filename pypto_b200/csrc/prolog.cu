@@ -161,8 +161,12 @@ __global__ void __launch_bounds__(kKwCols) prolog_kw_finish_kernel(PrologParams 
   __shared__ __align__(16) __nv_bfloat16 had_s[128][128];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok = blockIdx.x;
-  for (int c = tid; c < 128 * 16; c += kKwCols)
-    *reinterpret_cast<int4*>(&had_s[c / 16][(c % 16) * 8]) = *reinterpret_cast<const int4*>(p.had_k + c * 8);
+  // the hadamard matrix (32 KB) travels to shared memory asynchronously, under the reduction / LayerNorm / RoPE below
+  for (int c = tid; c < 128 * 16; c += kKwCols) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(&had_s[c / 16][(c % 16) * 8]));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(p.had_k + c * 8) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
   float sum = 0.f;
   for (int kc = 0; kc < nsplits; ++kc) sum += p.partial[(static_cast<size_t>(kc) * p.t + tok) * kKwCols + tid];
 
@@ -194,6 +198,7 @@ __global__ void __launch_bounds__(kKwCols) prolog_kw_finish_kernel(PrologParams 
   if (tid < 128)
     r_s[tid] = (tid < 64) ? rope_elem(v_s, tid, p.cos + static_cast<size_t>(tok) * 64, p.sin + static_cast<size_t>(tok) * 64)
                           : v_s[tid];
+  asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's pieces of the hadamard matrix have landed
   __syncthreads();
   float hv = 0.f;
   if (tid < 128) {
