@@ -33,16 +33,10 @@ int check_launch(const char* what) {
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 static int pick_sfa_splits(int t, int nq, int topk, int requested) {
-  if (requested <= 0) {  // DSV32_SFA_KV_SPLITS overrides the automatic choice (profiling knob)
-    static const int env_splits = [] {
-      const char* e = getenv("DSV32_SFA_KV_SPLITS");
-      return e != nullptr ? atoi(e) : 0;
-    }();
-    requested = env_splits;
-  }
   const int max_splits = topk / 128 > 0 ? (topk / 128 < 16 ? topk / 128 : 16) : 1;
   if (requested > 0) return requested < max_splits ? requested : max_splits;
-  const int ctas = t * (nq / 64);
+  (void)nq;
+  const int ctas = t * 2;  // one CTA per token and half of the value dims
   if (ctas >= 148) return 1;
   int s = (2 * 148 + ctas - 1) / ctas;
   if (s > max_splits) s = max_splits;
@@ -83,7 +77,7 @@ static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, in
   REQUIRE(a != nullptr, "sfa: args is NULL");
   REQUIRE(a->b >= 0 && a->s1 >= 1, "sfa: bad b=%d s1=%d", a->b, a->s1);
   if (a->b == 0) return DSV32_OK;
-  REQUIRE(a->n_q > 0 && a->n_q % 64 == 0, "sfa: n_q=%d must be a positive multiple of 64", a->n_q);
+  REQUIRE(a->n_q >= 1 && a->n_q <= 128, "sfa: n_q=%d must be in [1, 128]", a->n_q);
   REQUIRE(a->topk >= 1, "sfa: topk=%d must be >= 1", a->topk);
   REQUIRE(a->block_size >= 1 && a->max_blocks >= 1, "sfa: bad block_size=%d max_blocks=%d", a->block_size,
           a->max_blocks);
@@ -134,16 +128,6 @@ static int sfa_run(const Dsv32SfaArgs* a, void* cuda_stream, int nope_stride, in
       p.part_lse = reinterpret_cast<float*>(ws + o_bytes);
     }
   }
-  // bring-up switch: DSV32_SFA_IMPL=mma selects the warp-MMA kernel instead of the tcgen05 one
-  static const bool use_mma = [] {
-    const char* e = getenv("DSV32_SFA_IMPL");
-    return e != nullptr && e[0] == 'm';
-  }();
-  if (bf16_cache && (use_mma || a->n_q != 128)) {
-    set_error("sfa: the bf16 latent cache is only supported by the tcgen05 kernel (n_q == 128, got %d)", a->n_q);
-    return DSV32_ERR_UNSUPPORTED;
-  }
-  if (use_mma || a->n_q != 128) return launch_sfa_mma(p, static_cast<cudaStream_t>(cuda_stream));
   return launch_sfa_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
@@ -307,12 +291,7 @@ int dsv32_indexer_topk(const Dsv32IndexerArgs* a, void* cuda_stream) {
   p.b = a->b; p.s1 = a->s1; p.block_size = a->block_size; p.max_blocks = a->max_blocks; p.ld = ld;
   p.key_begin = a->key_begin;
   p.key_end = a->key_end;
-  // bring-up switch: DSV32_INDEXER_IMPL=mma selects the warp-MMA kernel instead of the tcgen05 one
-  static const bool use_mma = [] {
-    const char* e = getenv("DSV32_INDEXER_IMPL");
-    return e != nullptr && e[0] == 'm';
-  }();
-  int rc = use_mma ? launch_indexer_scores_mma(p, st) : launch_indexer_scores_tc(p, st);
+  int rc = launch_indexer_scores_tc(p, st);
   if (rc != DSV32_OK || a->topk_res == nullptr) return rc;
   TopkParams tp{};
   tp.scores = scores;
@@ -323,7 +302,7 @@ int dsv32_indexer_topk(const Dsv32IndexerArgs* a, void* cuda_stream) {
   tp.out_scores = a->topk_scores;
   tp.s1 = a->s1;
   tp.key_begin = a->key_begin;
-  tp.key_end = a->key_end;
+  tp.key_end = a->key_end < full_ld ? a->key_end : full_ld;  // scores exist up to the page table's capacity
   tp.ld = ld;
   tp.k = a->selected_count;
   tp.id_base = 0;
@@ -439,12 +418,6 @@ int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {
   p.cache_rows = a->cache_rows;
   p.t = a->t;
   p.eps = a->ln_eps;
-  // bring-up switch: DSV32_PROLOG_IMPL=simt selects the CUDA-core kernels instead of the tcgen05 ones
-  static const bool use_simt = [] {
-    const char* e = getenv("DSV32_PROLOG_IMPL");
-    return e != nullptr && e[0] == 's';
-  }();
-  if (use_simt) return launch_prolog(p, static_cast<cudaStream_t>(cuda_stream));
   return launch_prolog_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 

@@ -75,9 +75,15 @@ __global__ void __launch_bounds__(TcShape<TOK>::kThreads, 2) indexer_scores_tc_k
   const int b = blockIdx.y;
   const int tok0 = blockIdx.z * TOK;
   const int ntok = min(TOK, p.s1 - tok0);
-  const int L = p.act_seq[b];
-  const int hi = min(L, p.key_end);
   const int bs = 128;
+  // A sequence length beyond what the request's page-table row can describe is reported and clamped: nothing is
+  // read past the row of the page table or written past the row of the score buffer.
+  int L = p.act_seq[b];
+  if (L > p.max_blocks * bs) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) report_status(p.status, DSV32_STATUS_BAD_INDEX, b, static_cast<uint32_t>(L));
+    L = p.max_blocks * bs;
+  }
+  const int hi = min(L, p.key_end);
   const int blk_begin = p.key_begin / bs + blockIdx.x * p.blocks_per_cta;
   const int blk_end = min(blk_begin + p.blocks_per_cta, (hi + bs - 1) / bs);
   if (blk_begin >= blk_end || hi <= p.key_begin) return;  // uniform for the CTA

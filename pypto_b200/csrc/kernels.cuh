@@ -32,7 +32,6 @@ struct IndexerParams {
   int key_begin, key_end;
   int blocks_per_cta;  // key blocks one CTA of the tcgen05 kernel walks (chosen by its launcher)
 };
-int launch_indexer_scores_mma(const IndexerParams& p, cudaStream_t stream);
 int launch_indexer_scores_tc(const IndexerParams& p, cudaStream_t stream);
 
 struct SfaParams {
@@ -73,7 +72,6 @@ struct SfaParams {
                   // 2 = selected compressed keys (the union of both selections is built by scfa_pair_ids_kernel)
   int cmp_dense;  // 1: every compressed position [0, cur_len / cmp_ratio) instead of the rows topk_idx selects
 };
-int launch_sfa_mma(const SfaParams& p, cudaStream_t stream);
 int launch_sfa_tc(const SfaParams& p, cudaStream_t stream);
 int launch_sfa_combine(const SfaParams& p, cudaStream_t stream);
 
@@ -103,7 +101,7 @@ struct PrologParams {
   int t;
   float eps;
 };
-int launch_prolog(const PrologParams& p, cudaStream_t stream);
+constexpr int kPrologKSplits = 16;  // CTAs that share the 7168-long reduction of x . [wk | w_proj]
 int launch_prolog_tc(const PrologParams& p, cudaStream_t stream);
 int launch_prolog_v4(const PrologParams& p, int h, float w_scale, cudaStream_t stream);
 size_t prolog_v4_workspace_bytes(int t, int h);

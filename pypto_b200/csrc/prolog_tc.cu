@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kPqThreads, 1) prolog_kw_tc_kernel(const __gri
 // ---- host ---------------------------------------------------------------------------------------------------
 int launch_prolog_finish(const PrologParams& p, int splits, cudaStream_t stream);  // prolog.cu
 
-int prolog_tc_splits() { return 16; }  // 7 reduction chunks of 64 per CTA
+constexpr int prolog_tc_splits() { return kPrologKSplits; }  // 7 reduction chunks of 64 per CTA
 
 // The Q path and the K/W path of the prolog are independent (64 and 16 CTAs per 128 tokens, both latency-
 // bound), so the Q kernel runs on a side stream of the library, forked from and joined back into the caller's

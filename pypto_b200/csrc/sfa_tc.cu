@@ -45,18 +45,6 @@ constexpr size_t kStSmemBytes = kStOffTmem + 16 + 1024;
 
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;
 
-// Optional pipeline trace (profiling builds only, -DDSV32_SFA_TRACE): SM clock at eight points per tile
-// for the first four CTAs.  Not compiled into the product library.
-#ifdef DSV32_SFA_TRACE
-__device__ unsigned long long g_sfa_trace[4][40][8];
-#define ST_TRACE(tile, slot)                                                                        \
-  do {                                                                                              \
-    const int cta_ = blockIdx.x + 2 * blockIdx.y;                                                   \
-    if (cta_ < 4 && (tile) < 40) g_sfa_trace[cta_][tile][slot] = clock64();                         \
-  } while (0)
-#else
-#define ST_TRACE(tile, slot) do { } while (0)
-#endif
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -209,7 +197,6 @@ constexpr int kPairBitmapWords = 4096;   // 131,072 compressed positions per req
 __global__ void __launch_bounds__(256) scfa_pair_ids_kernel(SfaParams p) {
   __shared__ uint32_t bm_a[kPairBitmapWords], bm_b[kPairBitmapWords];
   __shared__ int warp_cnt[8];
-  __shared__ int base_s;
   const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int lo = 0, hi = p.b;
   while (hi - lo > 1) {
@@ -429,7 +416,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         const int s = i & 1;
         ok = mbar_wait(&full_bar[s], (i >> 1) & 1, p.status, 11);
         if (!ok) break;
-        ST_TRACE(i, 2);
         tc_fence_after();
         const uint32_t d = tmem_base + kColS + s * kStTile;
         const uint32_t klo = stage_lo[s];
@@ -442,7 +428,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
           umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
                       desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
         umma_commit(&sfull_bar[s]);
-        ST_TRACE(i, 3);
       }
     }
   } else if (warp <= 4) {
@@ -459,7 +444,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (!kCompress || head < live_rows) v = __ldg(qrow + c * 8 + j);
+          if (head < live_rows) v = __ldg(qrow + c * 8 + j);
           r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
         }
         tmem_st_32x32b_x32(tmem_base + lane_addr + kColQ + c * 32, r);
@@ -485,7 +470,11 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       // the CTA), bit 1 = a key of the token in lanes 64..127; this warp's lanes all belong to one of them.
       const int* vm = valid_s + s * kStTile;
       const int hb = !kCompress ? 1 : (head < p.nq ? 1 : (head < live_rows ? 2 : 3));   // idle lanes take every key
-      const bool all_valid = __all_sync(0xffffffffu, (vm[lane] & vm[32 + lane] & hb) != 0);
+      // The shortcut must hold for every lane of the warp: with fewer than 32 heads per token a warp holds heads
+      // of both tokens (and idle lanes), so the flags are tested against the bits of all of them.
+      const uint32_t need_bits = __reduce_or_sync(0xffffffffu, static_cast<uint32_t>(hb == 3 ? 0 : hb));
+      const bool all_valid = __all_sync(0xffffffffu, (static_cast<uint32_t>(vm[lane]) & need_bits) == need_bits &&
+                                                         (static_cast<uint32_t>(vm[32 + lane]) & need_bits) == need_bits);
       if (!all_valid) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -547,7 +536,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
             const uint32_t a = smem_u32(k_s + s * kStStageBytes);
             const uint32_t vlo = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);
-            ST_TRACE(i, 4);
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
@@ -557,7 +545,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
                           (i > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(&pvdone_bar[s]);
-            ST_TRACE(i, 5);
           }
         }
         if (!__all_sync(0xffffffffu, okpv)) { ok = false; break; }
@@ -572,8 +559,11 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
           l_run += exp2f(fmaf(__ldg(p.sinks + (head >= p.nq ? head - p.nq : head)), 1.4426950408889634f, -m_run));
       }
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      if (kCompress && head >= live_rows) {
-        // idle lane of the M = 128 tile: nothing to store
+      // tcgen05.ld is a warp-wide instruction: a warp whose lanes are partly idle (a head count that is not a
+      // multiple of 32) runs the loops below as a whole and only the stores are per lane.
+      const bool live = head < live_rows;
+      if (quarter * 32 >= live_rows) {
+        // idle warp of the M = 128 tile: nothing to store
       } else if (p.splits == 1) {
         __nv_bfloat16* orow = p.out + (static_cast<size_t>(tok) * p.nq + head) * kKvLora + half * 256;
 #pragma unroll 1
@@ -588,7 +578,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
             v.y = pack_bf16x2(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
             v.z = pack_bf16x2(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
             v.w = pack_bf16x2(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + j) = v;
+            if (live) *reinterpret_cast<uint4*>(orow + c * 32 + j) = v;
           }
         }
       } else {
@@ -601,11 +591,12 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(orow + c * 32 + j) =
-                make_float4(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv,
-                            __uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+            if (live)
+              *reinterpret_cast<float4*>(orow + c * 32 + j) =
+                  make_float4(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv,
+                              __uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
         }
-        if (half == 0)
+        if (half == 0 && live)
           p.part_lse[prow] = (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       }
     }
@@ -775,7 +766,6 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       // (both waits pass at once for i < 2): that part of the refill runs under the softmax and PV of tile i-2.
       const uint32_t prev = ((i >> 1) & 1) ^ 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], prev, p.status, 30))) break;
-      if (ptid == 0) ST_TRACE(i, 0);
       commit_other(i, 0, pf0);
       commit_other(i, 1, pf1);
       // the own value chunks (and the validity flags the softmax reads) are free once PV of tile i-2 has completed
@@ -785,17 +775,14 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
       __syncwarp();
       if (pwarp_lane0) mbar_arrive(&full_bar[s]);
-      if (ptid == 0) ST_TRACE(i, 1);
       if (i + 1 < ntiles) {
         fetch_ids(i + 3);
         ids_wait_all_but_one();                   // ids of tile i+2 have landed
         issue_loads(row_of(i + 1, 0), pf0);       // tile i+1
         issue_loads(row_of(i + 1, 1), pf1);
-        if (ptid == 0) ST_TRACE(i, 6);
         l2_prefetch(row_of(i + 2, 0));            // tile i+2 (its slot holds zeros past the last tile)
         l2_prefetch(row_of(i + 2, 1));
       }
-      if (ptid == 0) ST_TRACE(i, 7);
     }
   }
 
@@ -812,8 +799,8 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
 int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
   const int t = p.compress ? p.t_total : p.b * p.s1;
   if (t <= 0) return DSV32_OK;
-  if (p.compress ? (p.nq < 1 || p.nq > 128) : p.nq != 128) {
-    set_error("sfa: the tcgen05 kernel needs n_q == 128 (1..128 for the compress variant), got %d", p.nq);
+  if (p.nq < 1 || p.nq > 128) {
+    set_error("sfa: n_q=%d must be in [1, 128] (the heads of a token are the rows of one M = 128 tile)", p.nq);
     return DSV32_ERR_UNSUPPORTED;
   }
   if (p.compress && p.splits != 1) {
@@ -870,9 +857,3 @@ int launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
 }
 
 }  // namespace dsv32
-
-#ifdef DSV32_SFA_TRACE
-extern "C" int dsv32_debug_sfa_trace(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, dsv32::g_sfa_trace, sizeof(dsv32::g_sfa_trace));
-}
-#endif

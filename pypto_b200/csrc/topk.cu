@@ -14,13 +14,6 @@
 
 namespace dsv32 {
 
-#ifdef DSV32_TOPK_TRACE
-__device__ unsigned long long g_topk_trace[16];
-#define TK_TRACE(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_topk_trace[slot] = clock64(); } while (0)
-#else
-#define TK_TRACE(slot) do { } while (0)
-#endif
-
 constexpr int kTopkThreads = 1024;
 constexpr int kTopkMaxK = 2048;
 constexpr int kHistBins = 4096;
@@ -168,7 +161,6 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   };
 
   bool emitted = false;
-  TK_TRACE(0);
   if (n > 0 && irow == nullptr) {
     // ---- fast path: scan 1 = histogram of the top 12 key bits (vectorised when the row is 16-byte aligned) ----
     for (int i = tid; i < kHistBins; i += kTopkThreads) hist[i] = 0;
@@ -200,10 +192,8 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
     }
     for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) atomicAdd(&hist[float_to_key(srow[j]) >> 20], 1u);
     __syncthreads();
-    TK_TRACE(1);
     uint32_t total;
     narrow(st, hist, warp_tot, s_tmp, 52, 0xFFFu, total);
-    TK_TRACE(2);
     if (!st.done && s_tmp[2] <= static_cast<uint32_t>(kCandCap)) {
       // ---- scan 2: winners go to the output list, the threshold bucket to the candidate list ---------------
       const uint32_t bin = static_cast<uint32_t>(st.prefix >> 52);
@@ -261,14 +251,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
       }
       for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) place(srow[j], j);
       __syncthreads();
-      TK_TRACE(3);
       const int ncand = static_cast<int>(s_ncand);
       auto from_cand = [&](int j, uint64_t& c) -> bool {
         c = cand[j];
         return true;
       };
       radix_passes(st, 1, ncand, from_cand, hist, warp_tot, s_tmp);
-      TK_TRACE(4);
       for (int j = tid; j < ncand; j += kTopkThreads) {
         const uint64_t c = cand[j];
         if ((c & st.mask) >= st.prefix) sel[atomicAdd(&s_nsel, 1u)] = c;
@@ -298,7 +286,6 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   while (npad < nsel) npad <<= 1;
   for (int i = tid; i < npad; i += kTopkThreads)
     if (i >= nsel) sel[i] = 0ull;
-  TK_TRACE(5);
   // ---- bitonic sort, descending ------------------------------------------------------------------------------
   // Thread t owns elements 2t and 2t+1.  Compare-exchange steps with a stride of 32 or less stay inside a
   // warp (stride 1 inside the thread, the others by shuffle), so only the steps with a stride of 64 or more
@@ -369,7 +356,6 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
     }
   }
   __syncthreads();
-  TK_TRACE(6);
   for (int i = tid; i < p.k; i += kTopkThreads) {
     if (i < nsel) {
       const uint64_t c = sel[i];
@@ -381,14 +367,6 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
     }
   }
 }
-
-#ifdef DSV32_TOPK_TRACE
-}  // namespace dsv32
-extern "C" int dsv32_debug_topk_trace(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, dsv32::g_topk_trace, sizeof(dsv32::g_topk_trace));
-}
-namespace dsv32 {
-#endif
 
 int launch_topk(const TopkParams& p, int rows, cudaStream_t stream) {
   if (rows <= 0) return DSV32_OK;

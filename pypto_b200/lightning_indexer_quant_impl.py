@@ -67,7 +67,10 @@ def indexer_scores_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale
         rt.check_tensor(topk_scores, "topk_scores", torch.float32, (t, int(selected_count)))
         tensors.append(topk_scores)
     if scores_out is not None:
-        rt.check_tensor(scores_out, "scores_out", torch.float32, (t, ld))
+        rt.check_tensor(scores_out, "scores_out", torch.float32, (t, None))  # rows may be longer than the page table
+        if scores_out.shape[1] < ld:
+            raise ValueError(f"scores_out: rows of {scores_out.shape[1]} scores, need at least {ld}")
+        ld = scores_out.shape[1]
         tensors.append(scores_out)
     if dots_out is not None:
         rt.check_tensor(dots_out, "dots_out", torch.int32, (t, 64, ld))

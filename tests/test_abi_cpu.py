@@ -49,7 +49,7 @@ def test_host_side_rejections(lib):
     assert lib.dsv32_sfa_quant(None, None) == -1
     assert b"NULL" in lib.dsv32_last_error()
     a = _lib.SfaArgs()
-    a.b, a.s1, a.n_q, a.topk, a.block_size, a.max_blocks = 1, 1, 100, 2048, 128, 1
+    a.b, a.s1, a.n_q, a.topk, a.block_size, a.max_blocks = 1, 1, 129, 2048, 128, 1
     assert lib.dsv32_sfa_quant(C.byref(a), None) == -1
     assert b"n_q" in lib.dsv32_last_error()
     i = _lib.IndexerArgs()

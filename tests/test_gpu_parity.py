@@ -184,6 +184,45 @@ def test_indexer_key_range_shards_merge_to_global_topk():
     assert torch.equal(orc.merge_topk_candidates(cand_s, cand_i, k), full[:, 0])
 
 
+@pytest.mark.parametrize("act_seq,s1", [([3000, 700], 8), ([5000], 64), ([260, 9000], 5)])
+def test_indexer_many_query_tokens_per_request(act_seq, s1):
+    """More than four query tokens per request (a prefill-style chunk): the kernel walks the tokens in groups of
+    four (grid.z), the last group may be partial.  Checked like the ragged cases: scores, top-k sets, pads."""
+    d = helpers.gen_indexer_inputs(300 + s1, act_seq, s1=s1, extra_blocks=2)
+    res, tsc, scores, dots = _run_indexer(d, want_dots=True)
+    _check_indexer_against_oracle(d, res, scores)
+    for bi, L in enumerate(act_seq):   # bit-exact int32 dot products of the first and the last token of a request
+        rows = orc.paged_rows(d["block_table"][bi], torch.arange(L), 128)
+        keys = d["key"].reshape(-1, 128)[rows].to(torch.int32)
+        for si in (0, s1 - 1):
+            t = bi * s1 + si
+            assert torch.equal(dots[t, :, :L], d["query"][t].to(torch.int32) @ keys.t())
+
+
+def test_indexer_sequence_longer_than_page_table_is_clamped_and_reported():
+    """act_seq beyond max_blocks * 128: status BAD_INDEX, nothing written past the page table's capacity (a guard
+    region after every score row stays untouched), the keys the table does describe are still scored."""
+    import pypto_b200
+    from pypto_b200.lightning_indexer_quant_impl import indexer_scores_topk
+    d = helpers.gen_indexer_inputs(12, [1100, 1152], s1=2)       # 9 blocks per request
+    max_blocks = d["block_table"].shape[1]
+    cap = max_blocks * 128
+    good, _, good_scores, _ = _run_indexer(dict(d, act_seq=torch.tensor([cap, cap], dtype=torch.int32)))
+    d["act_seq"] = torch.tensor([cap + 300, 1152], dtype=torch.int32)
+    c = _cuda(d)
+    t, guard = d["query"].shape[0], 64 * 128
+    res = torch.zeros((t, 1, 2048), dtype=torch.int32, device=DEV)
+    scores = torch.full((t, cap + guard), 12345.0, dtype=torch.float32, device=DEV)
+    indexer_scores_topk(c["query"], c["q_scale"], c["key"], c["k_scale"], c["weights"], c["act_seq"], c["block_table"],
+                        res, 2048, scores_out=scores)
+    with pytest.raises(RuntimeError, match="status"):
+        pypto_b200.check_status()
+    sc = scores.cpu()
+    assert (sc[:, cap:] == 12345.0).all()
+    assert torch.equal(sc[:2, :cap], good_scores[:2, :cap])      # request 0: every key of its nine pages
+    assert torch.equal(res.cpu()[1], good[1])                    # its last token sees all of them in both runs
+
+
 def test_indexer_bad_page_table_sets_status_not_fault():
     import pypto_b200
     d = helpers.gen_indexer_inputs(3, [600], s1=1)
@@ -296,6 +335,8 @@ def test_scfa_reference_golden_fixture():
     (7, [5000], [1], 64, {}),                                                  # one token: fewer query rows than the 128-row tile
     (8, [300], [1], 32, {"topk": 64}),
     (9, [2100, 900, 3000], [2, 3, 4], 64, {"holes": 37}),                      # paired tokens with -1 entries among the selected
+    (10, [2100, 300, 129], [2, 4, 3], 16, {}),                                 # 16 heads: both tokens of a pair in one warp
+    (11, [900, 5000], [3, 2], 48, {"holes": 11}),                              # 48 heads: a warp with heads of both tokens
 ])
 def test_scfa_seeded_cases(seed, ori_seq, s1_list, nq, kw):
     d = helpers.gen_scfa_inputs(700 + seed, ori_seq, s1_list, nq=nq, **kw)
@@ -436,6 +477,8 @@ def test_cfa_reference_golden_fixture():
     (2, [65536, 130, 700, 50], 2, 64, 128),   # 512 compressed rows; a context shorter than the window
     (3, [3000, 5, 1, 2], 3, 64, 4),       # compression ratio 4: 750 compressed rows; tokens with no key at all
     (4, [2100, 4000], 1, 128, 4),         # 128 heads
+    (5, [2100, 130, 9], 2, 16, 4),        # 16 heads: both tokens of a pair in one warp
+    (6, [700, 3000], 3, 48, 128),         # 48 heads: a warp with heads of both tokens
 ])
 def test_cfa_seeded_cases(seed, ori_seq, s1, nq, cmp_ratio):
     d = _as_cfa_inputs(helpers.gen_scfa_inputs(800 + seed, ori_seq, [s1] * len(ori_seq), nq=nq, cmp_ratio=cmp_ratio), s1)
@@ -477,6 +520,8 @@ def test_win_attention_reference_golden_fixture():
     (3, [1000, 40], [2, 1], 128, 300),              # 128 heads; a window over more than two pages
     (4, [1, 2, 3, 200], [2, 2, 2, 7], 64, 128),     # paired tokens: the first of a pair without any key; an odd count
     (5, [500, 600], [2, 4], 32, 128),               # 32 heads, two tokens per CTA
+    (6, [500, 3, 129], [2, 4, 3], 16, 128),         # 16 heads: both tokens of a pair in one warp
+    (7, [260, 90], [3, 2], 48, 128),                # 48 heads: a warp with heads of both tokens
 ])
 def test_win_attention_seeded_cases(seed, ori_seq, s1_list, nq, win):
     d = helpers.gen_scfa_inputs(900 + seed, ori_seq, s1_list, nq=nq, win_size=win)
@@ -582,9 +627,17 @@ def test_sfa_ragged_edges_vs_oracle(act_seq, s1):
 @pytest.mark.parametrize("nq,topk,act_seq", [(64, 2048, [2600, 90]), (128, 512, [3000, 300]), (128, 1024, [1024, 5000]),
                                              (64, 1024, [700])])
 def test_sfa_other_head_counts_and_selection_sizes(nq, topk, act_seq):
-    """64 heads run on the warp-level MMA kernel; a smaller top-k shortens every index row."""
+    """64 heads fill half of the 128-row tile; a smaller top-k shortens every index row."""
     d = helpers.gen_sfa_inputs(40 + nq + topk, act_seq, s1=2, nq=nq, topk=topk)
     _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
+
+
+@pytest.mark.parametrize("nq,act_seq,s1", [(16, [2600, 90], 2), (48, [700], 3), (1, [300], 1), (96, [2100], 2)])
+def test_sfa_head_counts_below_the_tile(nq, act_seq, s1):
+    """Fewer than 128 heads: the heads of a token are the first rows of the 128-row tile, the rest idle."""
+    d = helpers.gen_sfa_inputs(140 + nq, act_seq, s1=s1, nq=nq)
+    _assert_attention_close(_run_sfa(d), _sfa_oracle(d))
+    _assert_attention_close(_run_sfa(d, kv_splits=3), _sfa_oracle(d))
 
 
 def test_sfa_negative_index_inside_prefix_is_skipped():
