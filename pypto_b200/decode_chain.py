@@ -18,8 +18,30 @@ from .sparse_flash_attention_quant_impl import SaTileShapeConfig, sparse_flash_a
 STEP_INPUTS = ("x", "q_norm", "q_norm_scale", "cos", "sin", "cache_index", "q_nope", "q_rope")
 
 
+class PackedTensors:
+    """A set of named tensors laid out back to back (256-byte aligned) in ONE byte buffer, on a device or in
+    pinned host memory, so that the whole set moves with a single copy.  `views[name]` are typed views."""
+
+    def __init__(self, like: dict, device, pin=False):
+        self.offsets, pos = {}, 0
+        for k, v in like.items():
+            self.offsets[k] = pos
+            pos += (v.numel() * v.element_size() + 255) // 256 * 256
+        self.nbytes = pos
+        self.buf = torch.empty(pos, dtype=torch.uint8, device=device)
+        if pin:
+            self.buf = self.buf.pin_memory()
+        self.views = {}
+        for k, v in like.items():
+            n = v.numel() * v.element_size()
+            self.views[k] = self.buf[self.offsets[k]:self.offsets[k] + n].view(v.dtype).view(v.shape)
+            self.views[k].copy_(v)
+
+
 class SparseDecodeStep:
-    def __init__(self, w, nq=128, topk=2048):
+    def __init__(self, w, nq=128, topk=2048, acts=None):
+        """`w`: a synth.DecodeWorkload (caches, page table, weights: device-resident state).  `acts`: the per-step
+        activations (a dict with the STEP_INPUTS names); default: the ones that come with the workload."""
         self.w = w
         dev = w.k_nope.device
         t = w.t
@@ -33,18 +55,22 @@ class SparseDecodeStep:
         self.softmax_scale = 576 ** -0.5
         self._cfg = (IndexerPrologQuantConfigs(), IndexerPrologQuantAttr(eps=1e-6), LightningIndexerConfigs(),
                      SaTileShapeConfig())
-        self._dev_in = {k: getattr(w, k) for k in STEP_INPUTS}
+        acts = acts if acts is not None else {k: getattr(w, k) for k in STEP_INPUTS}
+        self.dev_pack = PackedTensors({k: acts[k] for k in STEP_INPUTS}, dev)
+        self._dev_in = self.dev_pack.views
+        self.host_pack = None
         self.host_in = None
         self.host_out = None
 
     # ---- end-to-end staging -----------------------------------------------------------------------
     def enable_host_io(self):
-        """Keep pinned host copies of the per-step activations and a pinned output buffer."""
-        self.host_in = {k: v.cpu().pin_memory() for k, v in self._dev_in.items()}
+        """Keep a pinned host copy of the per-step activations (one contiguous buffer: one copy per step) and a
+        pinned output buffer.  Returns the bytes per step in each direction."""
+        self.host_pack = PackedTensors(self._dev_in, "cpu", pin=True)
+        self.host_in = self.host_pack.views
         self.host_out = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
-        h2d = sum(v.numel() * v.element_size() for v in self.host_in.values())
         d2h = self.host_out.numel() * self.host_out.element_size()
-        return h2d, d2h
+        return self.host_pack.nbytes, d2h
 
     # ---- stages -------------------------------------------------------------------------------------
     def prolog(self):
@@ -102,8 +128,7 @@ class SparseDecodeStep:
 
     def step_from_host(self):
         """End-to-end step: pinned host activations -> device, the three stages, output -> pinned host."""
-        for k, h in self.host_in.items():
-            self._dev_in[k].copy_(h, non_blocking=True)
+        self.dev_pack.buf.copy_(self.host_pack.buf, non_blocking=True)
         self.step()
         self.host_out.copy_(self.out, non_blocking=True)
         return self.host_out
@@ -115,7 +140,7 @@ class HostPipelinedDecode:
     Every step still copies its own activations from pinned host memory and returns its own attention
     output to pinned host memory, but on separate streams: while step k runs, the inputs of step k+1 are
     copied in and the output of step k-1 is copied out (two device buffers per direction, events between the
-    three streams).  `submit(host_inputs)` enqueues one step and returns the pinned tensor its output will land
+    three streams).  `submit(host_pack)` (a pinned PackedTensors of the step's activations) enqueues one step and returns the pinned tensor its output will land
     in; `drain()` makes the current stream wait for everything submitted so far.
     """
 
@@ -125,7 +150,8 @@ class HostPipelinedDecode:
         self.dev = dev
         self.s_in = torch.cuda.Stream(dev)
         self.s_out = torch.cuda.Stream(dev)
-        self.dev_in = [dict(step._dev_in), {k: v.clone() for k, v in step._dev_in.items()}]  # both sets valid from the start
+        self.dev_packs = [step.dev_pack, PackedTensors(step._dev_in, dev)]  # both sets valid from the start
+        self.dev_in = [p.views for p in self.dev_packs]
         self.dev_out = [step.out, torch.empty_like(step.out)]
         self.host_out = [torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory() for _ in range(2)]
         self.in_ready = [torch.cuda.Event() for _ in range(2)]
@@ -139,7 +165,7 @@ class HostPipelinedDecode:
                 step._dev_in, step.out = self.dev_in[p], self.dev_out[p]
                 self.graphs.append(step.capture()[0])
 
-    def submit(self, host_inputs):
+    def submit(self, host_pack: PackedTensors):
         step, p = self.step, self.k & 1
         run = torch.cuda.current_stream(self.dev)
         if self.k >= 2:
@@ -147,8 +173,7 @@ class HostPipelinedDecode:
         else:
             self.s_in.wait_stream(run)                   # everything enqueued before the first steps
         with torch.cuda.stream(self.s_in):
-            for name, h in host_inputs.items():
-                self.dev_in[p][name].copy_(h, non_blocking=True)
+            self.dev_packs[p].buf.copy_(host_pack.buf, non_blocking=True)   # all activations of the step: one copy
             self.in_ready[p].record(self.s_in)
         run.wait_event(self.in_ready[p])
         if self.k >= 2:

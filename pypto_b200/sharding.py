@@ -59,6 +59,12 @@ def key_range_for_rank(max_ctx: int, rank: int, world: int, block_size: int = 12
     return begin, (INT32_MAX if rank == world - 1 else end)
 
 
+def token_slice_for_rank(n_tokens: int, rank: int, world: int):
+    """Contiguous slice [first, last + 1) of a request's query tokens whose attention `rank` runs."""
+    per = math.ceil(n_tokens / world)
+    return min(rank * per, n_tokens), min((rank + 1) * per, n_tokens)
+
+
 def _cuda_local_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key, block_table,
                      selected_count, key_begin, key_end):
     from .lightning_indexer_quant_impl import indexer_scores_topk

@@ -116,3 +116,64 @@ def make_decode_workload(ctx, s1, seed, device, nq=128, block_size=128):
         hadamard=sylvester_hadamard(128, bf, dev), x=x, q_norm=q_norm, q_norm_scale=q_norm_scale,
         cos=torch.cos(ang).to(bf), sin=torch.sin(ang).to(bf), cache_index=cache_index,
         q_nope=randn((t * nq, 512)), q_rope=randn((t * nq, 64)))
+
+
+def make_step_activations(w: DecodeWorkload, seed, nq=128):
+    """Another set of per-step activations for the same workload (same shapes, distributions and cache positions,
+    different values): rotating between sets keeps a timed loop from replaying the same queries and top-k rows."""
+    dev = w.k_nope.device
+    g = torch.Generator(device=dev).manual_seed(seed)
+    t, bf = w.t, torch.bfloat16
+
+    def randn(shape):
+        return torch.randn(shape, generator=g, device=dev).to(bf)
+
+    qr = torch.randn((t, 1536), generator=g, device=dev)
+    amax = qr.abs().amax(-1, keepdim=True)
+    ang = torch.rand((t, 64), generator=g, device=dev) * 2 * math.pi
+    return dict(x=randn((t, 7168)), q_norm=torch.round(qr * (127 / amax)).to(torch.int8),
+                q_norm_scale=(amax / 127).float().contiguous(), cos=torch.cos(ang).to(bf), sin=torch.sin(ang).to(bf),
+                cache_index=w.cache_index.clone(), q_nope=randn((t * nq, 512)), q_rope=randn((t * nq, 64)))
+
+
+def make_long_request(ctx, s1, seed, device, token_slice=None, sample=None, block_size=128, nq=128):
+    """One long request (prefill-style chunk): `ctx` keys in both paged caches and `s1` query tokens, the i-th of
+    which sees ctx - s1 + 1 + i keys.  Everything is drawn from CPU generators (the same bits on every rank and in
+    the CPU tests) and then moved to `device`.  The index-side query tensors cover all s1 tokens; the attention
+    queries only `token_slice` = (first, last + 1) (default: all).  With `sample` = n the query side is cut down
+    to n tokens spread evenly over the chunk and `eff` holds their valid-key counts (CPU baseline / oracle checks).
+    Returns a dict."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    blocks = math.ceil(ctx / block_size)
+    rows = blocks * block_size
+    block_table = torch.randperm(blocks, generator=g).to(torch.int32).reshape(1, blocks)
+    idx_k = torch.randint(-127, 128, (blocks, block_size, 1, 128), generator=g, dtype=torch.int8)
+    idx_k_scale = (torch.rand((blocks, block_size, 1), generator=g) * 0.019 + 0.001).to(torch.float16)
+    k_nope = torch.randint(-127, 128, (rows, 512), generator=g, dtype=torch.int8)
+    k_rope = torch.randn((rows, 64), generator=g).to(bf)
+    k_scales = torch.rand((rows, 4), generator=g) * 0.019 + 0.001
+    q_int8 = torch.randint(-127, 128, (s1, 64, 128), generator=g, dtype=torch.int8)
+    q_scale = (torch.rand((s1, 64), generator=g) * 0.019 + 0.001).to(torch.float16)
+    weights = (torch.randn((s1, 64), generator=g) * 0.1).to(torch.float16)
+    if sample is not None:
+        pick = sorted({int(round(j * (s1 - 1) / max(sample - 1, 1))) for j in range(sample)})
+    else:
+        t0, t1 = token_slice if token_slice is not None else (0, s1)
+        pick = list(range(t0, t1))
+    qn, qr = [], []
+    for i in pick:   # per-token generators: a token's attention query does not depend on which rank draws it
+        gi = torch.Generator().manual_seed(seed * 1000003 + i)
+        qn.append(torch.randn((nq, 512), generator=gi).to(bf))
+        qr.append(torch.randn((nq, 64), generator=gi).to(bf))
+    q_nope = torch.cat(qn) if qn else torch.empty((0, 512), dtype=bf)
+    q_rope = torch.cat(qr) if qr else torch.empty((0, 64), dtype=bf)
+    out = dict(block_table=block_table, act_seq=torch.tensor([ctx], dtype=torch.int32), idx_k=idx_k,
+               idx_k_scale=idx_k_scale, k_nope=k_nope, k_rope=k_rope, k_scales=k_scales, q_int8=q_int8, q_scale=q_scale,
+               weights=weights, q_nope=q_nope, q_rope=q_rope, tokens=pick)
+    if sample is not None:
+        sel = torch.tensor(pick, dtype=torch.long)
+        out.update(q_int8=q_int8[sel], q_scale=q_scale[sel], weights=weights[sel],
+                   eff=torch.tensor([ctx - s1 + 1 + i for i in pick], dtype=torch.int32))
+    dev = torch.device(device)
+    return {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in out.items()}

@@ -1368,14 +1368,16 @@ def test_host_pipelined_decode_matches_serial_steps():
     w = synth.make_decode_workload([3000, 700, 2600, 129], 2, 77, DEV)
     step = SparseDecodeStep(w)
     step.enable_host_io()
-    set_a = step.host_in
+    from pypto_b200.decode_chain import PackedTensors
+    set_a = step.host_pack            # the step's activations as one pinned buffer
     g = torch.Generator().manual_seed(5)
-    set_b = dict(set_a)
+    other = dict(set_a.views)
     for name in ("q_nope", "q_rope", "x"):
-        set_b[name] = (torch.randn(set_a[name].shape, generator=g) * 0.5).to(set_a[name].dtype).pin_memory()
+        other[name] = (torch.randn(other[name].shape, generator=g) * 0.5).to(other[name].dtype)
+    set_b = PackedTensors(other, "cpu", pin=True)
     want = {}
     for tag, hs in (("a", set_a), ("b", set_b)):
-        step.host_in = hs
+        step.host_pack = hs
         want[tag] = step.step_from_host().clone()
         torch.cuda.synchronize()
         want[tag] = step.host_out.clone()
@@ -1419,7 +1421,7 @@ def test_captured_step_matches_eager_step():
         assert torch.equal(got, want) and torch.equal(step.topk_res, want_topk)
     step.enable_host_io()
     pipe = HostPipelinedDecode(step, use_graphs=True)
-    bufs = [pipe.submit(step.host_in) for _ in range(3)]
+    bufs = [pipe.submit(step.host_pack) for _ in range(3)]
     pipe.drain()
     torch.cuda.synchronize()
     pypto_b200.check_status()

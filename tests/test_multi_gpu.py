@@ -1,0 +1,129 @@
+"""Two-GPU runs of the partitioned paths (one process per GPU, NCCL): skipped unless two CUDA devices are visible.
+
+* one long request: the index-key range is sharded, candidates are all-gathered and re-selected, attention runs on
+  the rank that owns each slice of the query chunk -- against the CPU oracle of the unsharded request;
+* a ragged decode batch assigned to the ranks by longest-processing-time-first: every rank runs the whole chain on
+  its own requests -- against the CPU oracle of those requests.
+The host-side logic of both (gloo ranks, no GPU) is covered in tests/test_sharding_cpu.py.
+"""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+WORLD = 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _long_request(rank, world):
+    """ctx 6000 / 37 query tokens: the second rank's key range holds the partly masked tail."""
+    import pypto_b200
+    from oracle import dsv32_oracle as orc
+    from pypto_b200 import sharding, synth
+    from pypto_b200.sparse_flash_attention_quant_impl import sparse_flash_attention_quant_d
+    dev = torch.device("cuda", rank)
+    L, s1, k = 6000, 37, 2048
+    t0, t1 = sharding.token_slice_for_rank(s1, rank, world)
+    d = synth.make_long_request(L, s1, 31, dev, token_slice=(t0, t1))
+    idx = sharding.sharded_indexer_topk(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"],
+                                        d["act_seq"], d["block_table"], k)
+    out = torch.empty((1, t1 - t0, 128, 512), dtype=torch.bfloat16, device=dev)
+    act_slice = torch.tensor([L - s1 + t1], dtype=torch.int32, device=dev)
+    sparse_flash_attention_quant_d(d["q_nope"], d["q_rope"], d["k_nope"], d["k_rope"], d["k_scales"],
+                                   idx[t0:t1].contiguous(), d["block_table"], act_slice, out, 128, 1, 576 ** -0.5, k, 128,
+                                   d["block_table"].shape[1], None)
+    pypto_b200.check_status(dev)
+    c = synth.make_long_request(L, s1, 31, "cpu", token_slice=(t0, t1))
+    ref_idx, ref_scores = orc.lightning_indexer(c["q_int8"], c["q_scale"], c["idx_k"], c["idx_k_scale"], c["weights"],
+                                                c["act_seq"], c["block_table"], k, return_scores=True)
+    got = idx.cpu()
+    for t in range(s1):
+        ok, ndiff, _ = orc.topk_sets_match(got[t], ref_idx[t, 0], ref_scores[0][t])
+        assert ok, (t, ndiff)
+    # attention of the own slice = the unsharded operator's rows of those tokens (on this rank's top-k)
+    q_full_n = torch.zeros((s1 * 128, 512), dtype=torch.bfloat16)
+    q_full_r = torch.zeros((s1 * 128, 64), dtype=torch.bfloat16)
+    q_full_n[t0 * 128:t1 * 128], q_full_r[t0 * 128:t1 * 128] = c["q_nope"], c["q_rope"]
+    ref = orc.sfa_quant(q_full_n, q_full_r, c["k_nope"], c["k_rope"], c["k_scales"], got, c["block_table"], c["act_seq"],
+                        128, 576 ** -0.5, tokens=range(t0, t1))
+    assert torch.allclose(out.cpu().float(), ref[:, t0:t1].float(), rtol=1e-2, atol=1e-2)
+
+
+def _ragged_batch(rank, world):
+    import pypto_b200
+    from oracle import dsv32_oracle as orc
+    from pypto_b200 import sharding, synth
+    from pypto_b200.decode_chain import SparseDecodeStep
+    dev = torch.device("cuda", rank)
+    ctx, s1 = [9000, 300, 2100, 4100, 1500, 129, 2047], 2
+    bins = sharding.lpt_assign([sharding.request_cost(c, s1) for c in ctx], world)
+    assert sorted(i for b in bins for i in b) == list(range(len(ctx)))
+    mine = [ctx[i] for i in bins[rank]]
+    w = synth.make_decode_workload(mine, s1, 500 + rank, dev)
+    step = SparseDecodeStep(w)
+    out = step.step()
+    pypto_b200.check_status(dev)
+    cpu = lambda t: t.detach().cpu()  # noqa: E731
+    ref_idx, ref_scores = orc.lightning_indexer(cpu(step.q_int8), cpu(step.q_scale).reshape(-1, 64), cpu(w.idx_k),
+                                                cpu(w.idx_k_scale), cpu(step.weights), cpu(w.act_seq), cpu(w.block_table),
+                                                2048, return_scores=True)
+    got_idx = cpu(step.topk_res)
+    for t in range(got_idx.shape[0]):
+        ok, nd, _ = orc.topk_sets_match(got_idx[t, 0], ref_idx[t, 0], ref_scores[t // s1][t % s1])
+        assert ok, (t, nd)
+    ref_out = orc.sfa_quant(cpu(w.q_nope), cpu(w.q_rope), cpu(w.k_nope), cpu(w.k_rope), cpu(w.k_scales),
+                            got_idx.reshape(-1, 2048), cpu(w.block_table), cpu(w.act_seq), 128, 576 ** -0.5)
+    assert torch.allclose(cpu(out).float(), ref_out.float(), rtol=1e-2, atol=1e-2)
+
+
+def _worker(rank, world, port, case, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60),
+                                device_id=torch.device("cuda", rank))
+        {"long": _long_request, "ragged": _ragged_batch}[case](rank, world)
+        dist.barrier()
+        ret[rank] = "ok"
+    except Exception as e:  # noqa: BLE001
+        ret[rank] = f"error: {type(e).__name__}: {e}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def _run(case):
+    if torch.cuda.device_count() < WORLD:
+        pytest.skip(f"needs {WORLD} CUDA devices")
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, WORLD, port, case, ret)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert not p.is_alive()
+    return dict(ret)
+
+
+def test_long_request_key_range_sharded_over_two_gpus():
+    assert _run("long") == {0: "ok", 1: "ok"}
+
+
+def test_ragged_batch_lpt_assigned_to_two_gpus():
+    assert _run("ragged") == {0: "ok", 1: "ok"}

@@ -36,6 +36,44 @@ def test_lpt_balances_ragged_batches():
     assert max(loads) / (sum(loads) / 8) < 1.05
 
 
+def test_token_slices_and_long_request_generator():
+    from pypto_b200 import synth
+    assert [sharding.token_slice_for_rank(4096, r, 8) for r in (0, 7)] == [(0, 512), (3584, 4096)]
+    assert [sharding.token_slice_for_rank(5, r, 4) for r in range(4)] == [(0, 2), (2, 4), (4, 5), (5, 5)]
+    full = synth.make_long_request(1000, 6, 9, "cpu")
+    part = synth.make_long_request(1000, 6, 9, "cpu", token_slice=(2, 5))
+    # the shared state and the index-side queries are the same bits on every rank; attention queries follow the slice
+    for k in ("block_table", "idx_k", "k_nope", "k_scales", "q_int8", "weights"):
+        assert torch.equal(full[k], part[k])
+    assert torch.equal(part["q_nope"], full["q_nope"][2 * 128:5 * 128])
+    smp = synth.make_long_request(1000, 6, 9, "cpu", sample=3)
+    assert smp["tokens"] == [0, 2, 5] and smp["eff"].tolist() == [995, 997, 1000]
+    assert torch.equal(smp["q_int8"], full["q_int8"][[0, 2, 5]])
+    assert torch.equal(smp["q_rope"][128:256], full["q_rope"][2 * 128:3 * 128])
+
+
+def test_packed_tensors_views_share_one_buffer():
+    from pypto_b200.decode_chain import PackedTensors
+    src = {"a": torch.arange(10, dtype=torch.int32), "b": torch.randn(3, 5).to(torch.bfloat16), "c": torch.tensor([7], dtype=torch.int64)}
+    pk = PackedTensors(src, "cpu")
+    for k, v in src.items():
+        assert torch.equal(pk.views[k], v) and pk.offsets[k] % 256 == 0
+    other = PackedTensors({k: torch.zeros_like(v) for k, v in src.items()}, "cpu")
+    other.buf.copy_(pk.buf)            # one copy moves every tensor
+    assert all(torch.equal(other.views[k], v) for k, v in src.items())
+
+
+def test_ragged_contexts_of_the_bench():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    ctx = bench.ragged_contexts(256, 1004)
+    assert len(ctx) == 256 and min(ctx) >= 64 and max(ctx) <= 131072
+    assert sum(c < 2048 for c in ctx) >= 26                      # every tenth request is forced below the top-k size
+    assert ctx == bench.ragged_contexts(256, 1004)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
