@@ -33,6 +33,7 @@ extern "C" {
 #define DSV32_STATUS_BAD_PAGE 1u    /* a page-table entry on the valid range was < 0 or >= number of blocks */
 #define DSV32_STATUS_BAD_INDEX 2u   /* a top-k index pointed outside the request's page table              */
 #define DSV32_STATUS_TIMEOUT 3u     /* a bounded device-side wait gave up (word 1 = location id)            */
+#define DSV32_STATUS_INTERNAL 4u    /* a kernel found its own launch state inconsistent (word 1 = location id) */
 
 /* ---------------------------------------------------------------------------------------
  * Sparse flash attention over the int8 paged latent cache.

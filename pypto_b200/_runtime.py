@@ -8,7 +8,8 @@ import torch
 from . import _lib
 
 _STATUS = {}
-STATUS_NAMES = {1: "bad page-table entry", 2: "top-k / cache index out of range", 3: "device-side wait timed out"}
+STATUS_NAMES = {1: "bad page-table entry", 2: "top-k / cache index out of range", 3: "device-side wait timed out",
+                4: "internal inconsistency in a kernel launch"}
 
 
 def require_cuda():

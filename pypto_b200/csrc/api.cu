@@ -32,15 +32,32 @@ int check_launch(const char* what) {
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Key splits of the attention kernel.  Its CTAs (one per token, half of the value dims and split) run one per SM
+// in waves; a CTA costs its key tiles plus about 3.5 tile times of set-up and epilogue, and a split run pays a
+// combine pass over the partial results.  The split count that minimises waves x (tiles per CTA + fixed cost) is taken; sequence lengths
+// live on the device, so every token is assumed to select `topk` keys.
 static int pick_sfa_splits(int t, int nq, int topk, int requested) {
+  (void)nq;
   const int max_splits = topk / 128 > 0 ? (topk / 128 < 16 ? topk / 128 : 16) : 1;
   if (requested > 0) return requested < max_splits ? requested : max_splits;
-  (void)nq;
-  const int ctas = t * 2;  // one CTA per token and half of the value dims
-  if (ctas >= 148) return 1;
-  int s = (2 * 148 + ctas - 1) / ctas;
-  if (s > max_splits) s = max_splits;
-  return s < 1 ? 1 : s;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = (topk + 63) / 64;
+  int best = 1;
+  double best_cost = 0.0;
+  for (int s = 1; s <= max_splits; ++s) {
+    const long long ctas = 2ll * t * s;
+    const long long waves = (ctas + sms - 1) / sms;
+    const int per = (((topk + s - 1) / s) + 63) / 64;  // tiles of one CTA
+    if (s > 1 && per * (s - 1) >= tiles) continue;     // a split that would be empty
+    // combine pass: every split writes and re-reads a 128 x 512 fp32 partial (0.5 MB: 0.034 tile times at copy speed)
+    const double cost = static_cast<double>(waves) * (per + 3.5) + (s > 1 ? 0.5 + 0.034 * t * s : 0.0);
+    if (s == 1 || cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 
 }  // namespace dsv32

@@ -12,8 +12,8 @@
 // stages of 64 gathered keys x 576 dims (nine 64x64 bf16 chunks, 128-byte swizzle).  A stage is read
 // K-major by S = Q K^T and MN-major (as V) by O += P V, so the dequantised rows are written once.
 // Warps: 0 = issuer of the S MMAs / tensor-memory owner, 1..4 = softmax + O rescale + epilogue (one head per
-// thread, so row max / row sum need no shuffles; lane 0 of warp 1 also issues the PV MMAs), 5..12 = gather +
-// dequantise producers.  A stage is refilled in two steps: the chunks only S reads (the other half's value
+// thread, so row max / row sum need no shuffles; lane 0 of warp 1 also issues the PV MMAs), 5..20 = gather +
+// dequantise producers (raw rows held in registers two tiles ahead of their use).  A stage is refilled in two steps: the chunks only S reads (the other half's value
 // dims, the rope dims) as soon as S of the tile two back has completed, this CTA's own value chunks once its
 // PV has.  The cache row of every selected key comes from a pre-pass (sfa_row_ids_kernel).
 // The running maximum is only raised when a tile exceeds it by more than 2^8 (warp-uniform decision), so
@@ -29,7 +29,8 @@
 
 namespace dsv32 {
 
-constexpr int kStThreads = 416;          // 13 warps
+constexpr int kStProducerWarps = 16;
+constexpr int kStThreads = (5 + kStProducerWarps) * 32;   // 21 warps: MMA issuer, 4 softmax, 16 gather + dequantise
 constexpr int kStTile = 64;              // keys per tile
 constexpr int kStChunkBytes = kStTile * 128;       // one 64-dim chunk of a K stage (8 KB)
 constexpr int kStStageBytes = 9 * kStChunkBytes;   // 73,728
@@ -37,11 +38,13 @@ constexpr int kStQChunkBytes = 128 * 128;          // one 64-dim chunk of Q (16 
 constexpr int kStQsBytes = 5 * kStQChunkBytes;     // dims 256..575
 constexpr int kStOffQ = 2 * kStStageBytes;
 constexpr int kStOffValid = kStOffQ + kStQsBytes;  // int[2][64]
-constexpr int kStOffRing = kStOffValid + 2 * kStTile * 4;   // int[8 producer warps][4 tiles][8 rows]: row ids in flight
-constexpr int kStOffBars = kStOffRing + 8 * 4 * 8 * 4;
+constexpr int kStRingTiles = 8;            // tiles of row ids in flight per producer warp
+constexpr int kStOffRing = kStOffValid + 2 * kStTile * 4;   // int[16 producer warps][8 tiles][4 rows]
+constexpr int kStOffBars = kStOffRing + kStProducerWarps * kStRingTiles * 4 * 4;
 constexpr int kStNumBars = 2 + 2 + 2 + 2 + 1;      // full[2], s_full[2], p_ready[2], pv_done[2], q_ready
 constexpr int kStOffTmem = kStOffBars + kStNumBars * 8;
-constexpr size_t kStSmemBytes = kStOffTmem + 16 + 1024;
+constexpr size_t kStSmemBytes = kStOffTmem + 16;   // no alignment slack: the kernel checks that its window is 1024-byte aligned
+static_assert(kStSmemBytes <= 232448, "shared memory of one CTA (227 KB)");
 
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;
 
@@ -65,19 +68,56 @@ struct StPrefetchT {
   bool valid;
 };
 
+// Two fp32 operations per instruction (sm_100 packed arithmetic): the int8 -> float -> scaled path of the
+// dequantisation is issue-bound, so halving its instruction count is what counts.
+__device__ __forceinline__ uint64_t f2_pack(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  uint32_t l, h;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(l), "=r"(h) : "l"(v));
+  lo = __uint_as_float(l);
+  hi = __uint_as_float(h);
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {  // {lo, hi} -> bf16 pair, round to nearest even
+  uint32_t lo, hi, d;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+  return d;
+}
+
+// 16 int8 -> 16 bf16 = bf16_rn( float(int8) * scale ), bit for bit as the golden: float(int8) is built without
+// the conversion pipe -- (2^23 + (x ^ 0x80)) read as a float, minus (2^23 + 128), is exactly x -- and the product
+// is one fp32 rounding followed by the bf16 rounding.
 __device__ __forceinline__ void st_dequant16(const int4& raw, float sc, uint4& lo, uint4& hi) {
-  // float(int8) without the conversion pipe: (2^23 + (x ^ 0x80)) as a float, minus (2^23 + 128), is exactly x
   const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint64_t bias = f2_pack(0xCB000080u, 0xCB000080u);  // -(2^23 + 128) twice
+  const uint64_t sc2 = f2_pack(__float_as_uint(sc), __float_as_uint(sc));
   uint32_t o[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t u = static_cast<uint32_t>(w[i]) ^ 0x80808080u;
-    const float f0 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.0f) * sc;
-    const float f1 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.0f) * sc;
-    const float f2 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.0f) * sc;
-    const float f3 = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f) * sc;
-    o[2 * i] = pack_bf16x2(f0, f1);
-    o[2 * i + 1] = pack_bf16x2(f2, f3);
+    const uint64_t a = f2_pack(__byte_perm(u, 0x4B000000u, 0x7540), __byte_perm(u, 0x4B000000u, 0x7541));
+    const uint64_t b = f2_pack(__byte_perm(u, 0x4B000000u, 0x7542), __byte_perm(u, 0x4B000000u, 0x7543));
+    o[2 * i] = f2_to_bf16x2(f2_mul(f2_add(a, bias), sc2));
+    o[2 * i + 1] = f2_to_bf16x2(f2_mul(f2_add(b, bias), sc2));
   }
   lo = make_uint4(o[0], o[1], o[2], o[3]);
   hi = make_uint4(o[4], o[5], o[6], o[7]);
@@ -304,14 +344,20 @@ template <int kMode>
 __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_constant__ CUtensorMap qn_map,
                                                                const __grid_constant__ CUtensorMap qr_map,
                                                                SfaParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The swizzled tiles need a 1024-byte aligned base.  The kernel has no static shared memory, so its dynamic
+  // window starts on such a boundary; should that ever not hold, the CTA reports it and leaves before any barrier.
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0) report_status(p.status, DSV32_STATUS_INTERNAL, 40, smem_u32(smem));
+    return;
+  }
   unsigned char* k_s = smem;
   unsigned char* q_s = smem + kStOffQ;
   int* valid_s = reinterpret_cast<int*>(smem + kStOffValid);
   int* ring_s = reinterpret_cast<int*>(smem + kStOffRing);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStOffBars);
-  uint64_t* full_bar = bars;         // [2] producers -> MMA            (8 warp arrivals)
+  uint64_t* full_bar = bars;         // [2] producers -> MMA            (one arrival per producer warp)
   uint64_t* sfull_bar = bars + 2;    // [2] S complete -> softmax       (tcgen05.commit)
   uint64_t* pready_bar = bars + 4;   // [2] P stored -> MMA             (128 thread arrivals)
   uint64_t* pvdone_bar = bars + 6;   // [2] PV complete -> producers / MMA / softmax (tcgen05.commit)
@@ -362,8 +408,8 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     if (lane == 0) {
       tma_prefetch_desc(&qn_map);
       tma_prefetch_desc(&qr_map);
-      mbar_init(&full_bar[0], 8);
-      mbar_init(&full_bar[1], 8);
+      mbar_init(&full_bar[0], kStProducerWarps);
+      mbar_init(&full_bar[1], kStProducerWarps);
       mbar_init(&sfull_bar[0], 1);
       mbar_init(&sfull_bar[1], 1);
       mbar_init(&pready_bar[0], 128);
@@ -384,51 +430,51 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
 
   if (warp == 0) {
     // ================================ MMA issuer ==========================================================
-    if (lane == 0) {
+    // The whole warp runs the loop (uniform operands, no divergent region); lane 0 issues.
+    const bool leader = lane == 0;
+    if (leader) {
       // Q dims 256..575 -> shared memory (TMA, 128-byte swizzle): nope chunks 4..7 and the rope chunk
       mbar_arrive_expect_tx(q_bar, kCompress ? 4 * kStQChunkBytes : kStQsBytes);
       for (int c = 0; c < 4; ++c)
         tma_load_2d(q_s + c * kStQChunkBytes, &qn_map, (4 + c) * 128, tok * p.nq, q_bar);
       if constexpr (!kCompress) tma_load_2d(q_s + 4 * kStQChunkBytes, &qr_map, 0, tok * p.nq, q_bar);
+    }
+    __syncwarp();
+    constexpr uint32_t idesc_s = umma_idesc_bf16(128, kStTile, false, false);
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_bar, 0, p.status, 10));
+    const uint32_t tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
 
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, kStTile, false, false);
-      bool ok = mbar_wait(q_bar, 0, p.status, 10);
+    // Descriptors are assembled from precomputed 32-bit halves: per MMA only the start-address field moves.
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+    auto desc = [](uint32_t lo) -> uint64_t {
+      uint64_t d;
+      asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+      return d;
+    };
+    const uint32_t q_lo = ((smem_u32(q_s) >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t stage0_lo = ((smem_u32(k_s) >> 4) & 0x3FFFu) | (1u << 16);   // K-major (S)
 
-      // Descriptors are assembled from precomputed 32-bit halves: per MMA only the start-address field moves.
-      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
-      auto desc = [](uint32_t lo) -> uint64_t {
-        uint64_t d;
-        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
-        return d;
-      };
-      const uint32_t q_lo = ((smem_u32(q_s) >> 4) & 0x3FFFu) | (1u << 16);
-      uint32_t stage_lo[2];
+    // This warp issues S = Q K^T of every tile; PV is issued by a warp of the softmax group as soon as
+    // P is stored, so that it never waits behind the issue of the next S (the issuer blocks while the
+    // tensor-core queue is full).  MMAs of both issuers execute in the order they enter the queue; S(i+2),
+    // which overwrites the buffer PV(i) reads P from, is only issued after the producers have seen PV(i)
+    // complete (they refill its K stage before signalling `full`).
+    for (int i = 0; ok && i < ntiles; ++i) {
+      const int s = i & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i >> 1) & 1, p.status, 11));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d = tbase + kColS + s * kStTile;
+      const uint32_t klo = stage0_lo + s * (kStStageBytes >> 4);
 #pragma unroll
-      for (int s = 0; s < 2; ++s)
-        stage_lo[s] = ((smem_u32(k_s + s * kStStageBytes) >> 4) & 0x3FFFu) | (1u << 16);   // K-major (S)
-
-      // This thread issues S = Q K^T of every tile; PV is issued by a thread of the softmax group as soon as
-      // P is stored, so that it never waits behind the issue of the next S (this thread blocks while the
-      // tensor-core queue is full).  MMAs of both threads execute in the order they enter the queue; S(i+2),
-      // which overwrites the buffer PV(i) reads P from, is only issued after the producers have seen PV(i)
-      // complete (they refill its K stage before signalling `full`).
-      for (int i = 0; ok && i < ntiles; ++i) {
-        const int s = i & 1;
-        ok = mbar_wait(&full_bar[s], (i >> 1) & 1, p.status, 11);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d = tmem_base + kColS + s * kStTile;
-        const uint32_t klo = stage_lo[s];
+      for (int ks = 0; ks < 16; ++ks)  // Q dims 0..255 from tensor memory
+        umma_f16_ts_if(leader, d, tbase + kColQ + ks * 8, desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)),
+                       idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < 16; ++ks)  // Q dims 0..255 from tensor memory
-          umma_f16_ts(d, tmem_base + kColQ + ks * 8, desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)),
-                      idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 16; ks < kSteps; ++ks)  // Q dims 256..575 (256..511 in mode 2) from shared memory
-          umma_f16_ss(d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
-                      desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
-        umma_commit(&sfull_bar[s]);
-      }
+      for (int ks = 16; ks < kSteps; ++ks)  // Q dims 256..575 (256..511 in mode 2) from shared memory
+        umma_f16_ss_if(leader, d, desc(q_lo + ((((ks >> 2) - 4) * kStQChunkBytes + (ks & 3) * 32) >> 4)),
+                       desc(klo + (((ks >> 2) * kStChunkBytes + (ks & 3) * 32) >> 4)), idesc_s, 1u);
+      umma_commit_if(leader, &sfull_bar[s]);
     }
   } else if (warp <= 4) {
     // ================================ softmax / epilogue ==================================================
@@ -461,13 +507,9 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], (i >> 1) & 1, p.status, 20))) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + kColS + s * kStTile;
-      uint32_t r0[32], r1[32];
-      tmem_ld_32x32b_x32(s_addr, r0);
-      tmem_ld_32x32b_x32(s_addr + 32, r1);
-      tmem_ld_wait();
       // Masking is only needed when the tile holds an invalid key (tail of the list, or a -1 entry).
       // A flag holds membership bits: bit 0 = a key of the token in lanes 0..63 (the only token unless two share
-      // the CTA), bit 1 = a key of the token in lanes 64..127; this warp's lanes all belong to one of them.
+      // the CTA), bit 1 = a key of the token in lanes 64..127.
       const int* vm = valid_s + s * kStTile;
       const int hb = !kCompress ? 1 : (head < p.nq ? 1 : (head < live_rows ? 2 : 3));   // idle lanes take every key
       // The shortcut must hold for every lane of the warp: with fewer than 32 heads per token a warp holds heads
@@ -475,16 +517,23 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       const uint32_t need_bits = __reduce_or_sync(0xffffffffu, static_cast<uint32_t>(hb == 3 ? 0 : hb));
       const bool all_valid = __all_sync(0xffffffffu, (static_cast<uint32_t>(vm[lane]) & need_bits) == need_bits &&
                                                          (static_cast<uint32_t>(vm[32 + lane]) & need_bits) == need_bits);
-      if (!all_valid) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (!(vm[j] & hb)) r0[j] = 0xff800000u;       // -inf
-          if (!(vm[32 + j] & hb)) r1[j] = 0xff800000u;
-        }
-      }
+      // The 64 scores of a row are read from tensor memory twice, 32 at a time -- once for the row maximum, once
+      // for the exponentials -- instead of being held in 64 registers: tensor-memory loads are cheap, and the
+      // register file is what limits the number of gather warps.
+      uint32_t r[32];
       float m_raw = -INFINITY;  // row maximum of the raw scores (the softmax scale is positive)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
+      for (int h = 0; h < 2; ++h) {
+        tmem_ld_32x32b_x32(s_addr + 32 * h, r);
+        tmem_ld_wait();
+        if (!all_valid) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (!(vm[32 * h + j] & hb)) r[j] = 0xff800000u;       // -inf
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+      }
       const float m_tile = m_raw * sc2;
       const bool need = m_tile > m_run + kRescaleThreshold;  // also true on the first non-empty tile (m_run = -inf)
       if (__any_sync(0xffffffffu, need)) {
@@ -508,46 +557,64 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         }
       }
       const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-      float lsum0 = 0.f, lsum1 = 0.f;
-      uint32_t pk[32];
+      // p = 2^(s*scale*log2e - m): packed fp32 arithmetic (two keys per FMA and per addition), one ex2 per key
+      const uint64_t sc22 = f2_pack(__float_as_uint(sc2), __float_as_uint(sc2));
+      const uint64_t negm2 = f2_pack(__float_as_uint(neg_m), __float_as_uint(neg_m));
+      uint64_t lsum_a = 0ull, lsum_b = 0ull;   // two pairs of partial row sums
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {  // p = 2^(s*scale*log2e - m): one FMA + one ex2 per key
-        const float p0 = fast_exp2(fmaf(__uint_as_float(r0[j]), sc2, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(r0[j + 1]), sc2, neg_m));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(r1[j]), sc2, neg_m));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(r1[j + 1]), sc2, neg_m));
-        lsum0 += p0 + p1;
-        lsum1 += p2 + p3;
-        pk[j >> 1] = pack_bf16x2(p0, p1);
-        pk[16 + (j >> 1)] = pack_bf16x2(p2, p3);
+      for (int h = 0; h < 2; ++h) {
+        tmem_ld_32x32b_x32(s_addr + 32 * h, r);
+        tmem_ld_wait();
+        if (!all_valid) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (!(vm[32 * h + j] & hb)) r[j] = 0xff800000u;
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float p0, p1, p2, p3;
+          f2_unpack(f2_fma(f2_pack(r[j], r[j + 1]), sc22, negm2), p0, p1);
+          f2_unpack(f2_fma(f2_pack(r[j + 2], r[j + 3]), sc22, negm2), p2, p3);
+          p0 = fast_exp2(p0);
+          p1 = fast_exp2(p1);
+          p2 = fast_exp2(p2);
+          p3 = fast_exp2(p3);
+          lsum_a = f2_add(lsum_a, f2_pack(__float_as_uint(p0), __float_as_uint(p1)));
+          lsum_b = f2_add(lsum_b, f2_pack(__float_as_uint(p2), __float_as_uint(p3)));
+          pk[j >> 1] = pack_bf16x2(p0, p1);
+          pk[(j >> 1) + 1] = pack_bf16x2(p2, p3);
+        }
+        // P (32 keys as 16 bf16 pairs) over the first half of the S buffer: columns 16h .. 16h+15 held scores
+        // that have been consumed (h = 1) or are this pass's own (h = 0); columns 32.. are still intact for h = 1
+        tmem_st_32x32b_x16(s_addr + 16 * h, pk);
       }
-      const float lsum = lsum0 + lsum1;
-      l_run += lsum;
-      tmem_st_32x32b_x32(s_addr, pk);  // P (64 keys as 32 bf16 pairs) over the first half of its S buffer
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(lsum_a, a0, a1);
+        f2_unpack(lsum_b, b0, b1);
+        l_run += (a0 + a1) + (b0 + b1);
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pready_bar[s]);
       if (warp == 1) {  // second MMA issuer: PV of this tile, as soon as all four softmax warps have stored P
-        bool okpv = true;
-        if (lane == 0) {
-          okpv = mbar_wait(&pready_bar[s], (i >> 1) & 1, p.status, 13);
-          if (okpv) {
-            constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 256, false, true);
-            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
-            const uint32_t a = smem_u32(k_s + s * kStStageBytes);
-            const uint32_t vlo = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);
-            tc_fence_after();
+        // (the whole warp waits and computes the uniform operands; lane 0 issues)
+        if (!__all_sync(0xffffffffu, mbar_wait(&pready_bar[s], (i >> 1) & 1, p.status, 13))) { ok = false; break; }
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 256, false, true);
+        constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+        const uint32_t tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
+        const uint32_t a = smem_u32(k_s) + s * kStStageBytes;
+        const uint32_t vlo = (((a + 4 * half * kStChunkBytes) >> 4) & 0x3FFFu) | ((kStChunkBytes >> 4) << 16);
+        tc_fence_after();
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
-              uint64_t d;
-              asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(vlo + ((kk * 2048) >> 4)), "r"(kDescHi));
-              umma_f16_ts(tmem_base + kColO, tmem_base + kColS + s * kStTile + kk * 8, d, idesc_pv,
-                          (i > 0 || kk > 0) ? 1u : 0u);
-            }
-            umma_commit(&pvdone_bar[s]);
-          }
+        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per instruction; V = this CTA's four 64-dim chunks, MN-major
+          uint64_t d;
+          asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(vlo + ((kk * 2048) >> 4)), "r"(kDescHi));
+          umma_f16_ts_if(lane == 0, tbase + kColO, tbase + kColS + s * kStTile + kk * 8, d, idesc_pv,
+                         (i > 0 || kk > 0) ? 1u : 0u);
         }
-        if (!__all_sync(0xffffffffu, okpv)) { ok = false; break; }
+        umma_commit_if(lane == 0, &pvdone_bar[s]);
       }
     }
     // ---- epilogue: O / l -> bf16 (or fp32 partial + log-sum-exp for a key split) -----------------------------
@@ -602,34 +669,36 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
     }
   } else {
     // ================================ gather + dequantise producers ========================================
-    const int ptid = tid - 160;            // 0..255
-    const int pwarp_lane0 = (lane == 0);
-    const int gkey = ptid >> 3, gpart = ptid & 7;  // two passes of 32 keys; 16-byte chunks gpart + 8*j
-    // The cache row of every selected key was resolved by sfa_row_ids_kernel (row + 1, 0 = none).  Row ids
-    // travel global -> shared memory with 4-byte cp.async three tiles ahead, so no register holds a loaded
-    // value across the dequantisation of a tile: lanes 0..7 of a producer warp fetch the ids of the warp's
-    // eight rows of a tile (row = pass*32 + gkey, gkey = 4*warp + 0..3).
-    const int pw = warp - 5;
-    int* ring = ring_s + pw * 32;
+    // 512 threads: thread (gkey, gpart) owns the 16-byte column gpart of every 128-byte group of key row gkey of
+    // each tile.  Raw rows travel global -> registers TWO tiles ahead of their use (two register sets that
+    // alternate by tile parity; one set for the bf16 caches, whose rows are twice as wide), are dequantised and
+    // stored into the swizzled K stage once the MMAs of the tile two back have released it.
+    const int ptid = tid - 160;            // 0..511
+    const int gkey = ptid >> 3, gpart = ptid & 7;
+    const int pw = warp - 5;               // this warp's rows of a tile: 4*pw .. 4*pw + 3
+#ifndef DSV32_SFA_DEPTH
+#define DSV32_SFA_DEPTH 1
+#endif
+    constexpr int kDepth = kBf16 ? 1 : DSV32_SFA_DEPTH;  // register sets = tiles of raw rows in flight
+    // The cache row of every selected key was resolved by the pre-pass (row + 1, 0 = none).  Row ids travel
+    // global -> shared memory with 4-byte cp.async six tiles ahead (ring of eight tiles per warp), so that the
+    // L2 prefetch (four tiles ahead) and the loads (kDepth tiles ahead) find them in place.
+    int* ring = ring_s + pw * (kStRingTiles * 4);
     const int32_t* ids_row = p.row_ids + static_cast<size_t>(tok) * p.topk;
     auto fetch_ids = [&](int tile) {
-      if (lane < 8) {
-        const int j = k_lo + tile * kStTile + (lane >> 2) * 32 + 4 * pw + (lane & 3);
+      if (lane < 4) {
+        const int j = k_lo + tile * kStTile + 4 * pw + lane;
         const bool in = tile < ntiles && j < k_hi;
-        const uint32_t dst = smem_u32(ring + (tile & 3) * 8 + lane);
+        const uint32_t dst = smem_u32(ring + (tile & (kStRingTiles - 1)) * 4 + lane);
         const int32_t* src = ids_row + (in ? j : 0);
         asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(in ? 4 : 0) : "memory");
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    auto ids_wait_all_but_one = [&]() {
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-      __syncwarp();
-    };
     // Mode 2 keeps the pre-pass entry as it is (bit 31 = row of the second cache, low bits = row + 1, 0 = none);
     // the other modes turn it into the row, -1 = none.
-    auto row_of = [&](int tile, int pass) -> long long {
-      const int v = ring[(tile & 3) * 8 + pass * 4 + (lane >> 3)];
+    auto row_of = [&](int tile) -> long long {
+      const int v = ring[(tile & (kStRingTiles - 1)) * 4 + (lane >> 3)];
       if constexpr (kCompress) return static_cast<long long>(v);
       else return static_cast<long long>(v) - 1;
     };
@@ -660,9 +729,7 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
       } else if (gpart == 5) {
         a = scale_b + row * p.scale_stride;
       }
-#ifndef DSV32_SFA_NO_PREFETCH
       if (a != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-#endif
     };
     // Register layout of a row: nope[0..1] / sc.x,.y = this CTA's own value dims (128-dim groups 2*half, 2*half+1),
     // nope[2..3] / sc.z,.w = the other half's.  The runtime half only enters the addresses.
@@ -703,17 +770,16 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         }
       }
     };
-    // one 16-dim group (two 16-byte units of bf16) of key row r, 128-dim group q, into its swizzled place
-    auto store_units = [&](unsigned char* stage, int r, int q, const uint4& lo, const uint4& hi) {
-      const int chunk = 2 * q + (gpart >> 2);  // 64-dim chunk 0..7
-      const int u0 = (gpart & 3) * 2;          // first of two 16-byte units inside the 128-byte line
-      unsigned char* line = stage + chunk * kStChunkBytes + r * 128;
-      *reinterpret_cast<uint4*>(line + ((u0 ^ (r & 7)) << 4)) = lo;
-      *reinterpret_cast<uint4*>(line + (((u0 + 1) ^ (r & 7)) << 4)) = hi;
-    };
-    // group k of the row held in pf: k = 0, 1 -> this CTA's own value dims, 2, 3 -> the other half's
-    auto store_group = [&](unsigned char* stage, int r, int q, int k, const StPrefetch& pf) {
-      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+    // This thread's two 16-byte units of a 128-byte line of its key row, 128-byte swizzle; the row is the same
+    // in every tile, so the offsets inside a stage are fixed.
+    const int u0 = (gpart & 3) * 2;
+    const uint32_t off_lo = static_cast<uint32_t>(gkey * 128 + ((u0 ^ (gkey & 7)) << 4));
+    const uint32_t off_hi = static_cast<uint32_t>(gkey * 128 + (((u0 + 1) ^ (gkey & 7)) << 4));
+    const uint32_t off_rope = static_cast<uint32_t>(8 * kStChunkBytes + gkey * 128 + ((gpart ^ (gkey & 7)) << 4));
+    // group k of the row held in pf (k = 0, 1 -> this CTA's own value dims, 2, 3 -> the other half's) as bf16
+    auto make_group = [&](int k, const StPrefetch& pf, uint4& lo, uint4& hi) {
+      lo = make_uint4(0, 0, 0, 0);
+      hi = lo;
       if constexpr (kBf16) {
         if (pf.valid) {
           const int4 a = pf.nope[2 * k], b = pf.nope[2 * k + 1];
@@ -724,66 +790,79 @@ __global__ void __launch_bounds__(kStThreads, 1) sfa_tc_kernel(const __grid_cons
         const float sc = k == 0 ? pf.sc.x : k == 1 ? pf.sc.y : k == 2 ? pf.sc.z : pf.sc.w;
         if (pf.valid) st_dequant16(pf.nope[k], sc, lo, hi);
       }
-      store_units(stage, r, q, lo, hi);
     };
-    // The chunks that only S reads (the other half's value dims and the rope dims) ...
-    auto commit_other = [&](int tile, int pass, const StPrefetch& pf) {
+    // ... into the two 16-byte units this thread owns of 128-dim group q
+    auto store_group = [&](unsigned char* stage, int q, const uint4& lo, const uint4& hi) {
+      unsigned char* chunk = stage + (2 * q + (gpart >> 2)) * kStChunkBytes;  // 64-dim chunk 0..7
+      *reinterpret_cast<uint4*>(chunk + off_lo) = lo;
+      *reinterpret_cast<uint4*>(chunk + off_hi) = hi;
+    };
+    // The chunks that only S reads (the other half's value dims and the rope dims)
+    auto commit_other = [&](int tile, const StPrefetch& pf) {
       unsigned char* stage = k_s + (tile & 1) * kStStageBytes;
-      const int r = pass * 32 + gkey;  // row (key) inside the tile
-      store_group(stage, r, q_oth, 2, pf);
-      store_group(stage, r, q_oth + 1, 3, pf);
+      uint4 lo, hi;
+      make_group(2, pf, lo, hi);
+      store_group(stage, q_oth, lo, hi);
+      make_group(3, pf, lo, hi);
+      store_group(stage, q_oth + 1, lo, hi);
       if constexpr (!kCompress) {
-        unsigned char* line = stage + 8 * kStChunkBytes + r * 128;
         const int4 v = pf.valid ? pf.rope : make_int4(0, 0, 0, 0);
-        *reinterpret_cast<int4*>(line + ((gpart ^ (r & 7)) << 4)) = v;
+        *reinterpret_cast<int4*>(stage + off_rope) = v;
       }
     };
-    // ... and the chunks that PV reads as V (this CTA's own value dims), plus the validity flag
-    auto commit_own = [&](int tile, int pass, const StPrefetch& pf) {
-      const int s = tile & 1;
-      unsigned char* stage = k_s + s * kStStageBytes;
-      const int r = pass * 32 + gkey;
-      store_group(stage, r, q_own, 0, pf);
-      store_group(stage, r, q_own + 1, 1, pf);
-      if (gpart == 0) {  // membership bits for the softmax; the tile's ids are still in the ring (mode 2 keeps them raw)
-        if constexpr (kCompress) valid_s[s * kStTile + r] = (static_cast<int>(row_of(tile, pass)) >> 29) & 3;
-        else valid_s[s * kStTile + r] = pf.valid ? 1 : 0;
-      }
-    };
-
-    StPrefetch pf0, pf1;
-    fetch_ids(0);
-    fetch_ids(1);
-    fetch_ids(2);
-    ids_wait_all_but_one();  // tiles 0 and 1
-    issue_loads(row_of(0, 0), pf0);
-    issue_loads(row_of(0, 1), pf1);
-    l2_prefetch(row_of(1, 0));
-    l2_prefetch(row_of(1, 1));
-    for (int i = 0; i < ntiles; ++i) {
+    // One tile: refill its stage from `pf`, then start the loads of the tile kDepth ahead into the same registers.
+    auto do_tile = [&](int i, StPrefetch& pf) -> bool {
       const int s = i & 1;
       // Once S of tile i-2 has completed, every chunk of the stage except this CTA's own value chunks is free
       // (both waits pass at once for i < 2): that part of the refill runs under the softmax and PV of tile i-2.
       const uint32_t prev = ((i >> 1) & 1) ^ 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], prev, p.status, 30))) break;
-      commit_other(i, 0, pf0);
-      commit_other(i, 1, pf1);
-      // the own value chunks (and the validity flags the softmax reads) are free once PV of tile i-2 has completed
-      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], prev, p.status, 31))) break;
-      commit_own(i, 0, pf0);
-      commit_own(i, 1, pf1);
+      if (!__all_sync(0xffffffffu, mbar_wait(&sfull_bar[s], prev, p.status, 30))) return false;
+      commit_other(i, pf);
+      // The chunks that PV reads as V (this CTA's own value dims) are free once PV of tile i-2 has completed.  That
+      // wait is on the critical path (PV(i-2) -> refill -> S(i)), so the rows are dequantised before it and only
+      // the stores (and the validity flags the softmax reads) come after it.
+      uint4 own_lo[2], own_hi[2];
+      make_group(0, pf, own_lo[0], own_hi[0]);
+      make_group(1, pf, own_lo[1], own_hi[1]);
+      if (!__all_sync(0xffffffffu, mbar_wait(&pvdone_bar[s], prev, p.status, 31))) return false;
+      {
+        unsigned char* stage = k_s + s * kStStageBytes;
+        store_group(stage, q_own, own_lo[0], own_hi[0]);
+        store_group(stage, q_own + 1, own_lo[1], own_hi[1]);
+        if (gpart == 0) {  // membership bits for the softmax; the tile's ids are still in the ring (mode 2 keeps them raw)
+          if constexpr (kCompress) valid_s[s * kStTile + gkey] = (static_cast<int>(row_of(i)) >> 29) & 3;
+          else valid_s[s * kStTile + gkey] = pf.valid ? 1 : 0;
+        }
+      }
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
       __syncwarp();
-      if (pwarp_lane0) mbar_arrive(&full_bar[s]);
-      if (i + 1 < ntiles) {
-        fetch_ids(i + 3);
-        ids_wait_all_but_one();                   // ids of tile i+2 have landed
-        issue_loads(row_of(i + 1, 0), pf0);       // tile i+1
-        issue_loads(row_of(i + 1, 1), pf1);
-        l2_prefetch(row_of(i + 2, 0));            // tile i+2 (its slot holds zeros past the last tile)
-        l2_prefetch(row_of(i + 2, 1));
-      }
+      if (lane == 0) mbar_arrive(&full_bar[s]);
+      // The loads of the tile kDepth ahead go out after the hand-over: issued before the wait above they hold the
+      // warp at the load/store unit (its miss queue is the scarce resource) and the hand-over comes later (measured).
+      fetch_ids(i + 6);
+      asm volatile("cp.async.wait_group 2;" ::: "memory");   // ids up to tile i + 4 have landed
+      __syncwarp();
+      if (i + kDepth < ntiles) issue_loads(row_of(i + kDepth), pf);
+      if (i + 4 < ntiles) l2_prefetch(row_of(i + 4));
+      return true;
+    };
+
+    StPrefetch pfA, pfB;
+    for (int tl = 0; tl < 6; ++tl) fetch_ids(tl);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    issue_loads(row_of(0), pfA);
+    if constexpr (kDepth == 2) {
+      if (1 < ntiles) issue_loads(row_of(1), pfB);
+      else pfB.valid = false;
     }
+    for (int tl = kDepth; tl < 4; ++tl)
+      if (tl < ntiles) l2_prefetch(row_of(tl));
+    for (int i = 0; i < ntiles; i += 2) {
+      if (!do_tile(i, pfA)) break;
+      if (i + 1 < ntiles && !do_tile(i + 1, kDepth == 2 ? pfB : pfA)) break;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");   // no row-id copy may still be in flight at exit
   }
 
   // ---- teardown ------------------------------------------------------------------------------------------
