@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define DSV32_ABI_VERSION 1
+#define DSV32_ABI_VERSION 2
 
 /* host-side return codes */
 #define DSV32_OK 0
@@ -287,41 +287,61 @@ int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* args, void* cuda_stream);
 size_t dsv32_prolog_v4_workspace_bytes(int32_t t, int32_t h);
 
 /* ---------------------------------------------------------------------------------------
- * Fused element-wise stages of the MLA prolog (quant), the MLA half of
- * mla_indexer_prolog_quant_d / _p
- * (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:112-211,486-528; helpers
- * mla_prolog_quant_impl.py:96-361).  The plain projections between the stages are library
- * GEMMs issued by the host layer (pypto_b200/mla_indexer_prolog_quant_impl.py).
- *   stage 0: q_a -> RMSNorm(gamma_cq) -> bf16 -> per-token int8 -> q_norm, q_norm_scale
- *   stage 1: q_b int32 -> * q_norm_scale * w_qb_scale -> bf16; nope -> q_nope_tmp [128][t][128],
- *            rope -> de-interleave + RoPE -> q_rope [t,128,64]
- *   stage 2: kv_a -> RMSNorm(gamma_ckv) -> 4 x 128-dim int8 groups + fp32 scales -> kv_cache /
- *            k_scale_cache at rows cache_index; last 64 dims -> de-interleave + RoPE -> kr_cache
+ * MLA prolog (quant).  Replaces mla_prolog_quant_d / _p
+ * (models/deepseek_v32_exp/mla_prolog_quant_impl.py:848-875 / 751-778) and is the MLA half of
+ * the fused entry below:
+ *   q_a  = bf16(x . w_dq) -> RMSNorm(gamma_cq) -> bf16 -> per-token int8 -> q_norm, q_norm_scale
+ *   q_b  = bf16(int32(q_norm . w_uq_qr) * q_norm_scale * w_qb_scale), per head 128 nope + 64 rope dims
+ *   query_nope = bf16(q_b nope . w_uk[head]);  query_rope = de-interleave + rotate-half RoPE of q_b rope
+ *   kv_a = bf16(x . w_dkv_kr): first 512 -> RMSNorm(gamma_ckv) -> four 128-dim int8 groups + fp32
+ *          scales -> kv_cache / k_scale_cache at rows cache_index; last 64 -> RoPE -> kr_cache
+ * All four projections run in this library's tensor-core kernels; weights are plain row-major
+ * [K, N] (the reference passes NZ-formatted views of the same logical matrices).  Caches are
+ * updated in place; no other row is touched.  One call enqueues everything on cuda_stream.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
-  const void* q_a;                /* stage 0: bf16 [t, 1536]                         */
-  const void* gamma_cq;           /* bf16 [1536]                                     */
-  int8_t* q_norm;                 /* stage 0 out: int8 [t, 1536]                     */
-  float* q_norm_scale;            /* stage 0 out / stage 1 in: fp32 [t]              */
-  const int32_t* q_b;             /* stage 1: int32 [t, q_b_ld], first 24576 columns */
-  const float* w_qb_scale;        /* fp32 [24576]                                    */
-  void* q_nope_tmp;               /* stage 1 out: bf16 [128, t, 128]                 */
-  void* q_rope;                   /* stage 1 out: bf16 [t, 128, 64]                  */
-  const void* kv_a;               /* stage 2: bf16 [t, 576]                          */
-  const void* gamma_ckv;          /* bf16 [512]                                      */
-  const void* cos;                /* bf16 [t, 64]                                    */
-  const void* sin;                /* bf16 [t, 64]                                    */
-  const int64_t* cache_index;     /* int64 [t]                                       */
-  int8_t* kv_cache;               /* in/out int8 [cache_rows, 512]                   */
-  void* kr_cache;                 /* in/out bf16 [cache_rows, 64]                    */
-  float* k_scale_cache;           /* in/out fp32 [cache_rows, 4]                     */
+  const void* x;                  /* bf16 [t, 7168]                                   */
+  const void* w_dq;               /* bf16 [7168, 1536]                                */
+  const int8_t* w_uq_qr;          /* int8 [1536, 24576]                               */
+  const float* w_qb_scale;        /* fp32 [24576]                                     */
+  const void* w_uk;               /* bf16 [128, 128, 512]                             */
+  const void* w_dkv_kr;           /* bf16 [7168, 576]                                 */
+  const void* gamma_cq;           /* bf16 [1536]                                      */
+  const void* gamma_ckv;          /* bf16 [512]                                       */
+  const void* cos;                /* bf16 [t, 64]                                     */
+  const void* sin;                /* bf16 [t, 64]                                     */
+  const int64_t* cache_index;     /* int64 [t]                                        */
+  int8_t* kv_cache;               /* in/out int8 [cache_rows, 512]                    */
+  void* kr_cache;                 /* in/out bf16 [cache_rows, 64]                     */
+  float* k_scale_cache;           /* in/out fp32 [cache_rows, 4]                      */
+  int8_t* q_norm;                 /* out int8 [t, 1536]                               */
+  float* q_norm_scale;            /* out fp32 [t]                                     */
+  void* query_nope;               /* out bf16 [t, 128, 512]                           */
+  void* query_rope;               /* out bf16 [t, 128, 64]                            */
+  void* workspace;                /* >= dsv32_mla_prolog_workspace_bytes(t), 256-byte aligned */
+  size_t workspace_bytes;
   uint32_t* status;
   int64_t cache_rows;
-  int32_t t, q_b_ld;
+  int32_t t;
   float eps_cq, eps_ckv;
-} Dsv32MlaStageArgs;
+} Dsv32MlaPrologArgs;
 
-int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* args, int32_t stage, void* cuda_stream);
+int dsv32_mla_prolog(const Dsv32MlaPrologArgs* args, void* cuda_stream);
+size_t dsv32_mla_prolog_workspace_bytes(int32_t t);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused MLA prolog + indexer prolog (quant).  Replaces mla_indexer_prolog_quant_d / _p
+ * (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:486-528 / 327-369): the MLA half
+ * above, whose int8 q_norm / q_norm_scale feed the indexer half (dsv32_indexer_prolog) on the
+ * device, as in the reference (:112-211, 213-317).  `indexer.x`, `indexer.q_norm` and
+ * `indexer.q_norm_scale` must be the pointers of the MLA half.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  Dsv32MlaPrologArgs mla;
+  Dsv32PrologArgs indexer;
+} Dsv32FusedPrologArgs;
+
+int dsv32_mla_indexer_prolog(const Dsv32FusedPrologArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused element-wise stages of the DeepSeek-V4 MLA prolog (quant), between its three

@@ -112,14 +112,19 @@ class PrologArgs(C.Structure):
     ]
 
 
-class MlaStageArgs(C.Structure):
+class MlaPrologArgs(C.Structure):
     _fields_ = [
-        ("q_a", c_void_p), ("gamma_cq", c_void_p), ("q_norm", c_void_p), ("q_norm_scale", c_void_p), ("q_b", c_void_p),
-        ("w_qb_scale", c_void_p), ("q_nope_tmp", c_void_p), ("q_rope", c_void_p), ("kv_a", c_void_p),
-        ("gamma_ckv", c_void_p), ("cos", c_void_p), ("sin", c_void_p), ("cache_index", c_void_p), ("kv_cache", c_void_p),
-        ("kr_cache", c_void_p), ("k_scale_cache", c_void_p), ("status", c_void_p), ("cache_rows", c_i64), ("t", c_i32),
-        ("q_b_ld", c_i32), ("eps_cq", c_float), ("eps_ckv", c_float),
+        ("x", c_void_p), ("w_dq", c_void_p), ("w_uq_qr", c_void_p), ("w_qb_scale", c_void_p), ("w_uk", c_void_p),
+        ("w_dkv_kr", c_void_p), ("gamma_cq", c_void_p), ("gamma_ckv", c_void_p), ("cos", c_void_p), ("sin", c_void_p),
+        ("cache_index", c_void_p), ("kv_cache", c_void_p), ("kr_cache", c_void_p), ("k_scale_cache", c_void_p),
+        ("q_norm", c_void_p), ("q_norm_scale", c_void_p), ("query_nope", c_void_p), ("query_rope", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("status", c_void_p), ("cache_rows", c_i64),
+        ("t", c_i32), ("eps_cq", c_float), ("eps_ckv", c_float),
     ]
+
+
+class FusedPrologArgs(C.Structure):
+    _fields_ = [("mla", MlaPrologArgs), ("indexer", PrologArgs)]
 
 
 # every symbol include/dsv32_b200.h declares: name -> (restype, argtypes)
@@ -145,10 +150,12 @@ EXPORTS = {
     "dsv32_hc_pre_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_indexer_prolog": (c_i32, [C.POINTER(PrologArgs), c_void_p]),
-    "dsv32_mla_prolog_stage": (c_i32, [C.POINTER(MlaStageArgs), c_i32, c_void_p]),
+    "dsv32_mla_prolog": (c_i32, [C.POINTER(MlaPrologArgs), c_void_p]),
+    "dsv32_mla_prolog_workspace_bytes": (c_size_t, [c_i32]),
+    "dsv32_mla_indexer_prolog": (c_i32, [C.POINTER(FusedPrologArgs), c_void_p]),
 }
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 _lib = None
 
 

@@ -438,31 +438,33 @@ int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {
   return launch_prolog_tc(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
-// ---- MLA prolog stages ----------------------------------------------------------------------------------
-int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* a, int32_t stage, void* cuda_stream) {
-  REQUIRE(a != nullptr, "mla: args is NULL");
-  REQUIRE(stage >= 0 && stage <= 2, "mla: stage=%d must be 0, 1 or 2", stage);
-  REQUIRE(a->t >= 0, "mla: bad t=%d", a->t);
-  if (a->t == 0) return DSV32_OK;
-  if (stage == 0) REQUIRE(a->q_a && a->gamma_cq && a->q_norm && a->q_norm_scale, "mla stage 0: NULL tensor pointer");
-  if (stage == 1)
-    REQUIRE(a->q_b && a->q_norm_scale && a->w_qb_scale && a->q_nope_tmp && a->q_rope && a->cos && a->sin &&
-                a->q_b_ld >= 24576,
-            "mla stage 1: NULL tensor pointer or q_b_ld=%d < 24576", a->q_b_ld);
-  if (stage == 2)
-    REQUIRE(a->kv_a && a->gamma_ckv && a->cos && a->sin && a->cache_index && a->kv_cache && a->kr_cache &&
-                a->k_scale_cache && a->cache_rows >= 1,
-            "mla stage 2: NULL tensor pointer or empty cache");
-  MlaStageParams p{};
-  p.q_a = static_cast<const __nv_bfloat16*>(a->q_a);
-  p.gamma_cq = static_cast<const __nv_bfloat16*>(a->gamma_cq);
-  p.q_norm = a->q_norm;
-  p.q_norm_scale = a->q_norm_scale;
-  p.q_b = a->q_b;
+// ---- MLA prolog and the fused MLA + indexer prolog ---------------------------------------------------------------
+size_t dsv32_mla_prolog_workspace_bytes(int32_t t) { return mla_prolog_workspace_bytes(t); }
+
+static int mla_fill(const Dsv32MlaPrologArgs* a, MlaParams& p) {
+  REQUIRE(a->x && a->w_dq && a->w_uq_qr && a->w_qb_scale && a->w_uk && a->w_dkv_kr && a->gamma_cq && a->gamma_ckv &&
+              a->cos && a->sin && a->cache_index && a->kv_cache && a->kr_cache && a->k_scale_cache && a->q_norm &&
+              a->q_norm_scale && a->query_nope && a->query_rope,
+          "mla prolog: NULL tensor pointer");
+  REQUIRE(a->cache_rows >= 1, "mla prolog: cache_rows=%lld must be >= 1", static_cast<long long>(a->cache_rows));
+  REQUIRE(reinterpret_cast<uintptr_t>(a->x) % 16 == 0 && reinterpret_cast<uintptr_t>(a->w_dq) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->w_uq_qr) % 16 == 0 && reinterpret_cast<uintptr_t>(a->w_uk) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->w_dkv_kr) % 16 == 0 && reinterpret_cast<uintptr_t>(a->q_norm) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->query_nope) % 16 == 0 && reinterpret_cast<uintptr_t>(a->query_rope) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->cos) % 4 == 0 && reinterpret_cast<uintptr_t>(a->sin) % 4 == 0,
+          "mla prolog: x / weights / q_norm / query outputs must be 16-byte aligned, cos / sin 4-byte aligned");
+  const size_t need = mla_prolog_workspace_bytes(a->t);
+  if (a->workspace == nullptr || a->workspace_bytes < need || reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) {
+    set_error("mla prolog: workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.w_dq = static_cast<const __nv_bfloat16*>(a->w_dq);
+  p.w_uq_qr = a->w_uq_qr;
   p.w_qb_scale = a->w_qb_scale;
-  p.q_nope_tmp = static_cast<__nv_bfloat16*>(a->q_nope_tmp);
-  p.q_rope = static_cast<__nv_bfloat16*>(a->q_rope);
-  p.kv_a = static_cast<const __nv_bfloat16*>(a->kv_a);
+  p.w_uk = static_cast<const __nv_bfloat16*>(a->w_uk);
+  p.w_dkv_kr = static_cast<const __nv_bfloat16*>(a->w_dkv_kr);
+  p.gamma_cq = static_cast<const __nv_bfloat16*>(a->gamma_cq);
   p.gamma_ckv = static_cast<const __nv_bfloat16*>(a->gamma_ckv);
   p.cos = static_cast<const __nv_bfloat16*>(a->cos);
   p.sin = static_cast<const __nv_bfloat16*>(a->sin);
@@ -470,13 +472,39 @@ int dsv32_mla_prolog_stage(const Dsv32MlaStageArgs* a, int32_t stage, void* cuda
   p.kv_cache = a->kv_cache;
   p.kr_cache = static_cast<__nv_bfloat16*>(a->kr_cache);
   p.k_scale_cache = a->k_scale_cache;
+  p.q_norm = a->q_norm;
+  p.q_norm_scale = a->q_norm_scale;
+  p.q_nope = static_cast<__nv_bfloat16*>(a->query_nope);
+  p.q_rope = static_cast<__nv_bfloat16*>(a->query_rope);
+  p.workspace = a->workspace;
   p.status = a->status;
   p.cache_rows = a->cache_rows;
   p.t = a->t;
-  p.q_b_ld = a->q_b_ld;
   p.eps_cq = a->eps_cq;
   p.eps_ckv = a->eps_ckv;
-  return launch_mla_stage(p, stage, static_cast<cudaStream_t>(cuda_stream));
+  return DSV32_OK;
+}
+
+int dsv32_mla_prolog(const Dsv32MlaPrologArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "mla prolog: args is NULL");
+  REQUIRE(a->t >= 0, "mla prolog: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  MlaParams p{};
+  const int rc = mla_fill(a, p);
+  if (rc != DSV32_OK) return rc;
+  return launch_mla_prolog(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int dsv32_mla_indexer_prolog(const Dsv32FusedPrologArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "mla indexer prolog: args is NULL");
+  REQUIRE(a->mla.t == a->indexer.t, "mla indexer prolog: token counts differ (%d / %d)", a->mla.t, a->indexer.t);
+  // the indexer half reads the int8 q_norm / q_norm_scale the MLA half writes, and the same x
+  REQUIRE(a->indexer.q_norm == a->mla.q_norm && a->indexer.q_norm_scale == a->mla.q_norm_scale &&
+              a->indexer.x == a->mla.x,
+          "mla indexer prolog: the indexer half must take x, q_norm and q_norm_scale of the MLA half");
+  int rc = dsv32_mla_prolog(&a->mla, cuda_stream);
+  if (rc != DSV32_OK) return rc;
+  return dsv32_indexer_prolog(&a->indexer, cuda_stream);
 }
 
 int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* a, int32_t stage, void* cuda_stream) {

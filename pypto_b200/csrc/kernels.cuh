@@ -108,16 +108,16 @@ size_t prolog_v4_workspace_bytes(int t, int h);
 size_t prolog_workspace_bytes(int t);
 
 
+// MLA prolog (quant): x . [w_dq | w_dkv_kr] has 1536 + 576 = 2112 output columns and its reduction over the hidden
+// size is split over kMlaXSplits CTAs, whose fp32 partial sums the two finish kernels add in a fixed order.
+constexpr int kMlaXSplits = 4;
+constexpr int kMlaXCols = 2112;
+
 struct MlaStageParams {
-  const __nv_bfloat16* q_a;
+  const float* partial;        // [kMlaXSplits][t][kMlaXCols] partial sums of x . [w_dq | w_dkv_kr]
   const __nv_bfloat16* gamma_cq;
   int8_t* q_norm;
   float* q_norm_scale;
-  const int32_t* q_b;
-  const float* w_qb_scale;
-  __nv_bfloat16* q_nope_tmp;
-  __nv_bfloat16* q_rope;
-  const __nv_bfloat16* kv_a;
   const __nv_bfloat16* gamma_ckv;
   const __nv_bfloat16* cos;
   const __nv_bfloat16* sin;
@@ -127,10 +127,38 @@ struct MlaStageParams {
   float* k_scale_cache;
   uint32_t* status;
   long long cache_rows;
-  int t, q_b_ld;
+  int t;
   float eps_cq, eps_ckv;
 };
 int launch_mla_stage(const MlaStageParams& p, int stage, cudaStream_t stream);
+
+struct MlaParams {
+  const __nv_bfloat16* x;          // [t, 7168]
+  const __nv_bfloat16* w_dq;       // [7168, 1536]
+  const int8_t* w_uq_qr;           // [1536, 128 * 192]
+  const float* w_qb_scale;         // [128 * 192]
+  const __nv_bfloat16* w_uk;       // [128, 128, 512]
+  const __nv_bfloat16* w_dkv_kr;   // [7168, 576]
+  const __nv_bfloat16* gamma_cq;
+  const __nv_bfloat16* gamma_ckv;
+  const __nv_bfloat16* cos;        // [t, 64]
+  const __nv_bfloat16* sin;
+  const long long* cache_index;    // [t]
+  int8_t* kv_cache;                // [cache_rows, 512]
+  __nv_bfloat16* kr_cache;         // [cache_rows, 64]
+  float* k_scale_cache;            // [cache_rows, 4]
+  int8_t* q_norm;                  // out [t, 1536]
+  float* q_norm_scale;             // out [t]
+  __nv_bfloat16* q_nope;           // out [t, 128, 512]
+  __nv_bfloat16* q_rope;           // out [t, 128, 64]
+  void* workspace;                 // mla_prolog_workspace_bytes(t), 256-byte aligned
+  uint32_t* status;
+  long long cache_rows;
+  int t;
+  float eps_cq, eps_ckv;
+};
+int launch_mla_prolog(const MlaParams& p, cudaStream_t stream);
+size_t mla_prolog_workspace_bytes(int t);
 
 struct MlaV4StageParams {
   // quant != 0: the quantised operator (fp32 / int32 GEMM results, int8 qr); 0: the bf16 operator (bf16 throughout)

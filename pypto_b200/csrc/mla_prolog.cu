@@ -1,17 +1,25 @@
-// Fused element-wise stages of the MLA prolog (quant) -- the MLA half of mla_indexer_prolog_quant
+// Element-wise stages of the MLA prolog (quant) -- the MLA half of mla_indexer_prolog_quant
 // (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:112-211; helpers mla_prolog_quant_impl.py:96-361;
-// golden deepseekv32_mla_indexer_prolog_quant.py:395-539).  The four plain projections between these stages
-// (x.w_dq, int8 q_norm.w_uq_qr, per-head q_nope.w_uk, x.w_dkv_kr) are library GEMMs issued by the host layer.
-//   stage 0: q_a (bf16 [t,1536]) -> RMSNorm(gamma_cq) -> bf16 -> per-token int8 quant -> q_norm, q_norm_scale
-//   stage 1: q_b (int32 [t, 128*192]) -> * q_norm_scale * w_qb_scale -> bf16; nope part -> [head][t][128] for the
-//            w_uk projection, rope part -> de-interleave + rotate-half RoPE -> q_rope
-//   stage 2: kv_a (bf16 [t,576]) -> RMSNorm(gamma_ckv) of the first 512 -> four 128-dim int8 groups + fp32 scales
-//            scattered into the latent cache; last 64 -> de-interleave + RoPE -> rope cache
+// golden deepseekv32_mla_indexer_prolog_quant.py:395-539) -- that follow the split-reduction projection
+// x . [w_dq | w_dkv_kr] of mla_prolog_tc.cu: both kernels first add its fp32 partial sums in a fixed order and round
+// to bf16 (the reference's q_a / kv_a).
+//   stage 0: q_a (columns 0..1535) -> RMSNorm(gamma_cq) -> bf16 -> per-token int8 quant -> q_norm, q_norm_scale
+//   stage 2: kv_a (columns 1536..2111) -> RMSNorm(gamma_ckv) of the first 512 -> four 128-dim int8 groups + fp32
+//            scales scattered into the latent cache; last 64 -> de-interleave + RoPE -> rope cache
+// (the dequantisation and rotary embedding of the q_b projection are the epilogue of that projection's kernel)
 #include "kernels.cuh"
 
 namespace dsv32 {
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// q_a / kv_a element: the projection's partial sums added in split order, rounded to bf16
+__device__ __forceinline__ float partial_sum_bf16(const MlaStageParams& p, int tok, int col) {
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMlaXSplits; ++k) s += p.partial[(static_cast<size_t>(k) * p.t + tok) * kMlaXCols + col];
+  return bf16r(s);
+}
 
 template <int THREADS>
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -51,11 +59,10 @@ __device__ __forceinline__ float rope_deinterleaved(const float* x, int j, const
 __global__ void __launch_bounds__(256) mla_rmsnorm_quant_kernel(MlaStageParams p) {
   __shared__ float red[8];
   const int tok = blockIdx.x, tid = threadIdx.x;
-  const __nv_bfloat16* row = p.q_a + static_cast<size_t>(tok) * 1536;
   float x[6], ss = 0.f;
 #pragma unroll
   for (int i = 0; i < 6; ++i) {
-    x[i] = __bfloat162float(row[tid + i * 256]);
+    x[i] = partial_sum_bf16(p, tok, tid + i * 256);
     ss += __fmul_rn(__fmul_rn(x[i], x[i]), 1.0f / 1536.0f);
   }
   const float rms = sqrtf(block_sum<256>(ss, red) + p.eps_cq);
@@ -73,35 +80,14 @@ __global__ void __launch_bounds__(256) mla_rmsnorm_quant_kernel(MlaStageParams p
   if (tid == 0) p.q_norm_scale[tok] = __fdiv_rn(1.0f, sq);
 }
 
-// ---- stage 1: one CTA per (token, head), 192 threads -----------------------------------------------------------
-__global__ void __launch_bounds__(192) mla_q_finish_kernel(MlaStageParams p) {
-  __shared__ float rope_s[64];
-  const int tok = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-  const int col = head * 192 + d;
-  const float v = bf16r(__fmul_rn(__fmul_rn(__int2float_rn(p.q_b[static_cast<size_t>(tok) * p.q_b_ld + col]),
-                                            p.q_norm_scale[tok]), p.w_qb_scale[col]));
-  if (d < 128) {
-    p.q_nope_tmp[(static_cast<size_t>(head) * p.t + tok) * 128 + d] = __float2bfloat16_rn(v);
-  } else {
-    rope_s[d - 128] = v;
-  }
-  __syncthreads();
-  if (d >= 128) {
-    const int j = d - 128;
-    p.q_rope[(static_cast<size_t>(tok) * 128 + head) * 64 + j] = __float2bfloat16_rn(
-        rope_deinterleaved(rope_s, j, p.cos + static_cast<size_t>(tok) * 64, p.sin + static_cast<size_t>(tok) * 64));
-  }
-}
-
 // ---- stage 2: one CTA per token, 512 threads -------------------------------------------------------------------
 __global__ void __launch_bounds__(512) mla_kv_finish_kernel(MlaStageParams p) {
   __shared__ float red[16];
   __shared__ float gmax[4];
   __shared__ float rope_s[64];
   const int tok = blockIdx.x, tid = threadIdx.x;
-  const __nv_bfloat16* row = p.kv_a + static_cast<size_t>(tok) * 576;
-  const float x = __bfloat162float(row[tid]);
-  if (tid < 64) rope_s[tid] = __bfloat162float(row[512 + tid]);
+  const float x = partial_sum_bf16(p, tok, 1536 + tid);
+  if (tid < 64) rope_s[tid] = partial_sum_bf16(p, tok, 1536 + 512 + tid);
   const float rms = sqrtf(block_sum<512>(__fmul_rn(__fmul_rn(x, x), 1.0f / 512.0f), red) + p.eps_ckv);
   const float y = bf16r(__fmul_rn(__fdiv_rn(x, rms), __bfloat162float(p.gamma_ckv[tid])));
   // per 128-dim group (4 warps) maximum
@@ -129,8 +115,6 @@ int launch_mla_stage(const MlaStageParams& p, int stage, cudaStream_t stream) {
   if (p.t <= 0) return DSV32_OK;
   if (stage == 0) {
     mla_rmsnorm_quant_kernel<<<p.t, 256, 0, stream>>>(p);
-  } else if (stage == 1) {
-    mla_q_finish_kernel<<<dim3(p.t, 128), 192, 0, stream>>>(p);
   } else {
     mla_kv_finish_kernel<<<p.t, 512, 0, stream>>>(p);
   }

@@ -1,0 +1,380 @@
+// The four projections of the MLA prolog (quant) on tcgen05 tensor cores -- the MLA half of
+// mla_indexer_prolog_quant (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:112-211; projections
+// mla_prolog_quant_impl.py:452-459 x.w_dq, :480 q_norm.w_uq_qr, :499-509 x.w_dkv_kr, :667 q_nope.w_uk; golden
+// deepseekv32_mla_indexer_prolog_quant.py:395-539).
+//
+// One kernel template, three instantiations.  A CTA computes D[128 tokens x N] = A[tokens, k range] x B[k range, N]
+// with the activations K-major (row-major [tokens, K]) and the weights MN-major (row-major [K, N], as the caller
+// holds them), both streamed by TMA (128-byte swizzle, never multicast) through a ring of shared-memory stages;
+// the accumulator lives in tensor memory and every epilogue thread owns one token row.
+//   kXproj  bf16  x[t,7168] x [w_dq | w_dkv_kr] (2112 columns in tiles of 64), the reduction split over four CTAs;
+//                 fp32 partial sums go to the workspace (finished by mla_rmsnorm_quant_kernel / mla_kv_finish_kernel)
+//   kQb     int8  q_norm[t,1536] x w_uq_qr[1536, 128 heads x 192] in tiles of 128 columns; the epilogue dequantises
+//                 (x q_norm_scale x w_qb_scale -> bf16), sends the 128 "nope" dims of a head to a compact
+//                 [t,128,128] buffer and the 64 "rope" dims through the de-interleaving rotary embedding to q_rope
+//   kUk     bf16  per head: nope[t,128] x w_uk[head][128,512] (256 columns per CTA) -> q_nope[t,128,512] bf16
+// The weights (85 MB) are read once; the projections are bound by that stream, not by arithmetic.
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace dsv32 {
+
+constexpr int kGemmThreads = 192;   // warp 0: TMA producer, warp 1: MMA issuer + tensor-memory owner, 2..5: epilogue
+constexpr int kMlaH = 7168, kMlaQLora = 1536, kMlaHeads = 128, kMlaNope = 128, kMlaRope = 64, kMlaLora = 512;
+
+enum { kXproj = 0, kQb = 1, kUk = 2 };
+
+struct MlaGemmParams {
+  float* partial;                  // kXproj out: [kMlaXSplits][t][kMlaXCols]
+  const float* q_norm_scale;       // kQb: [t]
+  const float* w_qb_scale;         // kQb: [24576]
+  const __nv_bfloat16* cos;        // kQb: [t, 64]
+  const __nv_bfloat16* sin;
+  __nv_bfloat16* q_nope_in;        // kQb out / kUk in: [t, 128, 128]
+  __nv_bfloat16* q_rope;           // kQb out: [t, 128, 64]
+  __nv_bfloat16* q_nope;           // kUk out: [t, 128, 512]
+  uint32_t* status;
+  int t;
+};
+
+template <int kKind>
+struct GemmShape {
+  static constexpr bool kInt8 = kKind == kQb;
+  static constexpr int kNChunks = kKind == kUk ? 4 : 1;               // 128-byte column chunks of B per stage
+  static constexpr int kN = kNChunks * (kInt8 ? 128 : 64);            // 64 / 128 / 256 columns per CTA
+  static constexpr int kKRows = kInt8 ? 128 : 64;                     // reduction elements per stage (128 B of A)
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBChunk = kKRows * 128;
+  static constexpr int kStageBytes = kABytes + kNChunks * kBChunk;    // 24 / 32 / 48 KB
+  static constexpr int kStages = kKind == kXproj ? 6 : (kKind == kQb ? 3 : 2);
+  static constexpr int kChunksTotal = kKind == kXproj ? kMlaH / 64 : (kKind == kQb ? kMlaQLora / 128 : kMlaNope / 64);
+  static constexpr int kOffWs = kStages * kStageBytes;                // kQb: 128 column scales
+  static constexpr int kOffBars = kOffWs + 512;
+  static constexpr int kOffTmem = kOffBars + (2 * kStages + 1) * 8;
+  static constexpr size_t kSmemBytes = kOffTmem + 16 + 1024;          // slack for manual 1024-byte alignment
+  static constexpr uint32_t kTmemCols = kN < 32 ? 32 : kN;
+  static constexpr int kCtasPerSm = kKind == kXproj ? 1 : 2;
+};
+
+__device__ __forceinline__ float mla_bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <int kKind>
+__global__ void __launch_bounds__(kGemmThreads, GemmShape<kKind>::kCtasPerSm)
+mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map0,
+                   const __grid_constant__ CUtensorMap b_map1, MlaGemmParams p) {
+  using Sh = GemmShape<kKind>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* ws_s = reinterpret_cast<float*>(smem + Sh::kOffWs);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sh::kOffBars);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Sh::kStages;
+  uint64_t* d_bar = bars + 2 * Sh::kStages;
+  uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + Sh::kOffTmem);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile = blockIdx.x;          // kXproj: column tile of 64; kQb: column tile of 128; kUk: head * 2 + half
+  const int split = blockIdx.y;         // kXproj only
+  const int t0 = blockIdx.z * 128;
+  // reduction chunks of this CTA
+  int c_begin = 0, nchunks = Sh::kChunksTotal;
+  if constexpr (kKind == kXproj) {
+    c_begin = split * (Sh::kChunksTotal / kMlaXSplits);
+    nchunks = Sh::kChunksTotal / kMlaXSplits;
+  }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&a_map);
+      tma_prefetch_desc(&b_map0);
+      if constexpr (kKind == kXproj) tma_prefetch_desc(&b_map1);
+      for (int i = 0; i < Sh::kStages; ++i) {
+        mbar_init(&full_bar[i], 1);
+        mbar_init(&empty_bar[i], 1);
+      }
+      mbar_init(d_bar, 1);
+      mbar_fence_init();
+    }
+  } else if (warp == 1) {
+    tmem_alloc(tmem_ptr_s, Sh::kTmemCols);
+    tmem_relinquish();
+  } else if constexpr (kKind == kQb) {
+    ws_s[tid - 64] = p.w_qb_scale[tile * 128 + (tid - 64)];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_s;
+
+  if (warp == 0) {
+    // ---- TMA producer -------------------------------------------------------------------------------------
+    if (lane == 0) {
+      for (int c = 0; c < nchunks; ++c) {
+        const int s = c % Sh::kStages;
+        if (!mbar_wait(&empty_bar[s], ((c / Sh::kStages) & 1) ^ 1, p.status, 60)) break;
+        unsigned char* st = smem + s * Sh::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[s], Sh::kStageBytes);
+        const int k0 = (c_begin + c) * Sh::kKRows;   // first reduction element of the chunk
+        if constexpr (kKind == kXproj) {
+          tma_load_2d(st, &a_map, k0 * 2, t0, &full_bar[s]);
+          if (tile < kMlaQLora / 64) tma_load_2d(st + Sh::kABytes, &b_map0, tile * 128, k0, &full_bar[s]);
+          else tma_load_2d(st + Sh::kABytes, &b_map1, (tile - kMlaQLora / 64) * 128, k0, &full_bar[s]);
+        } else if constexpr (kKind == kQb) {
+          tma_load_2d(st, &a_map, k0, t0, &full_bar[s]);
+          tma_load_2d(st + Sh::kABytes, &b_map0, tile * 128, k0, &full_bar[s]);
+        } else {
+          const int head = tile >> 1, half = tile & 1;
+          tma_load_2d(st, &a_map, head * 256 + k0 * 2, t0, &full_bar[s]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, half * 512 + j * 128, head * kMlaNope + k0,
+                        &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the whole warp runs the loop (uniform operands), lane 0 issues ---------------------------
+    const bool leader = lane == 0;
+    constexpr uint32_t idesc = Sh::kInt8 ? umma_idesc_i8(128, Sh::kN, true) : umma_idesc_bf16(128, Sh::kN, false, true);
+    const uint32_t tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
+    bool ok = true;
+    for (int c = 0; c < nchunks; ++c) {
+      const int s = c % Sh::kStages;
+      ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], (c / Sh::kStages) & 1, p.status, 61));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a_s = smem_u32(smem + s * Sh::kStageBytes), b_s = a_s + Sh::kABytes;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {  // 32 bytes of A's row per instruction: 32 int8 / 16 bf16 reduction elements
+        const uint64_t ad = umma_smem_desc_sw128(a_s + ks * 32, 16, 1024);
+        const uint64_t bd = umma_smem_desc_sw128(b_s + ks * (Sh::kInt8 ? 4096 : 2048), Sh::kBChunk, 1024);
+        const uint32_t acc = (c > 0 || ks > 0) ? 1u : 0u;
+        if constexpr (Sh::kInt8) {
+          asm volatile(
+              "{\n\t.reg .pred pa, pl;\n\tsetp.ne.b32 pa, %4, 0;\n\tsetp.ne.b32 pl, %5, 0;\n\t"
+              "@pl tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, pa;\n\t}" ::"r"(tbase),
+              "l"(ad), "l"(bd), "r"(idesc), "r"(acc), "r"(static_cast<uint32_t>(leader))
+              : "memory");
+        } else {
+          umma_f16_ss_if(leader, tbase, ad, bd, idesc, acc);
+        }
+      }
+      umma_commit_if(leader, &empty_bar[s]);
+    }
+    if (ok) umma_commit_if(leader, d_bar);
+  } else {
+    // ---- epilogue: thread = token row (tensor-memory lane quarter = warp % 4) ------------------------------------
+    const int quarter = warp & 3;
+    const int tok = t0 + quarter * 32 + lane;
+    const bool live = tok < p.t;
+    const int tk = live ? tok : 0;  // clamp for loads
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    if (__all_sync(0xffffffffu, mbar_wait(d_bar, 0, p.status, 62))) {
+      tc_fence_after();
+      if constexpr (kKind == kXproj) {
+        float* prow = p.partial + (static_cast<size_t>(split) * p.t + tk) * kMlaXCols + tile * 64;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(prow + c * 32 + j) =
+                  make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                              __uint_as_float(r[j + 3]));
+          }
+        }
+      } else if constexpr (kKind == kQb) {
+        // 384 columns = two heads: column tile 3j is the nope part of head 2j, tile 3j+1 its rope part followed by
+        // nope dims 0..63 of head 2j+1, tile 3j+2 nope dims 64..127 of head 2j+1 followed by its rope part.
+        const int m = tile % 3, pair = tile / 3;
+        const float qs = p.q_norm_scale[tk];
+        auto dequant32 = [&](int g, float (&v)[32]) {  // columns 32g .. 32g+31 of the tile -> bf16-rounded floats
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + g * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = mla_bf16r(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), qs), ws_s[g * 32 + j]));
+        };
+        auto store_nope32 = [&](int head, int d0, const float (&v)[32]) {  // nope dims d0 .. d0+31 of `head`
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) w[j >> 1] = pack_bf16x2(v[j], v[j + 1]);
+          if (live) {
+            uint4* dst = reinterpret_cast<uint4*>(p.q_nope_in + (static_cast<size_t>(tk) * kMlaHeads + head) * kMlaNope + d0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
+        };
+        // De-interleave (even dims, then odd dims) and rotate-half rotary embedding: out[j] = x[2j] cos[j] - x[2j+1] sin[j]
+        // for j < 32, out[j] = x[2(j-32)+1] cos[j] + x[2(j-32)] sin[j] for j >= 32; products and sum rounded separately.
+        auto rope_store = [&](int head, const float (&xa)[32], const float (&xb)[32]) {  // xa = x[0..31], xb = x[32..63]
+          const uint32_t* cw = reinterpret_cast<const uint32_t*>(p.cos + static_cast<size_t>(tk) * kMlaRope);
+          const uint32_t* sw = reinterpret_cast<const uint32_t*>(p.sin + static_cast<size_t>(tk) * kMlaRope);
+          uint32_t w[32];
+#pragma unroll
+          for (int jp = 0; jp < 16; ++jp) {  // output pairs (2jp, 2jp+1) of the first half and (32+2jp, 33+2jp) of the second
+            const uint32_t c_lo = __ldg(cw + jp), s_lo = __ldg(sw + jp), c_hi = __ldg(cw + 16 + jp), s_hi = __ldg(sw + 16 + jp);
+            float o_lo[2], o_hi[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int j = 2 * jp + e;                  // j < 32; inputs x[2j], x[2j+1]
+              const float xe = (2 * j < 32) ? xa[(2 * j) & 31] : xb[(2 * j) & 31];
+              const float xo = (2 * j + 1 < 32) ? xa[(2 * j + 1) & 31] : xb[(2 * j + 1) & 31];
+              const float cl = __uint_as_float(e ? (c_lo & 0xffff0000u) : (c_lo << 16));
+              const float sl = __uint_as_float(e ? (s_lo & 0xffff0000u) : (s_lo << 16));
+              const float ch = __uint_as_float(e ? (c_hi & 0xffff0000u) : (c_hi << 16));
+              const float sh = __uint_as_float(e ? (s_hi & 0xffff0000u) : (s_hi << 16));
+              o_lo[e] = __fadd_rn(__fmul_rn(xe, cl), __fmul_rn(-xo, sl));
+              o_hi[e] = __fadd_rn(__fmul_rn(xo, ch), __fmul_rn(xe, sh));
+            }
+            w[jp] = pack_bf16x2(o_lo[0], o_lo[1]);
+            w[16 + jp] = pack_bf16x2(o_hi[0], o_hi[1]);
+          }
+          if (live) {
+            uint4* dst = reinterpret_cast<uint4*>(p.q_rope + (static_cast<size_t>(tk) * kMlaHeads + head) * kMlaRope);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
+        };
+        float va[32], vb[32];
+        if (m == 0) {
+#pragma unroll 1
+          for (int g = 0; g < 4; ++g) {
+            dequant32(g, va);
+            store_nope32(2 * pair, g * 32, va);
+          }
+        } else if (m == 1) {
+          dequant32(0, va);
+          dequant32(1, vb);
+          rope_store(2 * pair, va, vb);
+          dequant32(2, va);
+          store_nope32(2 * pair + 1, 0, va);
+          dequant32(3, va);
+          store_nope32(2 * pair + 1, 32, va);
+        } else {
+          dequant32(0, va);
+          store_nope32(2 * pair + 1, 64, va);
+          dequant32(1, va);
+          store_nope32(2 * pair + 1, 96, va);
+          dequant32(2, va);
+          dequant32(3, vb);
+          rope_store(2 * pair + 1, va, vb);
+        }
+      } else {
+        const int head = tile >> 1, half = tile & 1;
+        __nv_bfloat16* orow = p.q_nope + (static_cast<size_t>(tk) * kMlaHeads + head) * kMlaLora + half * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+              *reinterpret_cast<uint4*>(orow + c * 32 + j) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Sh::kTmemCols);
+  }
+}
+
+template <int kKind>
+static int launch_gemm(const CUtensorMap& a_map, const CUtensorMap& b0, const CUtensorMap& b1, const MlaGemmParams& gp,
+                       dim3 grid, cudaStream_t stream, const char* what) {
+  using Sh = GemmShape<kKind>;
+  cudaFuncSetAttribute(mla_gemm_tc_kernel<kKind>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::kSmemBytes);
+  mla_gemm_tc_kernel<kKind><<<grid, kGemmThreads, Sh::kSmemBytes, stream>>>(a_map, b0, b1, gp);
+  count_launch();
+  return check_launch(what);
+}
+
+size_t mla_prolog_workspace_bytes(int t) {
+  if (t <= 0) return 0;
+  const size_t partial = static_cast<size_t>(kMlaXSplits) * t * kMlaXCols * sizeof(float);
+  const size_t nope_in = static_cast<size_t>(t) * kMlaHeads * kMlaNope * sizeof(__nv_bfloat16);
+  return (partial + 255) / 256 * 256 + (nope_in + 255) / 256 * 256;
+}
+
+// The MLA prolog on one stream: x projections -> (RMSNorm + int8 quantisation -> q_b projection with dequantisation
+// and rotary embedding -> w_uk projection) and (RMSNorm + cache quantisation + rotary embedding + cache scatter).
+int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
+  if (p.t <= 0) return DSV32_OK;
+  const int tiles = (p.t + 127) / 128;
+  char* ws = static_cast<char*>(p.workspace);
+  float* partial = reinterpret_cast<float*>(ws);
+  const size_t partial_bytes = (static_cast<size_t>(kMlaXSplits) * p.t * kMlaXCols * sizeof(float) + 255) / 256 * 256;
+  __nv_bfloat16* nope_in = reinterpret_cast<__nv_bfloat16*>(ws + partial_bytes);
+
+  CUtensorMap x_map, wdq_map, wkv_map, qn_map, wqb_map, ni_map, wuk_map;
+  int rc = make_tensor_map_2d_u8(&x_map, p.x, p.t, kMlaH * 2, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wdq_map, p.w_dq, kMlaH, kMlaQLora * 2, 64, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wkv_map, p.w_dkv_kr, kMlaH, (kMlaLora + kMlaRope) * 2, 64, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&qn_map, p.q_norm, p.t, kMlaQLora, 128, 128);
+  if (rc == DSV32_OK)
+    rc = make_tensor_map_2d_u8(&wqb_map, p.w_uq_qr, kMlaQLora, kMlaHeads * (kMlaNope + kMlaRope), 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&ni_map, nope_in, p.t, kMlaHeads * kMlaNope * 2, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wuk_map, p.w_uk, kMlaHeads * kMlaNope, kMlaLora * 2, 64, 128);
+  if (rc != DSV32_OK) return rc;
+
+  MlaGemmParams gp{};
+  gp.partial = partial;
+  gp.q_norm_scale = p.q_norm_scale;
+  gp.w_qb_scale = p.w_qb_scale;
+  gp.cos = p.cos;
+  gp.sin = p.sin;
+  gp.q_nope_in = nope_in;
+  gp.q_rope = p.q_rope;
+  gp.q_nope = p.q_nope;
+  gp.status = p.status;
+  gp.t = p.t;
+
+  rc = launch_gemm<kXproj>(x_map, wdq_map, wkv_map, gp, dim3(kMlaXCols / 64, kMlaXSplits, tiles), stream,
+                           "mla_gemm_tc_kernel (x projections)");
+  if (rc != DSV32_OK) return rc;
+  MlaStageParams sp{};
+  sp.partial = partial;
+  sp.gamma_cq = p.gamma_cq;
+  sp.q_norm = p.q_norm;
+  sp.q_norm_scale = p.q_norm_scale;
+  sp.gamma_ckv = p.gamma_ckv;
+  sp.cos = p.cos;
+  sp.sin = p.sin;
+  sp.cache_index = p.cache_index;
+  sp.kv_cache = p.kv_cache;
+  sp.kr_cache = p.kr_cache;
+  sp.k_scale_cache = p.k_scale_cache;
+  sp.status = p.status;
+  sp.cache_rows = p.cache_rows;
+  sp.t = p.t;
+  sp.eps_cq = p.eps_cq;
+  sp.eps_ckv = p.eps_ckv;
+  rc = launch_mla_stage(sp, 0, stream);
+  if (rc != DSV32_OK) return rc;
+  rc = launch_mla_stage(sp, 2, stream);
+  if (rc != DSV32_OK) return rc;
+  rc = launch_gemm<kQb>(qn_map, wqb_map, wqb_map, gp, dim3(kMlaHeads * (kMlaNope + kMlaRope) / 128, 1, tiles), stream,
+                        "mla_gemm_tc_kernel (q_norm . w_uq_qr)");
+  if (rc != DSV32_OK) return rc;
+  return launch_gemm<kUk>(ni_map, wuk_map, wuk_map, gp, dim3(kMlaHeads * 2, 1, tiles), stream,
+                          "mla_gemm_tc_kernel (q_nope . w_uk)");
+}
+
+}  // namespace dsv32

@@ -423,11 +423,9 @@ static PrologFork* prolog_fork_for_device() {
   std::lock_guard<std::mutex> lock(mu);
   PrologFork& f = forks[dev];
   if (f.side == nullptr) {
-    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
     if (cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming) != cudaSuccess) {
-      (void)st;
       (void)cudaGetLastError();
       f = PrologFork{};
       return nullptr;  // fall back to one stream

@@ -291,7 +291,6 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   // warp (stride 1 inside the thread, the others by shuffle), so only the steps with a stride of 64 or more
   // go through shared memory and a block barrier: 15 of the 66 steps of a 2048-element sort.
   if (npad >= 64) {
-    const int lane = tid & 31;
     const bool active = tid < (npad >> 1);  // whole warps: npad/2 is a multiple of 32
     const int e0 = 2 * tid;
     auto warp_steps = [&](uint64_t& a, uint64_t& b, int size, int first_stride) {

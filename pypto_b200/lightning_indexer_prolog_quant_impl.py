@@ -68,13 +68,11 @@ class IndexerPrologQuantConfigs:
     vec_nbuffer_setting: dict = field(default_factory=dict)
 
 
-def lightning_indexer_prolog_quant(x_in, q_norm_in, q_norm_scale_in, w_qb_in, w_qb_scale_in, wk_in, w_proj_in,
-                                   ln_gamma_k_in, ln_beta_k_in, cos_idx_rope_in, sin_idx_rope_in, hadamard_q_in,
-                                   hadamard_k_in, k_int8_in, k_scale_in, k_cache_index_in, q_int8_out, q_scale_out,
-                                   k_int8_out, k_scale_out, weights_out, configs=None, attrs=None):
-    """lightning_indexer_prolog_quant_impl.py:325-349.  k_int8_out / k_scale_out must alias
-    k_int8_in / k_scale_in (the reference tests pass the same tensors): the cache is updated in place at
-    rows k_cache_index_in and no other row is touched."""
+def prolog_args(x_in, q_norm_in, q_norm_scale_in, w_qb_in, w_qb_scale_in, wk_in, w_proj_in, ln_gamma_k_in,
+                ln_beta_k_in, cos_idx_rope_in, sin_idx_rope_in, hadamard_q_in, hadamard_k_in, k_int8_in, k_scale_in,
+                k_cache_index_in, q_int8_out, q_scale_out, k_int8_out, k_scale_out, weights_out, attrs=None):
+    """Validates the operator's tensors and returns (Dsv32PrologArgs, device, keep-alive list): the argument block
+    of dsv32_indexer_prolog, also embedded in the fused MLA + indexer prolog call."""
     rt.require_cuda()
     bf16 = torch.bfloat16
     rt.check_tensor(x_in, "x", bf16, (None, 7168))
@@ -114,5 +112,21 @@ def lightning_indexer_prolog_quant(x_in, q_norm_in, q_norm_scale_in, w_qb_in, w_
             rt.ptr(sin_idx_rope_in), rt.ptr(hadamard_q_in), rt.ptr(hadamard_k_in), rt.ptr(k_cache_index_in),
             rt.ptr(q_int8_out), rt.ptr(q_scale_out), rt.ptr(k_int8_in), rt.ptr(k_scale_in), rt.ptr(weights_out),
             rt.ptr(ws), int(ws_bytes), rt.ptr(rt.status_word(dev)), rows, t, eps)
-        rt.check(lib.dsv32_indexer_prolog(C.byref(a), rt.stream_ptr(dev)), "lightning_indexer_prolog_quant")
+    return a, dev, [ws]
+
+
+def lightning_indexer_prolog_quant(x_in, q_norm_in, q_norm_scale_in, w_qb_in, w_qb_scale_in, wk_in, w_proj_in,
+                                   ln_gamma_k_in, ln_beta_k_in, cos_idx_rope_in, sin_idx_rope_in, hadamard_q_in,
+                                   hadamard_k_in, k_int8_in, k_scale_in, k_cache_index_in, q_int8_out, q_scale_out,
+                                   k_int8_out, k_scale_out, weights_out, configs=None, attrs=None):
+    """lightning_indexer_prolog_quant_impl.py:325-349.  k_int8_out / k_scale_out must alias
+    k_int8_in / k_scale_in (the reference tests pass the same tensors): the cache is updated in place at
+    rows k_cache_index_in and no other row is touched."""
+    a, dev, keep = prolog_args(x_in, q_norm_in, q_norm_scale_in, w_qb_in, w_qb_scale_in, wk_in, w_proj_in, ln_gamma_k_in,
+                               ln_beta_k_in, cos_idx_rope_in, sin_idx_rope_in, hadamard_q_in, hadamard_k_in, k_int8_in,
+                               k_scale_in, k_cache_index_in, q_int8_out, q_scale_out, k_int8_out, k_scale_out,
+                               weights_out, attrs)
+    with torch.cuda.device(dev):
+        rt.check(_lib.load().dsv32_indexer_prolog(C.byref(a), rt.stream_ptr(dev)), "lightning_indexer_prolog_quant")
+    del keep
     return None

@@ -6,10 +6,9 @@ plain row-major matrices (the reference passes NZ-format views of the same logic
 updated in place at rows `cache_index`; the cache "out" arguments must be the same tensors as the cache inputs,
 as in the reference tests.
 
-The four plain projections (x.w_dq, int8 q_norm.w_uq_qr, per-head q_nope.w_uk, x.w_dkv_kr) are library GEMMs
-(cuBLAS through torch); everything between them -- RMSNorm, int8 quantisation, dequantisation, de-interleaved
-RoPE, four-group cache quantisation and the cache scatter -- runs in the fused CUDA stages of
-libdsv32_b200.so (dsv32_mla_prolog_stage).
+The four projections (x.w_dq, int8 q_norm.w_uq_qr, per-head q_nope.w_uk, x.w_dkv_kr) and everything between
+them -- RMSNorm, int8 quantisation, dequantisation, de-interleaved RoPE, four-group cache quantisation and the
+cache scatter -- run in the kernels of libdsv32_b200.so; one call of dsv32_mla_prolog enqueues the operator.
 """
 from __future__ import annotations
 
@@ -40,20 +39,11 @@ class RopeTileShapeConfig:
     four_dim: list = None
 
 
-def _int8_gemm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """int8 [m,k] x int8 [k,n] -> int32 [m', n] with m' >= m (the library kernel wants more than 16 rows)."""
-    m = a.shape[0]
-    if m <= 16:
-        pad = torch.zeros((32, a.shape[1]), dtype=torch.int8, device=a.device)
-        pad[:m] = a
-        a = pad
-    return torch._int_mm(a, b)
-
-
-def mla_prolog(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index,
-               kv_cache, kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out, query_rope_out,
-               kv_cache_out, kr_cache_out, k_scale_cache_out, epsilon_cq, epsilon_ckv, cache_mode):
-    """Validates the arguments and runs the MLA prolog on the current stream of the tensors' device."""
+def validate(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index,
+             kv_cache, kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out, query_rope_out,
+             kv_cache_out, kr_cache_out, k_scale_cache_out, cache_mode):
+    """Checks dtypes, shapes, contiguity, aliasing of the in-place caches and that everything lives on one
+    device; returns that device."""
     rt.require_cuda()
     bf16 = torch.bfloat16
     rt.check_tensor(token_x, "token_x", bf16, (None, H))
@@ -87,34 +77,43 @@ def mla_prolog(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, 
     dev = rt.same_device(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin,
                          cache_index, kv_cache, kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out,
                          query_rope_out)
-    if t == 0:
+    return dev
+
+
+def mla_prolog(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index,
+               kv_cache, kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out, query_rope_out,
+               kv_cache_out, kr_cache_out, k_scale_cache_out, epsilon_cq, epsilon_ckv, cache_mode):
+    """Validates the arguments and runs the MLA prolog on the current stream of the tensors' device."""
+    dev = validate(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index,
+                   kv_cache, kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out, query_rope_out,
+                   kv_cache_out, kr_cache_out, k_scale_cache_out, cache_mode)
+    if token_x.shape[0] == 0:
         return None
-    lib = _lib.load()
+    a, keep = mla_args(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index,
+                       kv_cache, kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out, query_rope_out,
+                       epsilon_cq, epsilon_ckv, dev)
     with torch.cuda.device(dev):
-        stream = rt.stream_ptr(dev)
-        status = rt.status_word(dev)
-        q_nope_tmp = torch.empty((N_HEADS, t, NOPE), dtype=bf16, device=dev)
-
-        def stage(n, **kw):
-            a = _lib.MlaStageArgs()
-            a.t, a.status = t, status.data_ptr()
-            a.eps_cq, a.eps_ckv = float(epsilon_cq), float(epsilon_ckv)
-            for k, v in kw.items():
-                setattr(a, k, v.data_ptr() if isinstance(v, torch.Tensor) else v)
-            rt.check(lib.dsv32_mla_prolog_stage(C.byref(a), n, stream), f"mla_prolog_quant (stage {n})")
-
-        # ---- q path ---------------------------------------------------------------------------------------
-        q_a = torch.matmul(token_x, w_dq)                                         # library GEMM, bf16 out
-        stage(0, q_a=q_a, gamma_cq=gamma_cq, q_norm=q_norm_out, q_norm_scale=q_norm_scale_out)
-        q_b = _int8_gemm(q_norm_out, w_uq_qr)                                     # library GEMM, int32 out
-        stage(1, q_b=q_b, q_b_ld=q_b.shape[1], q_norm_scale=q_norm_scale_out, w_qb_scale=dequant_scale,
-              q_nope_tmp=q_nope_tmp, q_rope=query_rope_out, cos=cos, sin=sin)
-        query_nope_out.copy_(torch.bmm(q_nope_tmp, w_uk).permute(1, 0, 2))       # library GEMM, [128, t, 512]
-        # ---- kv path --------------------------------------------------------------------------------------
-        kv_a = torch.matmul(token_x, w_dkv_kr)                                    # library GEMM, bf16 out
-        stage(2, kv_a=kv_a, gamma_ckv=gamma_ckv, cos=cos, sin=sin, cache_index=cache_index, kv_cache=kv_cache,
-              kr_cache=kr_cache, k_scale_cache=k_scale_cache, cache_rows=blocks * bs)
+        rt.check(_lib.load().dsv32_mla_prolog(C.byref(a), rt.stream_ptr(dev)), "mla_prolog_quant")
+    del keep
     return None
+
+
+def mla_args(token_x, w_dq, w_uq_qr, dequant_scale, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index, kv_cache,
+             kr_cache, k_scale_cache, q_norm_out, q_norm_scale_out, query_nope_out, query_rope_out, epsilon_cq,
+             epsilon_ckv, dev):
+    """(Dsv32MlaPrologArgs, keep-alive list) for already validated tensors."""
+    lib = _lib.load()
+    t = token_x.shape[0]
+    with torch.cuda.device(dev):
+        ws_bytes = lib.dsv32_mla_prolog_workspace_bytes(t)
+        ws = rt.workspace(ws_bytes, dev)
+        a = _lib.MlaPrologArgs(
+            rt.ptr(token_x), rt.ptr(w_dq), rt.ptr(w_uq_qr), rt.ptr(dequant_scale), rt.ptr(w_uk), rt.ptr(w_dkv_kr),
+            rt.ptr(gamma_cq), rt.ptr(gamma_ckv), rt.ptr(cos), rt.ptr(sin), rt.ptr(cache_index), rt.ptr(kv_cache),
+            rt.ptr(kr_cache), rt.ptr(k_scale_cache), rt.ptr(q_norm_out), rt.ptr(q_norm_scale_out), rt.ptr(query_nope_out),
+            rt.ptr(query_rope_out), rt.ptr(ws), int(ws_bytes), rt.ptr(rt.status_word(dev)),
+            kv_cache.shape[0] * kv_cache.shape[1], t, float(epsilon_cq), float(epsilon_ckv))
+    return a, [ws]
 
 
 def _entry(name, args):
