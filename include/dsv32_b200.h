@@ -344,6 +344,27 @@ typedef struct {
 int dsv32_mla_indexer_prolog(const Dsv32FusedPrologArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Next decode step of a batch, on the device: act_seq[b] += grow, then the cache rows of the
+ * step's s1 tokens by the reference's rule for its test data
+ * (models/deepseek_v32_exp/deepseekv32_mla_indexer_prolog_quant.py:184-194):
+ *   pos = act_seq[b] - s1 + j,  cache_index[b, j] = block_table[b, pos / block_size] * block_size + pos % block_size.
+ * A position beyond the page table or on an unassigned page (-1) sets the status word and
+ * yields cache_index -1, which the prologs report and skip.  The reference computes this on the
+ * host for every call; a captured multi-step decode loop needs it on the stream.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t* act_seq;               /* in/out int32 [b]: length including the current step's tokens */
+  const int32_t* block_table;     /* int32 [b, max_blocks]                                        */
+  int64_t* cache_index;           /* out int64 [b, s1]                                            */
+  uint32_t* status;
+  int32_t b, s1;
+  int32_t grow;                   /* tokens every request appends in the step being prepared (usually s1) */
+  int32_t block_size, max_blocks;
+} Dsv32AdvanceArgs;
+
+int dsv32_decode_advance(const Dsv32AdvanceArgs* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * Fused element-wise stages of the DeepSeek-V4 MLA prolog (quant), between its three
  * library GEMMs.  Replaces the vector work of mla_prolog_v4 / mla_prolog_v4_in
  * (models/deepseek_v4/mla_prolog_quant_v4_impl.py:406-517 / 567-629):

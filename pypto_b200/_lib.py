@@ -123,6 +123,11 @@ class MlaPrologArgs(C.Structure):
     ]
 
 
+class AdvanceArgs(C.Structure):
+    _fields_ = [("act_seq", c_void_p), ("block_table", c_void_p), ("cache_index", c_void_p), ("status", c_void_p),
+                ("b", c_i32), ("s1", c_i32), ("grow", c_i32), ("block_size", c_i32), ("max_blocks", c_i32)]
+
+
 class FusedPrologArgs(C.Structure):
     _fields_ = [("mla", MlaPrologArgs), ("indexer", PrologArgs)]
 
@@ -153,6 +158,7 @@ EXPORTS = {
     "dsv32_mla_prolog": (c_i32, [C.POINTER(MlaPrologArgs), c_void_p]),
     "dsv32_mla_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_mla_indexer_prolog": (c_i32, [C.POINTER(FusedPrologArgs), c_void_p]),
+    "dsv32_decode_advance": (c_i32, [C.POINTER(AdvanceArgs), c_void_p]),
 }
 
 ABI_VERSION = 2

@@ -507,6 +507,24 @@ int dsv32_mla_indexer_prolog(const Dsv32FusedPrologArgs* a, void* cuda_stream) {
   return dsv32_indexer_prolog(&a->indexer, cuda_stream);
 }
 
+// ---- multi-step decode: next step's sequence lengths and cache rows ----------------------------------------------
+int dsv32_decode_advance(const Dsv32AdvanceArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "decode advance: args is NULL");
+  REQUIRE(a->b >= 0 && a->s1 >= 1, "decode advance: bad b=%d s1=%d", a->b, a->s1);
+  if (a->b == 0) return DSV32_OK;
+  REQUIRE(a->grow >= 0, "decode advance: grow=%d must be >= 0", a->grow);
+  REQUIRE(a->block_size >= 1 && a->max_blocks >= 1, "decode advance: bad block_size=%d max_blocks=%d", a->block_size,
+          a->max_blocks);
+  REQUIRE(a->act_seq && a->block_table && a->cache_index, "decode advance: NULL tensor pointer");
+  AdvanceParams p{};
+  p.act_seq = a->act_seq;
+  p.block_table = a->block_table;
+  p.cache_index = reinterpret_cast<long long*>(a->cache_index);
+  p.status = a->status;
+  p.b = a->b; p.s1 = a->s1; p.grow = a->grow; p.block_size = a->block_size; p.max_blocks = a->max_blocks;
+  return launch_decode_advance(p, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int dsv32_mla_prolog_v4_stage(const Dsv32MlaV4StageArgs* a, int32_t stage, void* cuda_stream) {
   REQUIRE(a != nullptr, "mla v4: args is NULL");
   REQUIRE(stage >= 0 && stage <= 2, "mla v4: stage=%d must be 0, 1 or 2", stage);

@@ -109,9 +109,9 @@ size_t prolog_workspace_bytes(int t);
 
 
 // MLA prolog (quant): x . [w_dq | w_dkv_kr] has 1536 + 576 = 2112 output columns and its reduction over the hidden
-// size is split over kMlaXSplits CTAs, whose fp32 partial sums the two finish kernels add in a fixed order.
-constexpr int kMlaXSplits = 4;
-constexpr int kMlaXCols = 2112;
+// size (112 chunks of 64) is split over kMlaXSplits CTAs, whose fp32 partial sums the two finish kernels add in a fixed order.
+constexpr int kMlaXSplits = 8;
+constexpr int kMlaXCols = 2176;   // 2112 rounded up to whole column tiles of 128 (the last 64 are padding)
 
 struct MlaStageParams {
   const float* partial;        // [kMlaXSplits][t][kMlaXCols] partial sums of x . [w_dq | w_dkv_kr]
@@ -130,7 +130,7 @@ struct MlaStageParams {
   int t;
   float eps_cq, eps_ckv;
 };
-int launch_mla_stage(const MlaStageParams& p, int stage, cudaStream_t stream);
+int launch_mla_finish(const MlaStageParams& p, cudaStream_t stream);
 
 struct MlaParams {
   const __nv_bfloat16* x;          // [t, 7168]
@@ -178,6 +178,15 @@ struct MlaV4StageParams {
   float eps;
 };
 int launch_mla_v4_stage(const MlaV4StageParams& p, int stage, cudaStream_t stream);
+
+struct AdvanceParams {
+  int32_t* act_seq;              // in/out [b]
+  const int32_t* block_table;    // [b, max_blocks]
+  long long* cache_index;        // out [b, s1]
+  uint32_t* status;
+  int b, s1, grow, block_size, max_blocks;
+};
+int launch_decode_advance(const AdvanceParams& p, cudaStream_t stream);
 
 struct CompressorParams {
   const float* kv_total;       // [b*s1, coff*d]  x . wkv^T

@@ -1,7 +1,7 @@
 // Element-wise stages of the MLA prolog (quant) -- the MLA half of mla_indexer_prolog_quant
 // (models/deepseek_v32_exp/mla_indexer_prolog_quant_impl.py:112-211; helpers mla_prolog_quant_impl.py:96-361;
 // golden deepseekv32_mla_indexer_prolog_quant.py:395-539) -- that follow the split-reduction projection
-// x . [w_dq | w_dkv_kr] of mla_prolog_tc.cu: both kernels first add its fp32 partial sums in a fixed order and round
+// x . [w_dq | w_dkv_kr] of mla_prolog_tc.cu (one launch, blockIdx.y selects the stage): both first add its fp32 partial sums in a fixed order and round
 // to bf16 (the reference's q_a / kv_a).
 //   stage 0: q_a (columns 0..1535) -> RMSNorm(gamma_cq) -> bf16 -> per-token int8 quant -> q_norm, q_norm_scale
 //   stage 2: kv_a (columns 1536..2111) -> RMSNorm(gamma_ckv) of the first 512 -> four 128-dim int8 groups + fp32
@@ -55,37 +55,40 @@ __device__ __forceinline__ float rope_deinterleaved(const float* x, int j, const
   return __fadd_rn(__fmul_rn(xj, __bfloat162float(cos[j])), __fmul_rn(xr, __bfloat162float(sin[j])));
 }
 
-// ---- stage 0 ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) mla_rmsnorm_quant_kernel(MlaStageParams p) {
-  __shared__ float red[8];
-  const int tok = blockIdx.x, tid = threadIdx.x;
-  float x[6], ss = 0.f;
+// ---- stage 0: one CTA per token, 512 threads (three of the 1536 dims each) ------------------------------------------
+__device__ __forceinline__ void mla_rmsnorm_quant(const MlaStageParams& p, int tok, float* red) {
+  const int tid = threadIdx.x;
+  float x[3], ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 6; ++i) {
-    x[i] = partial_sum_bf16(p, tok, tid + i * 256);
+  for (int i = 0; i < 3; ++i) {
+    x[i] = partial_sum_bf16(p, tok, tid + i * 512);
     ss += __fmul_rn(__fmul_rn(x[i], x[i]), 1.0f / 1536.0f);
   }
-  const float rms = sqrtf(block_sum<256>(ss, red) + p.eps_cq);
+  const float rms = sqrtf(block_sum<512>(ss, red) + p.eps_cq);
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 6; ++i) {
-    x[i] = bf16r(__fmul_rn(__fdiv_rn(x[i], rms), __bfloat162float(p.gamma_cq[tid + i * 256])));
+  for (int i = 0; i < 3; ++i) {
+    x[i] = bf16r(__fmul_rn(__fdiv_rn(x[i], rms), __bfloat162float(p.gamma_cq[tid + i * 512])));
     amax = fmaxf(amax, fabsf(x[i]));
   }
-  amax = block_max<256>(amax, red);
+  amax = block_max<512>(amax, red);
   const float sq = __fdiv_rn(127.0f, amax);
 #pragma unroll
-  for (int i = 0; i < 6; ++i)
-    p.q_norm[static_cast<size_t>(tok) * 1536 + tid + i * 256] = static_cast<int8_t>(static_cast<int>(rintf(__fmul_rn(x[i], sq))));
+  for (int i = 0; i < 3; ++i)
+    p.q_norm[static_cast<size_t>(tok) * 1536 + tid + i * 512] = static_cast<int8_t>(static_cast<int>(rintf(__fmul_rn(x[i], sq))));
   if (tid == 0) p.q_norm_scale[tok] = __fdiv_rn(1.0f, sq);
 }
 
 // ---- stage 2: one CTA per token, 512 threads -------------------------------------------------------------------
-__global__ void __launch_bounds__(512) mla_kv_finish_kernel(MlaStageParams p) {
+__global__ void __launch_bounds__(512) mla_finish_kernel(MlaStageParams p) {
   __shared__ float red[16];
   __shared__ float gmax[4];
   __shared__ float rope_s[64];
   const int tok = blockIdx.x, tid = threadIdx.x;
+  if (blockIdx.y == 0) {   // both stages in one launch: blockIdx.y selects (uniform for the CTA)
+    mla_rmsnorm_quant(p, tok, red);
+    return;
+  }
   const float x = partial_sum_bf16(p, tok, 1536 + tid);
   if (tid < 64) rope_s[tid] = partial_sum_bf16(p, tok, 1536 + 512 + tid);
   const float rms = sqrtf(block_sum<512>(__fmul_rn(__fmul_rn(x, x), 1.0f / 512.0f), red) + p.eps_ckv);
@@ -111,15 +114,11 @@ __global__ void __launch_bounds__(512) mla_kv_finish_kernel(MlaStageParams p) {
         rope_deinterleaved(rope_s, tid, p.cos + static_cast<size_t>(tok) * 64, p.sin + static_cast<size_t>(tok) * 64));
 }
 
-int launch_mla_stage(const MlaStageParams& p, int stage, cudaStream_t stream) {
+int launch_mla_finish(const MlaStageParams& p, cudaStream_t stream) {
   if (p.t <= 0) return DSV32_OK;
-  if (stage == 0) {
-    mla_rmsnorm_quant_kernel<<<p.t, 256, 0, stream>>>(p);
-  } else {
-    mla_kv_finish_kernel<<<p.t, 512, 0, stream>>>(p);
-  }
+  mla_finish_kernel<<<dim3(p.t, 2), 512, 0, stream>>>(p);
   count_launch();
-  return check_launch("mla prolog stage kernel");
+  return check_launch("mla_finish_kernel");
 }
 
 }  // namespace dsv32

@@ -7,12 +7,12 @@
 // with the activations K-major (row-major [tokens, K]) and the weights MN-major (row-major [K, N], as the caller
 // holds them), both streamed by TMA (128-byte swizzle, never multicast) through a ring of shared-memory stages;
 // the accumulator lives in tensor memory and every epilogue thread owns one token row.
-//   kXproj  bf16  x[t,7168] x [w_dq | w_dkv_kr] (2112 columns in tiles of 64), the reduction split over four CTAs;
-//                 fp32 partial sums go to the workspace (finished by mla_rmsnorm_quant_kernel / mla_kv_finish_kernel)
-//   kQb     int8  q_norm[t,1536] x w_uq_qr[1536, 128 heads x 192] in tiles of 128 columns; the epilogue dequantises
+//   kXproj  bf16  x[t,7168] x [w_dq | w_dkv_kr] (2112 columns in 17 tiles of 128), the reduction split over eight CTAs;
+//                 fp32 partial sums go to the workspace (finished by mla_finish_kernel)
+//   kQb     int8  q_norm[t,1536] x w_uq_qr[1536, 128 heads x 192], 256 columns per CTA; the epilogue dequantises
 //                 (x q_norm_scale x w_qb_scale -> bf16), sends the 128 "nope" dims of a head to a compact
 //                 [t,128,128] buffer and the 64 "rope" dims through the de-interleaving rotary embedding to q_rope
-//   kUk     bf16  per head: nope[t,128] x w_uk[head][128,512] (256 columns per CTA) -> q_nope[t,128,512] bf16
+//   kUk     bf16  per head: nope[t,128] x w_uk[head][128,512] (one CTA per head) -> q_nope[t,128,512] bf16
 // The weights (85 MB) are read once; the projections are bound by that stream, not by arithmetic.
 #include "kernels.cuh"
 #include "tc_common.cuh"
@@ -40,26 +40,30 @@ struct MlaGemmParams {
 template <int kKind>
 struct GemmShape {
   static constexpr bool kInt8 = kKind == kQb;
-  static constexpr int kNChunks = kKind == kUk ? 4 : 1;               // 128-byte column chunks of B per stage
-  static constexpr int kN = kNChunks * (kInt8 ? 128 : 64);            // 64 / 128 / 256 columns per CTA
+  // 128-byte column chunks of B per stage: 128 / 256 / 512 columns per CTA.  Few, wide CTAs with deep rings: what
+  // bounds these kernels is the bytes of weights one SM keeps in flight, not the number of CTAs.
+  static constexpr int kNChunks = kKind == kUk ? 8 : 2;
+  static constexpr int kN = kNChunks * (kInt8 ? 128 : 64);
+  static constexpr int kMmaN = kN > 256 ? 256 : kN;                   // columns per MMA instruction
   static constexpr int kKRows = kInt8 ? 128 : 64;                     // reduction elements per stage (128 B of A)
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBChunk = kKRows * 128;
-  static constexpr int kStageBytes = kABytes + kNChunks * kBChunk;    // 24 / 32 / 48 KB
-  static constexpr int kStages = kKind == kXproj ? 6 : (kKind == kQb ? 3 : 2);
+  static constexpr int kStageBytes = kABytes + kNChunks * kBChunk;    // 32 / 48 / 80 KB
+  static constexpr int kStages = kKind == kXproj ? 6 : (kKind == kQb ? 4 : 2);
   static constexpr int kChunksTotal = kKind == kXproj ? kMlaH / 64 : (kKind == kQb ? kMlaQLora / 128 : kMlaNope / 64);
-  static constexpr int kOffWs = kStages * kStageBytes;                // kQb: 128 column scales
-  static constexpr int kOffBars = kOffWs + 512;
+  static constexpr int kOffWs = kStages * kStageBytes;                // kQb: 256 column scales
+  static constexpr int kOffBars = kOffWs + 1024;
   static constexpr int kOffTmem = kOffBars + (2 * kStages + 1) * 8;
   static constexpr size_t kSmemBytes = kOffTmem + 16 + 1024;          // slack for manual 1024-byte alignment
   static constexpr uint32_t kTmemCols = kN < 32 ? 32 : kN;
-  static constexpr int kCtasPerSm = kKind == kXproj ? 1 : 2;
 };
+constexpr int kMlaXTilesQ = kMlaQLora / 128;                          // 12 column tiles of w_dq, then 5 of w_dkv_kr
+constexpr int kMlaXTiles = kMlaXCols / 128;                           // (the last one half past the matrix: zero-filled)
 
 __device__ __forceinline__ float mla_bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 template <int kKind>
-__global__ void __launch_bounds__(kGemmThreads, GemmShape<kKind>::kCtasPerSm)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map0,
                    const __grid_constant__ CUtensorMap b_map1, MlaGemmParams p) {
   using Sh = GemmShape<kKind>;
@@ -73,7 +77,7 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
   uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + Sh::kOffTmem);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tile = blockIdx.x;          // kXproj: column tile of 64; kQb: column tile of 128; kUk: head * 2 + half
+  const int tile = blockIdx.x;          // kXproj: column tile of 128; kQb: column tile of 256 (two of 128); kUk: head
   const int split = blockIdx.y;         // kXproj only
   const int t0 = blockIdx.z * 128;
   // reduction chunks of this CTA
@@ -99,7 +103,8 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
     tmem_alloc(tmem_ptr_s, Sh::kTmemCols);
     tmem_relinquish();
   } else if constexpr (kKind == kQb) {
-    ws_s[tid - 64] = p.w_qb_scale[tile * 128 + (tid - 64)];
+    ws_s[tid - 64] = p.w_qb_scale[tile * 256 + (tid - 64)];
+    ws_s[tid + 64] = p.w_qb_scale[tile * 256 + 128 + (tid - 64)];
   }
   tc_fence_before();
   __syncthreads();
@@ -117,25 +122,28 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
         const int k0 = (c_begin + c) * Sh::kKRows;   // first reduction element of the chunk
         if constexpr (kKind == kXproj) {
           tma_load_2d(st, &a_map, k0 * 2, t0, &full_bar[s]);
-          if (tile < kMlaQLora / 64) tma_load_2d(st + Sh::kABytes, &b_map0, tile * 128, k0, &full_bar[s]);
-          else tma_load_2d(st + Sh::kABytes, &b_map1, (tile - kMlaQLora / 64) * 128, k0, &full_bar[s]);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (tile < kMlaXTilesQ) tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, tile * 256 + j * 128, k0, &full_bar[s]);
+            else tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map1, (tile - kMlaXTilesQ) * 256 + j * 128, k0, &full_bar[s]);
+          }
         } else if constexpr (kKind == kQb) {
           tma_load_2d(st, &a_map, k0, t0, &full_bar[s]);
-          tma_load_2d(st + Sh::kABytes, &b_map0, tile * 128, k0, &full_bar[s]);
-        } else {
-          const int head = tile >> 1, half = tile & 1;
-          tma_load_2d(st, &a_map, head * 256 + k0 * 2, t0, &full_bar[s]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, half * 512 + j * 128, head * kMlaNope + k0,
-                        &full_bar[s]);
+          for (int j = 0; j < 2; ++j)
+            tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, tile * 256 + j * 128, k0, &full_bar[s]);
+        } else {
+          tma_load_2d(st, &a_map, tile * 256 + k0 * 2, t0, &full_bar[s]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, j * 128, tile * kMlaNope + k0, &full_bar[s]);
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer: the whole warp runs the loop (uniform operands), lane 0 issues ---------------------------
     const bool leader = lane == 0;
-    constexpr uint32_t idesc = Sh::kInt8 ? umma_idesc_i8(128, Sh::kN, true) : umma_idesc_bf16(128, Sh::kN, false, true);
+    constexpr uint32_t idesc = Sh::kInt8 ? umma_idesc_i8(128, Sh::kMmaN, true) : umma_idesc_bf16(128, Sh::kMmaN, false, true);
     const uint32_t tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
@@ -147,16 +155,20 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {  // 32 bytes of A's row per instruction: 32 int8 / 16 bf16 reduction elements
         const uint64_t ad = umma_smem_desc_sw128(a_s + ks * 32, 16, 1024);
-        const uint64_t bd = umma_smem_desc_sw128(b_s + ks * (Sh::kInt8 ? 4096 : 2048), Sh::kBChunk, 1024);
         const uint32_t acc = (c > 0 || ks > 0) ? 1u : 0u;
-        if constexpr (Sh::kInt8) {
-          asm volatile(
-              "{\n\t.reg .pred pa, pl;\n\tsetp.ne.b32 pa, %4, 0;\n\tsetp.ne.b32 pl, %5, 0;\n\t"
-              "@pl tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, pa;\n\t}" ::"r"(tbase),
-              "l"(ad), "l"(bd), "r"(idesc), "r"(acc), "r"(static_cast<uint32_t>(leader))
-              : "memory");
-        } else {
-          umma_f16_ss_if(leader, tbase, ad, bd, idesc, acc);
+#pragma unroll
+        for (int h = 0; h < Sh::kN / Sh::kMmaN; ++h) {  // 512 columns: two instructions of 256
+          const uint64_t bd = umma_smem_desc_sw128(b_s + h * (Sh::kMmaN / (Sh::kInt8 ? 128 : 64)) * Sh::kBChunk +
+                                                       ks * (Sh::kInt8 ? 4096 : 2048), Sh::kBChunk, 1024);
+          if constexpr (Sh::kInt8) {
+            asm volatile(
+                "{\n\t.reg .pred pa, pl;\n\tsetp.ne.b32 pa, %4, 0;\n\tsetp.ne.b32 pl, %5, 0;\n\t"
+                "@pl tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, pa;\n\t}" ::"r"(tbase + h * Sh::kMmaN),
+                "l"(ad), "l"(bd), "r"(idesc), "r"(acc), "r"(static_cast<uint32_t>(leader))
+                : "memory");
+          } else {
+            umma_f16_ss_if(leader, tbase + h * Sh::kMmaN, ad, bd, idesc, acc);
+          }
         }
       }
       umma_commit_if(leader, &empty_bar[s]);
@@ -172,9 +184,9 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
     if (__all_sync(0xffffffffu, mbar_wait(d_bar, 0, p.status, 62))) {
       tc_fence_after();
       if constexpr (kKind == kXproj) {
-        float* prow = p.partial + (static_cast<size_t>(split) * p.t + tk) * kMlaXCols + tile * 64;
+        float* prow = p.partial + (static_cast<size_t>(split) * p.t + tk) * kMlaXCols + tile * 128;
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + lane_addr + c * 32, r);
           tmem_ld_wait();
@@ -189,15 +201,18 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
       } else if constexpr (kKind == kQb) {
         // 384 columns = two heads: column tile 3j is the nope part of head 2j, tile 3j+1 its rope part followed by
         // nope dims 0..63 of head 2j+1, tile 3j+2 nope dims 64..127 of head 2j+1 followed by its rope part.
-        const int m = tile % 3, pair = tile / 3;
         const float qs = p.q_norm_scale[tk];
+#pragma unroll 1
+        for (int sub = 0; sub < 2; ++sub) {   // the CTA's 256 columns are two tiles of 128
+        const int tile128 = tile * 2 + sub;
+        const int m = tile128 % 3, pair = tile128 / 3;
         auto dequant32 = [&](int g, float (&v)[32]) {  // columns 32g .. 32g+31 of the tile -> bf16-rounded floats
           uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + g * 32, r);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + sub * 128 + g * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            v[j] = mla_bf16r(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), qs), ws_s[g * 32 + j]));
+            v[j] = mla_bf16r(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), qs), ws_s[sub * 128 + g * 32 + j]));
         };
         auto store_nope32 = [&](int head, int d0, const float (&v)[32]) {  // nope dims d0 .. d0+31 of `head`
           uint32_t w[16];
@@ -264,11 +279,11 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
           dequant32(3, vb);
           rope_store(2 * pair + 1, va, vb);
         }
+        }
       } else {
-        const int head = tile >> 1, half = tile & 1;
-        __nv_bfloat16* orow = p.q_nope + (static_cast<size_t>(tk) * kMlaHeads + head) * kMlaLora + half * 256;
+        __nv_bfloat16* orow = p.q_nope + (static_cast<size_t>(tk) * kMlaHeads + tile) * kMlaLora;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 16; ++c) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + lane_addr + c * 32, r);
           tmem_ld_wait();
@@ -332,6 +347,7 @@ int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
     rc = make_tensor_map_2d_u8(&wqb_map, p.w_uq_qr, kMlaQLora, kMlaHeads * (kMlaNope + kMlaRope), 128, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&ni_map, nope_in, p.t, kMlaHeads * kMlaNope * 2, 128, 128);
   if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&wuk_map, p.w_uk, kMlaHeads * kMlaNope, kMlaLora * 2, 64, 128);
+  static_assert(kMlaXTiles * 128 == kMlaXCols && kMlaXTilesQ * 128 == kMlaQLora, "column tiles of the x projections");
   if (rc != DSV32_OK) return rc;
 
   MlaGemmParams gp{};
@@ -346,7 +362,7 @@ int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
   gp.status = p.status;
   gp.t = p.t;
 
-  rc = launch_gemm<kXproj>(x_map, wdq_map, wkv_map, gp, dim3(kMlaXCols / 64, kMlaXSplits, tiles), stream,
+  rc = launch_gemm<kXproj>(x_map, wdq_map, wkv_map, gp, dim3(kMlaXTiles, kMlaXSplits, tiles), stream,
                            "mla_gemm_tc_kernel (x projections)");
   if (rc != DSV32_OK) return rc;
   MlaStageParams sp{};
@@ -366,14 +382,12 @@ int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
   sp.t = p.t;
   sp.eps_cq = p.eps_cq;
   sp.eps_ckv = p.eps_ckv;
-  rc = launch_mla_stage(sp, 0, stream);
+  rc = launch_mla_finish(sp, stream);
   if (rc != DSV32_OK) return rc;
-  rc = launch_mla_stage(sp, 2, stream);
-  if (rc != DSV32_OK) return rc;
-  rc = launch_gemm<kQb>(qn_map, wqb_map, wqb_map, gp, dim3(kMlaHeads * (kMlaNope + kMlaRope) / 128, 1, tiles), stream,
+  rc = launch_gemm<kQb>(qn_map, wqb_map, wqb_map, gp, dim3(kMlaHeads * (kMlaNope + kMlaRope) / 256, 1, tiles), stream,
                         "mla_gemm_tc_kernel (q_norm . w_uq_qr)");
   if (rc != DSV32_OK) return rc;
-  return launch_gemm<kUk>(ni_map, wuk_map, wuk_map, gp, dim3(kMlaHeads * 2, 1, tiles), stream,
+  return launch_gemm<kUk>(ni_map, wuk_map, wuk_map, gp, dim3(kMlaHeads, 1, tiles), stream,
                           "mla_gemm_tc_kernel (q_nope . w_uk)");
 }
 

@@ -10,6 +10,10 @@ from __future__ import annotations
 
 import torch
 
+import ctypes as C
+
+from . import _lib
+from . import _runtime as rt
 from .lightning_indexer_prolog_quant_impl import (IndexerPrologQuantAttr, IndexerPrologQuantConfigs,
                                                   lightning_indexer_prolog_quant)
 from .lightning_indexer_quant_impl import LightningIndexerConfigs, lightning_indexer_decode
@@ -195,3 +199,106 @@ class HostPipelinedDecode:
         run = torch.cuda.current_stream(self.dev)
         for e in self.out_done[: min(self.k, 2)]:
             run.wait_event(e)
+
+
+def decode_advance(act_seq, block_table, cache_index, s1, grow=None, block_size=128):
+    """Prepare the next decode step on the device (dsv32_decode_advance): act_seq += grow (default s1) and the cache
+    rows of the step's tokens by the reference's rule (deepseekv32_mla_indexer_prolog_quant.py:184-194).  In place,
+    on the current stream, capturable."""
+    rt.require_cuda()
+    rt.check_tensor(act_seq, "act_seq", torch.int32, ndim=1)
+    b = act_seq.shape[0]
+    rt.check_tensor(block_table, "block_table", torch.int32, (b, None))
+    rt.check_tensor(cache_index, "cache_index", torch.int64, (b * int(s1),))
+    dev = rt.same_device(act_seq, block_table, cache_index)
+    a = _lib.AdvanceArgs(rt.ptr(act_seq), rt.ptr(block_table), rt.ptr(cache_index), rt.ptr(rt.status_word(dev)), b, int(s1),
+                         int(s1 if grow is None else grow), int(block_size), block_table.shape[1])
+    with torch.cuda.device(dev):
+        rt.check(_lib.load().dsv32_decode_advance(C.byref(a), rt.stream_ptr(dev)), "decode_advance")
+
+
+class FullDecodeStep:
+    """A decode loop that appends: every step runs the fused MLA + indexer prolog on the step's hidden states (which
+    writes the s1 new rows of both caches at `cache_index`), the lightning indexer + top-k over the grown context and
+    the sparse attention; `advance()` then moves the batch to the next positions on the device.  `w` is a
+    synth.FullDecodeWorkload; x / cos / sin of a step are copied into fixed buffers so that the loop can be captured."""
+
+    def __init__(self, w, nq=128, topk=2048):
+        from .mla_indexer_prolog_quant_impl import MlaTileConfig, RopeTileShapeConfig
+        self.w = w
+        dev = w.kv_cache.device
+        t = w.t
+        self.nq, self.topk = nq, topk
+        bf = torch.bfloat16
+        self.x = torch.zeros((t, 7168), dtype=bf, device=dev)
+        self.cos = torch.zeros((t, 64), dtype=bf, device=dev)
+        self.sin = torch.zeros((t, 64), dtype=bf, device=dev)
+        self.q_nope = torch.empty((t, nq, 512), dtype=bf, device=dev)
+        self.q_rope = torch.empty((t, nq, 64), dtype=bf, device=dev)
+        self.q_int8 = torch.empty((t, 64, 128), dtype=torch.int8, device=dev)
+        self.q_scale = torch.empty((t, 64, 1), dtype=torch.float16, device=dev)
+        self.weights = torch.empty((t, 64), dtype=torch.float16, device=dev)
+        self.topk_res = torch.empty((t, 1, topk), dtype=torch.int32, device=dev)
+        self.out = torch.empty((w.b, w.s1, nq, 512), dtype=bf, device=dev)
+        self._cfg = (MlaTileConfig(), IndexerPrologQuantAttr(eps=1e-6), IndexerPrologQuantConfigs(), RopeTileShapeConfig(),
+                     LightningIndexerConfigs(), SaTileShapeConfig())
+        self.graph = None
+
+    def set_inputs(self, x, cos, sin):
+        self.x.copy_(x, non_blocking=True)
+        self.cos.copy_(cos, non_blocking=True)
+        self.sin.copy_(sin, non_blocking=True)
+
+    def prolog(self):
+        from .mla_indexer_prolog_quant_impl import mla_indexer_prolog_quant_d
+        w = self.w
+        mla_cfg, ip_attr, ip_cfg, rope_cfg = self._cfg[:4]
+        mla_indexer_prolog_quant_d(
+            self.x, w.w_dq, w.w_uq_qr, w.w_uq_qr_scale, w.w_uk, w.w_dkv_kr, w.gamma_cq, w.gamma_ckv, self.cos, self.sin,
+            w.cache_index, w.kv_cache, w.kr_cache, w.k_scale_cache, w.w_qb, w.w_qb_scale, w.wk, w.w_proj, w.ln_gamma,
+            w.ln_beta, w.hadamard, w.hadamard, w.idx_k, w.idx_k_scale, self.q_nope, self.q_rope, w.kv_cache, w.kr_cache,
+            w.k_scale_cache, self.q_int8, self.q_scale, w.idx_k, w.idx_k_scale, self.weights, 1e-6, 1e-6, "PA_BSND",
+            mla_cfg, ip_attr, ip_cfg, rope_cfg)
+
+    def indexer(self):
+        w = self.w
+        lightning_indexer_decode(self.q_int8, self.q_scale.reshape(-1, 64), w.idx_k,
+                                 w.idx_k_scale.reshape(w.idx_k_scale.shape[0], 128, 1), self.weights, w.act_seq,
+                                 w.block_table, self.topk_res, None, self._cfg[4], self.topk)
+
+    def attention(self):
+        w = self.w
+        sparse_flash_attention_quant_d(self.q_nope.reshape(-1, 512), self.q_rope.reshape(-1, 64),
+                                       w.kv_cache.reshape(-1, 512), w.kr_cache.reshape(-1, 64),
+                                       w.k_scale_cache.reshape(-1, 4), self.topk_res.reshape(-1, self.topk), w.block_table,
+                                       w.act_seq, self.out, self.nq, 1, 576 ** -0.5, self.topk, 128, w.max_blocks,
+                                       self._cfg[5])
+
+    def step(self):
+        self.prolog()
+        self.indexer()
+        self.attention()
+        return self.out
+
+    def advance(self):
+        decode_advance(self.w.act_seq, self.w.block_table, self.w.cache_index, self.w.s1)
+
+    def capture(self):
+        """One CUDA graph of step() followed by advance(): every replay is the next decode step (new hidden states
+        are copied into `x`, `cos`, `sin` before it)."""
+        dev = self.out.device
+        cur = torch.cuda.current_stream(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(cur)
+        saved = (self.w.act_seq.clone(), self.w.cache_index.clone())
+        with torch.cuda.stream(side):   # warm-up outside capture (lazy initialisation); undone below
+            self.step()
+        cur.wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+            self.advance()
+        self.w.act_seq.copy_(saved[0])
+        self.w.cache_index.copy_(saved[1])
+        self.graph = g
+        return g

@@ -177,3 +177,109 @@ def make_long_request(ctx, s1, seed, device, token_slice=None, sample=None, bloc
                    eff=torch.tensor([ctx - s1 + 1 + i for i in pick], dtype=torch.int32))
     dev = torch.device(device)
     return {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in out.items()}
+
+
+@dataclass
+class FullDecodeWorkload:
+    """State of a multi-step decode loop through the fused MLA + indexer prolog: both paged caches (sharing one
+    page table with room to grow), the weights of both prolog halves, and the batch's position state."""
+    b: int
+    s1: int
+    block_table: torch.Tensor     # int32 [b, max_blocks], -1 = not assigned
+    act_seq: torch.Tensor         # int32 [b]: length including the current step's s1 tokens
+    cache_index: torch.Tensor     # int64 [b * s1]: cache rows of the current step's tokens
+    kv_cache: torch.Tensor        # int8 [blocks, 128, 1, 512]
+    kr_cache: torch.Tensor        # bf16 [blocks, 128, 1, 64]
+    k_scale_cache: torch.Tensor   # fp32 [blocks, 128, 1, 4]
+    idx_k: torch.Tensor           # int8 [blocks, 128, 1, 128]
+    idx_k_scale: torch.Tensor     # fp16 [blocks, 128, 1, 1]
+    w_dq: torch.Tensor
+    w_uq_qr: torch.Tensor
+    w_uq_qr_scale: torch.Tensor
+    w_uk: torch.Tensor
+    w_dkv_kr: torch.Tensor
+    gamma_cq: torch.Tensor
+    gamma_ckv: torch.Tensor
+    w_qb: torch.Tensor
+    w_qb_scale: torch.Tensor
+    wk: torch.Tensor
+    w_proj: torch.Tensor
+    ln_gamma: torch.Tensor
+    ln_beta: torch.Tensor
+    hadamard: torch.Tensor
+
+    @property
+    def t(self):
+        return self.b * self.s1
+
+    @property
+    def max_blocks(self):
+        return self.block_table.shape[1]
+
+
+def cache_index_for(act_seq, block_table, s1, block_size=128):
+    """The reference's rule (deepseekv32_mla_indexer_prolog_quant.py:184-194) on the host: rows of the s1 newest
+    positions of every request."""
+    bt = block_table.cpu()
+    out = []
+    for bi, cur in enumerate(act_seq.cpu().tolist()):
+        for j in range(s1):
+            pos = cur - s1 + j
+            out.append(int(bt[bi, pos // block_size]) * block_size + pos % block_size if pos >= 0 else -1)
+    return torch.tensor(out, dtype=torch.int64)
+
+
+def make_full_decode_workload(ctx, s1, grow_tokens, seed, device, block_size=128):
+    """ctx: per-request lengths including the first step's s1 tokens; every request gets pages for
+    ctx + grow_tokens positions.  Caches hold random history, weights follow the distributions of the single-step
+    workloads.  Drawn from a CPU generator (the same bits on any device)."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    b = len(ctx)
+    nblk = [math.ceil((c + grow_tokens) / block_size) for c in ctx]
+    blocks = sum(nblk)
+    perm = torch.randperm(blocks, generator=g).to(torch.int32)
+    block_table = torch.full((b, max(nblk)), -1, dtype=torch.int32)
+    pos = 0
+    for i, n in enumerate(nblk):
+        block_table[i, :n] = perm[pos:pos + n]
+        pos += n
+    act_seq = torch.tensor(ctx, dtype=torch.int32)
+
+    def randn(shape, std=1.0, dtype=bf):
+        return (torch.randn(shape, generator=g) * std).to(dtype)
+
+    def randint8(shape):
+        return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8)
+
+    wq = torch.randn((1536, 128 * 192), generator=g) * 0.02
+    wq_amax = wq.abs().amax(0, keepdim=True)
+    wi = torch.randn((1536, 8192), generator=g) * 0.02
+    wi_amax = wi.abs().amax(0, keepdim=True)
+    w = FullDecodeWorkload(
+        b=b, s1=s1, block_table=block_table, act_seq=act_seq, cache_index=cache_index_for(act_seq, block_table, s1),
+        kv_cache=randint8((blocks, block_size, 1, 512)), kr_cache=randn((blocks, block_size, 1, 64)),
+        k_scale_cache=torch.rand((blocks, block_size, 1, 4), generator=g) * 0.019 + 0.001,
+        idx_k=randint8((blocks, block_size, 1, 128)),
+        idx_k_scale=(torch.rand((blocks, block_size, 1, 1), generator=g) * 0.019 + 0.001).to(torch.float16),
+        w_dq=randn((7168, 1536), 0.02), w_uq_qr=torch.round(wq * (127 / wq_amax)).to(torch.int8),
+        w_uq_qr_scale=(wq_amax / 127).reshape(-1, 1).float().contiguous(), w_uk=randn((128, 128, 512), 0.05),
+        w_dkv_kr=randn((7168, 576), 0.02), gamma_cq=(1 + randn((1536,), 0.1, torch.float32)).to(bf),
+        gamma_ckv=(1 + randn((512,), 0.1, torch.float32)).to(bf),
+        w_qb=torch.round(wi * (127 / wi_amax)).to(torch.int8), w_qb_scale=(wi_amax / 127).reshape(8192, 1).float().contiguous(),
+        wk=randn((7168, 128), 0.02), w_proj=randn((7168, 64), 0.02), ln_gamma=torch.ones(128, dtype=bf),
+        ln_beta=torch.zeros(128, dtype=bf), hadamard=sylvester_hadamard(128, bf))
+    dev = torch.device(device)
+    for k, v in list(vars(w).items()):
+        if isinstance(v, torch.Tensor):
+            setattr(w, k, v.to(dev))
+    return w
+
+
+def make_full_step_activations(t, seed, device):
+    """Hidden states and rotary tables of one decode step: x bf16 [t, 7168], cos / sin bf16 [t, 64]."""
+    g = torch.Generator().manual_seed(seed)
+    ang = torch.rand((t, 64), generator=g) * 2 * math.pi
+    dev = torch.device(device)
+    return dict(x=torch.randn((t, 7168), generator=g).to(torch.bfloat16).to(dev), cos=torch.cos(ang).to(torch.bfloat16).to(dev),
+                sin=torch.sin(ang).to(torch.bfloat16).to(dev))

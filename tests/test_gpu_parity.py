@@ -1426,3 +1426,100 @@ def test_captured_step_matches_eager_step():
     torch.cuda.synchronize()
     pypto_b200.check_status()
     assert torch.equal(bufs[-1], want.cpu()) and torch.equal(bufs[-2], want.cpu())
+
+
+# --------------------------------------------------------------------------------------------------
+# multi-step decode: every step appends its tokens to both caches and the next step sees them
+# --------------------------------------------------------------------------------------------------
+def test_decode_loop_appends_to_both_caches_across_pages():
+    """Four decode steps of a small ragged batch through fused prolog -> indexer + top-k -> attention -> advance,
+    replayed from ONE captured CUDA graph.  Request 1 crosses a page boundary between steps, request 2 inside a
+    step.  After every step: the position state follows the reference's cache-index rule; exactly the rows of the
+    step's tokens changed in both caches, to the oracle's values; the top-k (on the device's own prolog outputs and
+    caches) and the attention (on the device's own queries, caches and top-k) match the oracle -- so the keys a step
+    appends are scored and attended to by the steps after it."""
+    import pypto_b200
+    from pypto_b200 import synth
+    from pypto_b200.decode_chain import FullDecodeStep
+    ctx, s1, steps = [300, 126, 255], 2, 4
+    w = synth.make_full_decode_workload(ctx, s1, s1 * steps, 41, DEV)
+    step = FullDecodeStep(w)
+    t = w.t
+    cpu = lambda x: x.detach().cpu()  # noqa: E731
+    wc = {k: cpu(v) for k, v in vars(w).items() if isinstance(v, torch.Tensor)}
+    step.set_inputs(**synth.make_full_step_activations(t, 899, DEV))   # the capture's warm-up run uses other inputs
+    step.capture()
+    for k in range(steps):
+        acts = synth.make_full_step_activations(t, 900 + k, "cpu")
+        step.set_inputs(**acts)
+        before = {n: cpu(getattr(w, n)).clone() for n in ("kv_cache", "kr_cache", "k_scale_cache", "idx_k", "idx_k_scale",
+                                                          "act_seq", "cache_index")}
+        step.graph.replay()
+        pypto_b200.check_status()
+        act, ci = before["act_seq"], before["cache_index"]
+        assert act.tolist() == [c + k * s1 for c in ctx]
+        assert torch.equal(ci, synth.cache_index_for(act, wc["block_table"], s1))
+        # ---- position state after the step ---------------------------------------------------------------
+        assert cpu(w.act_seq).tolist() == [c + (k + 1) * s1 for c in ctx]
+        assert torch.equal(cpu(w.cache_index), synth.cache_index_for(cpu(w.act_seq), wc["block_table"], s1))
+        # ---- caches: the oracle's rows at cache_index, every other row untouched ------------------------------
+        q_nope, q_rope, q_norm, q_norm_scale, kv_ref, kr_ref, ks_ref = orc.mla_prolog(
+            acts["x"], wc["w_dq"], wc["w_uq_qr"], wc["w_uq_qr_scale"], wc["w_uk"], wc["w_dkv_kr"], wc["gamma_cq"],
+            wc["gamma_ckv"], acts["cos"], acts["sin"], ci, before["kv_cache"], before["kr_cache"], before["k_scale_cache"])
+        _, _, ik_ref, iks_ref, _ = orc.indexer_prolog(
+            acts["x"], q_norm, q_norm_scale, wc["w_qb"], wc["w_qb_scale"], wc["wk"], wc["w_proj"], wc["ln_gamma"],
+            wc["ln_beta"], acts["cos"], acts["sin"], wc["hadamard"], wc["hadamard"], before["idx_k"],
+            before["idx_k_scale"].reshape(-1, 128, 1), ci)
+        kv, kr, ks = cpu(w.kv_cache), cpu(w.kr_cache), cpu(w.k_scale_cache)
+        ik, iks = cpu(w.idx_k), cpu(w.idx_k_scale)
+        rows = torch.zeros(kv.shape[0] * 128, dtype=torch.bool)
+        rows[ci] = True
+        for name, got, ref, old, width in (("kv", kv, kv_ref, before["kv_cache"], 512), ("kr", kr, kr_ref, before["kr_cache"], 64),
+                                           ("ks", ks, ks_ref, before["k_scale_cache"], 4), ("ik", ik, ik_ref, before["idx_k"], 128),
+                                           ("iks", iks, iks_ref.reshape(iks.shape), before["idx_k_scale"], 1)):
+            g2, r2, o2 = got.reshape(-1, width), ref.reshape(-1, width), old.reshape(-1, width)
+            assert torch.equal(g2[~rows], o2[~rows]), name          # no other row is touched
+            assert not torch.equal(g2[rows], o2[rows]), name        # the step's rows were written
+            if got.dtype == torch.int8:
+                assert (g2[rows].int() - r2[rows].int()).abs().max() <= 1, name
+            else:   # the reference's tolerances for these outputs; the rope rows may hold a few last-bit outliers
+                bad = orc.reference_compare_count(g2[rows], r2[rows], 1e-4 if name == "kr" else 2.5e-5, 0.008)
+                assert bad <= (0.02 * g2[rows].numel() if name == "kr" else 0), (name, bad)
+        # ---- queries against the oracle's (the reference's tolerances for the fused operator) -----------------
+        for name, got, ref in (("q_nope", cpu(step.q_nope), q_nope), ("q_rope", cpu(step.q_rope), q_rope)):
+            assert orc.reference_compare_count(got, ref, 0.005, 0.0078125) <= 0.015 * ref.numel(), name
+        # ---- indexer + top-k on the device's own prolog outputs and caches -----------------------------------------
+        ref_idx, ref_scores = orc.lightning_indexer(cpu(step.q_int8), cpu(step.q_scale).reshape(-1, 64), ik,
+                                                    iks.reshape(-1, 128, 1), cpu(step.weights), act, wc["block_table"], 2048,
+                                                    return_scores=True)
+        got_idx = cpu(step.topk_res)
+        for tok in range(t):
+            ok, nd, _ = orc.topk_sets_match(got_idx[tok, 0], ref_idx[tok, 0], ref_scores[tok // s1][tok % s1])
+            assert ok, (k, tok, nd)
+            eff = int(act[tok // s1]) - (s1 - 1 - tok % s1)      # fewer than 2048 keys: all of them, the newest included
+            assert sorted(got_idx[tok, 0, :eff].tolist()) == list(range(eff)) and (got_idx[tok, 0, eff:] == -1).all()
+        # ---- attention on the device's own queries, caches and top-k ------------------------------------------------
+        ref_out = orc.sfa_quant(cpu(step.q_nope).reshape(-1, 512), cpu(step.q_rope).reshape(-1, 64), kv.reshape(-1, 512),
+                                kr.reshape(-1, 64), ks.reshape(-1, 4), got_idx.reshape(-1, 2048), wc["block_table"], act, 128,
+                                576 ** -0.5)
+        _assert_attention_close(cpu(step.out), ref_out)
+
+
+def test_decode_advance_reports_positions_beyond_the_page_table():
+    import pypto_b200
+    from pypto_b200.decode_chain import decode_advance
+    bt = torch.tensor([[3, 1], [0, -1]], dtype=torch.int32, device=DEV)
+    act = torch.tensor([254, 100], dtype=torch.int32, device=DEV)
+    ci = torch.zeros(4, dtype=torch.int64, device=DEV)
+    decode_advance(act, bt, ci, 2)                         # request 0: positions 254, 255 -> page 1 rows 126, 127
+    pypto_b200.check_status()
+    assert act.tolist() == [256, 102] and ci.tolist() == [128 + 126, 128 + 127, 100, 101]
+    decode_advance(act, bt, ci, 2)                         # request 0 runs past its two pages
+    with pytest.raises(RuntimeError, match="status"):
+        pypto_b200.check_status()
+    assert ci.tolist()[:2] == [-1, -1] and ci.tolist()[2:] == [102, 103]
+    act[1] = 127
+    decode_advance(act, bt, ci, 2)                         # request 1 steps onto a page that is not assigned
+    with pytest.raises(RuntimeError, match="status"):
+        pypto_b200.check_status()
+    assert ci.tolist()[2:] == [127, -1]
