@@ -19,7 +19,6 @@ import torch
 
 from . import _lib
 from . import _runtime as rt
-from .mla_prolog_quant_impl import _int8_gemm
 
 Q_LORA_RANK, HEAD_DIM, ROPE_DIM = 1024, 512, 64
 
@@ -50,6 +49,16 @@ class MlaPrologV4Configs:
     t_sub_tile: int = 1
     chunk_size: int = 2
 
+
+
+def _int8_gemm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """int8 [m,k] x int8 [k,n] -> int32 [m', n] with m' >= m (the library kernel wants more than 16 rows)."""
+    m = a.shape[0]
+    if m <= 16:
+        pad = torch.zeros((32, a.shape[1]), dtype=torch.int8, device=a.device)
+        pad[:m] = a
+        a = pad
+    return torch._int_mm(a, b)
 
 def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_sin, wq_b_scale, q_out, kv_out, qr_out,
                   qr_scale_out, attrs=None, configs=None, tile_configs=None):

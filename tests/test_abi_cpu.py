@@ -78,3 +78,13 @@ def test_missing_library_is_an_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.Dsv32Error):
         _lib.load()
+
+
+def test_every_module_of_the_package_imports():
+    """An entry module that cannot be imported would only show on a GPU box otherwise."""
+    import importlib
+    import pkgutil
+    import pypto_b200
+    for m in pkgutil.iter_modules(pypto_b200.__path__):
+        if not m.name.startswith("lib"):   # the shared library sits in the package directory
+            importlib.import_module(f"pypto_b200.{m.name}")
