@@ -344,6 +344,15 @@ typedef struct {
 int dsv32_mla_indexer_prolog(const Dsv32FusedPrologArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Diagnostic with no counterpart in the reference: launches one tiny CTA that waits, for at
+ * most budget_cycles SM clock cycles, on a barrier nothing ever arrives at (no copy or tensor-
+ * core operation is in flight), so that the give-up path of the kernels' bounded waits can be
+ * observed -- status[0] = DSV32_STATUS_TIMEOUT, status[1] = 99 -- without stalling a real
+ * kernel.  The kernels themselves wait for about a second (2e9 cycles) before giving up.
+ * ------------------------------------------------------------------------------------- */
+int dsv32_wait_selftest(uint32_t* status, int64_t budget_cycles, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * Next decode step of a batch, on the device: act_seq[b] += grow, then the cache rows of the
  * step's s1 tokens by the reference's rule for its test data
  * (models/deepseek_v32_exp/deepseekv32_mla_indexer_prolog_quant.py:184-194):

@@ -159,6 +159,7 @@ EXPORTS = {
     "dsv32_mla_prolog_workspace_bytes": (c_size_t, [c_i32]),
     "dsv32_mla_indexer_prolog": (c_i32, [C.POINTER(FusedPrologArgs), c_void_p]),
     "dsv32_decode_advance": (c_i32, [C.POINTER(AdvanceArgs), c_void_p]),
+    "dsv32_wait_selftest": (c_i32, [c_void_p, c_i64, c_void_p]),
 }
 
 ABI_VERSION = 2

@@ -76,6 +76,8 @@ class side_stream:
 
     def __exit__(self, *exc):
         self.ctx.__exit__(*exc)
+        if exc[0] is not None:   # the side branch failed half-way: the caller's stream still waits for what it enqueued
+            self.join()
         return False
 
     def join(self):

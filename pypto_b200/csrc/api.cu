@@ -7,6 +7,7 @@
 #include <cstdlib>
 
 #include "kernels.cuh"
+#include "tc_common.cuh"
 
 namespace dsv32 {
 
@@ -505,6 +506,14 @@ int dsv32_mla_indexer_prolog(const Dsv32FusedPrologArgs* a, void* cuda_stream) {
   int rc = dsv32_mla_prolog(&a->mla, cuda_stream);
   if (rc != DSV32_OK) return rc;
   return dsv32_indexer_prolog(&a->indexer, cuda_stream);
+}
+
+// ---- diagnostic: a bounded device-side wait that runs out ---------------------------------------------------------
+int dsv32_wait_selftest(uint32_t* status, int64_t budget_cycles, void* cuda_stream) {
+  REQUIRE(status != nullptr, "wait selftest: status is NULL");
+  REQUIRE(budget_cycles >= 0 && budget_cycles <= 2000000000ll, "wait selftest: budget of %lld cycles is out of range",
+          static_cast<long long>(budget_cycles));
+  return launch_wait_selftest(status, budget_cycles, static_cast<cudaStream_t>(cuda_stream));
 }
 
 // ---- multi-step decode: next step's sequence lengths and cache rows ----------------------------------------------

@@ -283,6 +283,23 @@ int make_tensor_map_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uin
   return DSV32_OK;
 }
 
+__global__ void __launch_bounds__(32) wait_selftest_kernel(uint32_t* status, long long budget) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  // nobody arrives: the wait gives up after `budget` cycles, records DSV32_STATUS_TIMEOUT (location 99), returns false
+  if (threadIdx.x == 0) (void)mbar_wait(&bar, 0, status, 99, budget);
+}
+
+int launch_wait_selftest(uint32_t* status, long long budget_cycles, cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(status, budget_cycles);
+  count_launch();
+  return check_launch("wait_selftest_kernel");
+}
+
 template <int TOK>
 static int launch_tc(const IndexerParams& p, const CUtensorMap& key_map, dim3 grid, cudaStream_t stream) {
   CUtensorMap q_map;

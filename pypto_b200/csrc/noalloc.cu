@@ -21,7 +21,8 @@ static void* g_scratch_addr[kMaxDevices];  // device address of g_indexer_scratc
 static std::mutex g_scratch_mutex;
 
 // In host code `g_indexer_scratch` is only a handle for the runtime, not a device address; the address
-// that kernels may use is looked up once per device, with that device current.
+// that kernels may use is looked up once per device, with that device current.  "That device" is the CURRENT
+// device of the calling thread, which must be the device `cuda_stream` belongs to.
 static int scratch_for_current_device(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
@@ -30,6 +31,16 @@ static int scratch_for_current_device(void** out) {
     return DSV32_ERR_CUDA;
   }
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] != nullptr) {
+    // A device reset (or a destroyed and re-created primary context) makes the remembered address stale: it is
+    // kept only while the runtime still knows it as device memory of this device.
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, g_scratch_addr[dev]) != cudaSuccess || attr.type != cudaMemoryTypeDevice ||
+        attr.device != dev) {
+      (void)cudaGetLastError();
+      g_scratch_addr[dev] = nullptr;
+    }
+  }
   if (g_scratch_addr[dev] == nullptr) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_indexer_scratch);

@@ -11,9 +11,7 @@ namespace dsv32 {
 // Every wait gives up after kWaitBudgetCycles SM clock cycles (about one second), records
 // DSV32_STATUS_TIMEOUT and returns false; callers then leave their loops and meet at the final barrier.
 constexpr long long kWaitBudgetCycles = 2000000000ll;
-#ifndef DSV32_WAIT_HINT
-#define DSV32_WAIT_HINT 20000u
-#endif
+
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -49,8 +47,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Returns false on timeout (status recorded with `where`).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t where) {
+// Returns false on timeout (status recorded with `where`).  `budget` is in SM clock cycles.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t where,
+                                          long long budget = kWaitBudgetCycles) {
   if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -62,10 +61,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(DSV32_WAIT_HINT)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
         : "memory");
     if (ok) return true;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > budget) {
       report_status(status, DSV32_STATUS_TIMEOUT, where, blockIdx.x);
       return false;
     }
@@ -244,5 +243,8 @@ __device__ __forceinline__ bool elect_one() {
 // 2-D row-major byte tensor [rows, row_bytes], box [box_rows, box_bytes], 128-byte swizzle.
 int make_tensor_map_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                           uint32_t box_bytes);
+// A one-CTA kernel that waits, with the given budget, on a barrier that nothing arrives at (no copy or MMA in
+// flight): the way to see a bounded wait run out -- status word, clean return -- without stalling a real kernel.
+int launch_wait_selftest(uint32_t* status, long long budget_cycles, cudaStream_t stream);
 
 }  // namespace dsv32

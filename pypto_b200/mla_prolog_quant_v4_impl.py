@@ -8,7 +8,9 @@ mla_prolog_v4_in :567-629, mla_prolog_quant_pypto :655-658; compute mla_prolog_v
   kv           = bf16(RMSNorm(x @ wkv) * gamma_ckv), rotary embedding on its last 64 dims   (the new cache row)
 The three projections are library GEMMs (cuBLAS through torch: bf16 operands with fp32 accumulation and fp32 results, which is
 the reference golden's fp32 product of the widened operands up to summation order; int8 with int32 accumulation); everything between them is one fused CUDA kernel per stage.  Weights are
-plain row-major [K, N].  Work is only enqueued on the current CUDA stream.
+plain row-major [K, N].  Work is enqueued on the current CUDA stream and, for the
+independent kv branch, on a second stream of the device that is forked from and joined back into it by events
+(also when the q branch raises).
 """
 from __future__ import annotations
 
@@ -104,14 +106,16 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
             kv_a = rt.gemm_bf16_fp32(token_x, wkv)                               # [t, 512] fp32
             a.kv_a = rt.ptr(kv_a)
             rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 2, rt.stream_ptr(dev)), "mla_prolog_v4 (kv norm + rope)")
-        stream = rt.stream_ptr(dev)
-        q_a = rt.gemm_bf16_fp32(token_x, wq_a)                                   # [t, 1024] fp32
-        a.q_a = rt.ptr(q_a)
-        rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 0, stream), "mla_prolog_v4 (q norm + quant)")
-        q_b = _int8_gemm(qr_out, wq_b)                                    # [>= t, heads * 512] int32
-        a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]
-        rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 1, stream), "mla_prolog_v4 (q dequant + norm + rope)")
-        fork.join()
+        try:   # whatever happens on this branch, the caller's stream must wait for the side branch
+            stream = rt.stream_ptr(dev)
+            q_a = rt.gemm_bf16_fp32(token_x, wq_a)                                   # [t, 1024] fp32
+            a.q_a = rt.ptr(q_a)
+            rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 0, stream), "mla_prolog_v4 (q norm + quant)")
+            q_b = _int8_gemm(qr_out, wq_b)                                    # [>= t, heads * 512] int32
+            a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]
+            rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 1, stream), "mla_prolog_v4 (q dequant + norm + rope)")
+        finally:
+            fork.join()
     return None
 
 

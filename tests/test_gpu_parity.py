@@ -266,6 +266,7 @@ def _assert_attention_close(out, ref, strict_frac=0.15):
     err = (o - r).abs()
     assert torch.allclose(o, r, rtol=1e-2, atol=1e-2), f"max-abs {err.max():.4g} mean-abs {err.mean():.4g}"
     strict = orc.reference_compare_count(out, ref, 1e-4, 5e-3)
+    print(f"[attention] strict-rule outliers {strict / max(out.numel(), 1):.4f} of {out.numel()} (bound {strict_frac})")
     assert strict <= strict_frac * out.numel(), f"{strict} of {out.numel()} outside the reference's own last-bit rule"
     assert err.mean() <= 1e-2 * r.abs().mean() + 1e-6, f"mean-abs {err.mean():.4g} vs mean |ref| {r.abs().mean():.4g}"
     return float(err.max()), float(err.mean())
@@ -1523,3 +1524,26 @@ def test_decode_advance_reports_positions_beyond_the_page_table():
     with pytest.raises(RuntimeError, match="status"):
         pypto_b200.check_status()
     assert ci.tolist()[2:] == [127, -1]
+
+
+def test_bounded_wait_runs_out_with_a_status_word_and_a_clean_return():
+    """A device-side wait whose barrier never completes gives up after its cycle budget: status TIMEOUT with the
+    wait's location id, the kernel returns, the context stays usable (nothing asynchronous is in flight in this
+    diagnostic kernel; the production kernels use the same wait with a budget of about a second)."""
+    import ctypes as C
+    import time
+    import pypto_b200
+    from pypto_b200 import _lib, _runtime as rt
+    lib = _lib.load()
+    dev = torch.device(DEV)
+    pypto_b200.check_status(dev)
+    st = rt.status_word(dev)
+    t0 = time.perf_counter()
+    _lib.check(lib.dsv32_wait_selftest(C.c_void_p(st.data_ptr()), 200000, rt.stream_ptr(dev)), "wait selftest")
+    with pytest.raises(RuntimeError, match="timed out"):
+        pypto_b200.check_status(dev)
+    assert time.perf_counter() - t0 < 5.0
+    pypto_b200.check_status(dev)                          # cleared; the device still works
+    x = torch.arange(10, device=DEV)
+    assert int(x.sum()) == 45
+    assert lib.dsv32_wait_selftest(None, 10, None) == -1 and lib.dsv32_wait_selftest(C.c_void_p(st.data_ptr()), -1, None) == -1

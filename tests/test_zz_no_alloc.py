@@ -43,11 +43,16 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
         ref_idx = torch.zeros((t, 1, 2048), dtype=torch.int32, device=DEV)
         ref_sc = torch.zeros((t, 2048), dtype=torch.float32, device=DEV)
         _lib.check(lib.dsv32_indexer_topk(C.byref(_args(_lib, d, ref_idx, ref_sc, ws)), stream), "regular")
-        for _ in range(2):  # two calls in a row share the built-in scratch
+        for call in range(2):  # two calls in a row share the built-in scratch
             idx = torch.full((t, 1, 2048), -7, dtype=torch.int32, device=DEV)
             sc = torch.zeros((t, 2048), dtype=torch.float32, device=DEV)
-            _lib.check(lib.dsv32_indexer_topk_noalloc(C.byref(_args(_lib, d, idx, sc, None)), stream), "noalloc")
+            args = _args(_lib, d, idx, sc, None)
             torch.cuda.synchronize()
+            free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+            _lib.check(lib.dsv32_indexer_topk_noalloc(C.byref(args), stream), "noalloc")
+            torch.cuda.synchronize()
+            if seed != 31 or call > 0:   # what the entry point is for: after the device's first call, no allocation
+                assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == held0
             assert torch.equal(idx, ref_idx)
             assert torch.equal(sc, ref_sc)
 
