@@ -68,41 +68,6 @@ struct StPrefetchT {
   bool valid;
 };
 
-// Two fp32 operations per instruction (sm_100 packed arithmetic): the int8 -> float -> scaled path of the
-// dequantisation is issue-bound, so halving its instruction count is what counts.
-__device__ __forceinline__ uint64_t f2_pack(uint32_t lo, uint32_t hi) {
-  uint64_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  uint32_t l, h;
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(l), "=r"(h) : "l"(v));
-  lo = __uint_as_float(l);
-  hi = __uint_as_float(h);
-}
-__device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {  // {lo, hi} -> bf16 pair, round to nearest even
-  uint32_t lo, hi, d;
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
-  return d;
-}
-
 // 16 int8 -> 16 bf16 = bf16_rn( float(int8) * scale ), bit for bit as the golden: float(int8) is built without
 // the conversion pipe -- (2^23 + (x ^ 0x80)) read as a float, minus (2^23 + 128), is exactly x -- and the product
 // is one fp32 rounding followed by the bf16 rounding.

@@ -7,6 +7,43 @@
 
 namespace dsv32 {
 
+// ---- packed fp32 arithmetic ---------------------------------------------------------------------------------
+// Two fp32 operations per instruction (sm_100 packed arithmetic) for the issue-bound epilogues and the
+// dequantisation: a pair of floats travels in one 64-bit register.
+__device__ __forceinline__ uint64_t f2_pack(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  uint32_t l, h;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(l), "=r"(h) : "l"(v));
+  lo = __uint_as_float(l);
+  hi = __uint_as_float(h);
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {  // {lo, hi} -> bf16 pair, round to nearest even
+  uint32_t lo, hi, d;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+  return d;
+}
+
+
 // ---- bounded waits ---------------------------------------------------------------------------------
 // Every wait gives up after kWaitBudgetCycles SM clock cycles (about one second), records
 // DSV32_STATUS_TIMEOUT and returns false; callers then leave their loops and meet at the final barrier.
