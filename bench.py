@@ -17,7 +17,8 @@ config 4            ragged production decode, batch 256, context lengths log-uni
 One step = one pass of the chain over the batch.  The metric is decode tokens/s (whole job, all ranks).  Every
 figure is the median over rounds of exactly K steps, each round bracketed by a barrier and a device
 synchronisation, timed with CUDA events, maximum over ranks.  Prints ONE JSON line on rank 0.
-`--workload v4` times the DeepSeek-V4 operators instead (one JSON line per operator, N = 1).
+`--workload v4` times the DeepSeek-V4 operators instead (one JSON line per operator, N = 1); `--workload mla` the
+MLA prolog and the fused MLA + indexer prolog.
 """
 import argparse
 import json
@@ -395,12 +396,13 @@ def host_link_probe(dev, h2d_bytes, d2h_bytes, timer, iters=20):
 
 
 # ---- config 2 / 4: the decode chain, requests sharded over ranks ------------------------------------------------------
-def build_steps(ctx_list, s1, seed, dev):
+def build_steps(ctx_list, s1, seed, dev, kv_splits=0):
     from pypto_b200 import synth
     from pypto_b200.decode_chain import SparseDecodeStep
     w = synth.make_decode_workload(ctx_list, s1, seed, dev)
     a = SparseDecodeStep(w)
     b = SparseDecodeStep(w, acts=synth.make_step_activations(w, seed + 7919))
+    a.kv_splits = b.kv_splits = kv_splits
     return w, a, b
 
 
@@ -416,7 +418,7 @@ def run_chain(args, rank, world, local_rank):
     timer = Timer(dev, world)
     ctx_list = requests_of_rank(args, rank, world)
     tokens_rank = len(ctx_list) * args.s1
-    w, step_a, step_b = build_steps(ctx_list, args.s1, 1002 + rank, dev)
+    w, step_a, step_b = build_steps(ctx_list, args.s1, 1002 + rank, dev, args.kv_splits)
     steps = (step_a, step_b)
     with numa_local(local_rank) as nl:
         h2d, d2h = step_a.enable_host_io()
@@ -442,7 +444,7 @@ def run_chain(args, rank, world, local_rank):
     # warm-up (at least 3 steps; kept going for ~1 s so that the clock sampler sees the GPU under this load)
     t_warm = time.perf_counter()
     n_warm = 0
-    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < 1.0:
+    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < (1.0 if args.min_timed_ms > 0 else 0.0):
         steps[n_warm & 1].step()
         n_warm += 1
         if n_warm % 8 == 0:
@@ -454,7 +456,7 @@ def run_chain(args, rank, world, local_rank):
     whole = [s.capture(per_stage=False)[0] for s in steps]     # through the library's launch counter
     for i in range(4):
         whole[i & 1].replay()
-    ms_rounds = timer.rounds(lambda i: whole[i & 1].replay(), args.steps)
+    ms_rounds = timer.rounds(lambda i: whole[i & 1].replay(), args.steps, min_total_ms=args.min_timed_ms)
     dev_stats = spread(ms_rounds, args.steps)
     # stage times: the three stages of step A replayed from their own graphs, an event between them
     stage_graphs = step_a.capture(per_stage=True)
@@ -472,7 +474,7 @@ def run_chain(args, rank, world, local_rank):
     # end-to-end: pinned host activations in, attention output back, every step -- on one stream ...
     for i in range(2):
         steps[i].step_from_host()
-    ser_rounds = timer.rounds(lambda i: steps[i & 1].step_from_host(), args.steps, min_total_ms=200.0)
+    ser_rounds = timer.rounds(lambda i: steps[i & 1].step_from_host(), args.steps, min_total_ms=min(200.0, args.min_timed_ms))
     # ... and with the copies of steps k+1 / k-1 overlapping the compute of step k (three streams)
     with numa_local(local_rank):
         pipe = HostPipelinedDecode(step_a, use_graphs=True)
@@ -486,7 +488,7 @@ def run_chain(args, rank, world, local_rank):
         if i == args.steps - 1:
             pipe.drain()
 
-    e2e_rounds = timer.rounds(e2e_round, args.steps)
+    e2e_rounds = timer.rounds(e2e_round, args.steps, min_total_ms=args.min_timed_ms)
     e2e_stats = spread(e2e_rounds, args.steps)
     with numa_local(local_rank):
         link_s = host_link_probe(dev, h2d, d2h, timer)
@@ -659,7 +661,7 @@ def run_config3(args, rank, world, local_rank):
         step(i, record=False)
     launches_per_step = (pypto_b200.launch_count() - launches0) // n_warm
     pypto_b200.check_status(dev)
-    ms_rounds = timer.rounds(step, args.steps, min_total_ms=500.0, max_rounds=20, after_round=flush.zero_)
+    ms_rounds = timer.rounds(step, args.steps, min_total_ms=args.min_timed_ms, max_rounds=20, after_round=flush.zero_)
     stats = spread(ms_rounds, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     pypto_b200.check_status(dev)
@@ -823,6 +825,53 @@ def run_v4(args):
         _emit_json(r)
 
 
+def run_mla(args):
+    """The fused MLA + indexer prolog (mla_indexer_prolog_quant_d) and the MLA prolog alone at `batch * s1` tokens,
+    each replayed from a CUDA graph with a buffer larger than L2 written between replays (85 MB + 15 MB of weights
+    would otherwise stay in L2); median of CUDA-event durations, one JSON line."""
+    from pypto_b200 import check_status, synth
+    from pypto_b200.decode_chain import FullDecodeStep
+    from pypto_b200 import mla_prolog_quant_impl as mlp
+    dev = "cuda"
+    t = args.batch * args.s1
+    w = synth.make_full_decode_workload([4096] * args.batch, args.s1, 0, 7, dev)
+    step = FullDecodeStep(w)
+    step.set_inputs(**synth.make_full_step_activations(t, 8, dev))
+    q_norm = torch.empty((t, 1536), dtype=torch.int8, device=dev)
+    q_norm_scale = torch.empty((t, 1), dtype=torch.float32, device=dev)
+
+    def mla_only():
+        mlp.mla_prolog_quant_d(step.x, w.w_dq, w.w_uq_qr, w.w_uq_qr_scale, w.w_uk, w.w_dkv_kr, w.gamma_cq, w.gamma_ckv,
+                               step.cos, step.sin, w.cache_index, w.kv_cache, w.kr_cache, w.k_scale_cache, q_norm,
+                               q_norm_scale, step.q_nope, step.q_rope, w.kv_cache, w.kr_cache, w.k_scale_cache, 1e-6, 1e-6,
+                               "PA_BSND", mlp.MlaTileConfig(), mlp.RopeTileShapeConfig())
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, fn in (("mla_prolog_quant_d", mla_only), ("mla_indexer_prolog_quant_d", step.prolog)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        times = []
+        for _ in range(15):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        out[name] = round(statistics.median(times) * 1000.0, 1)
+    check_status()
+    weights = 7168 * 1536 * 2 + 1536 * 24576 + 128 * 128 * 512 * 2 + 7168 * 576 * 2
+    _emit_json({"workload": "mla", "tokens": t, "us": out, "mla_weight_bytes": weights,
+                "mla_weight_stream_gbs": weights / (out["mla_prolog_quant_d"] * 1e-6) / 1e9,
+                "timing": "CUDA graph replays, L2 flushed between replays, median of 15 CUDA-event durations"})
+
+
 _JSON_FD = None
 
 
@@ -854,7 +903,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4])
-    ap.add_argument("--workload", default="chain", choices=["chain", "v4"])
+    ap.add_argument("--workload", default="chain", choices=["chain", "v4", "mla"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--s1", type=int, default=None)
@@ -863,6 +912,9 @@ def main():
     ap.add_argument("--cpu-requests", type=int, default=None, help="requests (config 3: query tokens) in the bounded CPU sample")
     ap.add_argument("--cpu-passes", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-timed-ms", type=float, default=500.0, help="keep timing rounds of --steps until this much "
+                    "timed region has accumulated (profiling runs pass 0: three rounds)")
+    ap.add_argument("--kv-splits", type=int, default=0, help="fix the key splits of the attention kernel (0: automatic)")
     args = ap.parse_args()
     defaults = {2: (64, 65536, 2), 3: (1, 131072, 4096), 4: (256, None, 2)}[args.config]
     args.batch = args.batch if args.batch is not None else defaults[0]
@@ -884,11 +936,11 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the decode chain has no CPU fallback")
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (one process per GPU)")
-    if args.workload == "v4":
+    if args.workload in ("v4", "mla"):
         if rank == 0:
             if args.batch == 256:
                 args.batch = 64
-            run_v4(args)
+            (run_v4 if args.workload == "v4" else run_mla)(args)
         return
     if args.config == 3:
         run_config3(args, rank, world, local_rank)

@@ -17,7 +17,7 @@ from . import _runtime as rt
 from .lightning_indexer_prolog_quant_impl import (IndexerPrologQuantAttr, IndexerPrologQuantConfigs,
                                                   lightning_indexer_prolog_quant)
 from .lightning_indexer_quant_impl import LightningIndexerConfigs, lightning_indexer_decode
-from .sparse_flash_attention_quant_impl import SaTileShapeConfig, sparse_flash_attention_quant_d
+from .sparse_flash_attention_quant_impl import SaTileShapeConfig, _sfa, sparse_flash_attention_quant_d
 
 STEP_INPUTS = ("x", "q_norm", "q_norm_scale", "cos", "sin", "cache_index", "q_nope", "q_rope")
 
@@ -57,6 +57,7 @@ class SparseDecodeStep:
         self.out = torch.empty((w.b, w.s1, nq, 512), dtype=torch.bfloat16, device=dev)
         self.idx_k_scale4 = w.idx_k_scale.reshape(w.idx_k_scale.shape[0], 128, 1, 1)
         self.softmax_scale = 576 ** -0.5
+        self.kv_splits = 0   # key splits of the attention kernel: 0 = the library's choice (profiling may fix it)
         self._cfg = (IndexerPrologQuantConfigs(), IndexerPrologQuantAttr(eps=1e-6), LightningIndexerConfigs(),
                      SaTileShapeConfig())
         acts = acts if acts is not None else {k: getattr(w, k) for k in STEP_INPUTS}
@@ -92,9 +93,10 @@ class SparseDecodeStep:
 
     def attention(self):
         w, d = self.w, self._dev_in
-        sparse_flash_attention_quant_d(d["q_nope"], d["q_rope"], w.k_nope, w.k_rope, w.k_scales,
-                                       self.topk_res.reshape(-1, self.topk), w.block_table, w.act_seq, self.out,
-                                       self.nq, 1, self.softmax_scale, self.topk, 128, w.max_blocks, self._cfg[3])
+        # (the operator entry sparse_flash_attention_quant_d with the key split of the C ABI exposed: 0 = automatic)
+        _sfa(d["q_nope"], d["q_rope"], w.k_nope, w.k_rope, w.k_scales, self.topk_res.reshape(-1, self.topk),
+             w.block_table, w.act_seq, self.out, self.nq, 1, self.softmax_scale, self.topk, 128, w.max_blocks,
+             self._cfg[3], kv_splits=self.kv_splits)
 
     def step(self):
         """Device-resident step: prolog -> indexer + top-k -> attention on the current stream."""
