@@ -287,6 +287,61 @@ int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* args, void* cuda_stream);
 size_t dsv32_prolog_v4_workspace_bytes(int32_t t, int32_t h);
 
 /* ---------------------------------------------------------------------------------------
+ * Page-grouped lightning-indexer prolog with 8-bit float formats.  Replaces
+ * lightning_indexer_prolog_quant of python/tests/st/operator/pg/lightning_indexer_prolog_quant_mxfp8_impl.py:230-401
+ * (format DSV32_PG_FORMAT_MXFP8: float8 E4M3 codes, one E8M0 scale per 32 reduction elements of q_norm and of
+ * w_qb) and of lightning_indexer_prolog_quant_hif8_impl.py:230-406 (format DSV32_PG_FORMAT_HIF8: HiF8 codes, one
+ * fp32 scale per token and per output column):
+ *   q       = quant( bf16( rope_first64( bf16(q_norm . w_qb, scales applied) ) . hadamard_q ) ) per (token, head)
+ *   k       = quant( bf16( rope_first64( bf16( rmsnorm( bf16(x . wk) ) * gamma_k ) ) . hadamard_k ) ) per token,
+ *             scattered with its scale into the caches at rows k_cache_index / k_scale_cache_index
+ *   weights = bf16( bf16( bf16(x . w_proj) * heads^-0.5 ) * 128^-0.5 )
+ *   quant(v) = 8-bit codes of v / scale with scale = amax(|v|) * fl(1 / max_code), max_code 448 (E4M3,
+ *   saturating) or 32768 (HiF8: nearest value, ties away from zero, saturating)
+ * The caches are page-grouped: row r lives in page r / block_size at slot r % block_size, pages
+ * k_block_stride (bytes) apart -- a strided view into a buffer that other caches share.  head_dim is 128,
+ * the rotary part the first 64 dims; q_lora is a multiple of 256, h of 512, heads <= 128.
+ * ------------------------------------------------------------------------------------- */
+#define DSV32_PG_FORMAT_MXFP8 0
+#define DSV32_PG_FORMAT_HIF8 1
+typedef struct {
+  const void* x;                    /* bf16 [t, h]                                                  */
+  const uint8_t* q_norm;            /* codes [t, q_lora]                                            */
+  const void* q_norm_scale;         /* MXFP8: E8M0 [t, q_lora / 32]; HiF8: fp32 [t]                 */
+  const uint8_t* w_qb;              /* codes [q_lora, heads * 128]                                  */
+  const void* w_qb_scale;           /* MXFP8: E8M0 [q_lora / 64, heads * 128, 2]; HiF8: fp32 [heads * 128] */
+  const void* wk;                   /* bf16 [h, 128]                                                */
+  const void* w_proj;               /* bf16 [h, heads]                                              */
+  const void* gamma_k;              /* bf16 [128]                                                   */
+  const void* cos_idx_rope;         /* bf16 [t, 64]                                                 */
+  const void* sin_idx_rope;         /* bf16 [t, 64]                                                 */
+  const void* hadamard_q;           /* bf16 [128, 128]                                              */
+  const void* hadamard_k;           /* bf16 [128, 128]                                              */
+  const int64_t* k_cache_index;     /* int64 [t]                                                    */
+  const int64_t* k_scale_cache_index; /* int64 [t]                                                  */
+  uint8_t* q_quant;                 /* out codes [t, heads, 128]                                    */
+  float* q_scale;                   /* out fp32 [t, heads]                                          */
+  uint8_t* k_cache;                 /* in/out codes, page-grouped (see above)                       */
+  float* k_scale_cache;             /* in/out fp32, page-grouped                                    */
+  void* weights;                    /* out bf16 [t, heads]                                          */
+  void* workspace;                  /* >= dsv32_pg_indexer_prolog_workspace_bytes(...), 256-byte aligned */
+  size_t workspace_bytes;
+  uint32_t* status;
+  int64_t cache_rows;               /* pages * block_size                                           */
+  int64_t k_block_stride;           /* bytes between pages of k_cache (>= block_size * 128)         */
+  int64_t k_scale_block_stride;     /* bytes between pages of k_scale_cache (>= block_size * 4)     */
+  int32_t t, h, q_lora, heads, block_size, format;
+  float eps;                        /* RMSNorm epsilon (the operator uses 1e-6)                     */
+} Dsv32PgPrologArgs;
+
+int dsv32_pg_indexer_prolog(const Dsv32PgPrologArgs* args, void* cuda_stream);
+size_t dsv32_pg_indexer_prolog_workspace_bytes(int32_t t, int32_t h, int32_t q_lora, int32_t heads);
+
+/* Array conversions of the HiF8 format (device pointers; n elements):
+ * direction 0: fp32 -> codes (nearest value, ties away from zero, saturating at 2^15), 1: codes -> fp32. */
+int dsv32_hif8_convert(int32_t direction, const void* in, void* out, int64_t n, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * MLA prolog (quant).  Replaces mla_prolog_quant_d / _p
  * (models/deepseek_v32_exp/mla_prolog_quant_impl.py:848-875 / 751-778) and is the MLA half of
  * the fused entry below:

@@ -83,6 +83,19 @@ class PrologV4Args(C.Structure):
     ]
 
 
+class PgPrologArgs(C.Structure):
+    _fields_ = [
+        ("x", c_void_p), ("q_norm", c_void_p), ("q_norm_scale", c_void_p), ("w_qb", c_void_p), ("w_qb_scale", c_void_p),
+        ("wk", c_void_p), ("w_proj", c_void_p), ("gamma_k", c_void_p), ("cos_idx_rope", c_void_p),
+        ("sin_idx_rope", c_void_p), ("hadamard_q", c_void_p), ("hadamard_k", c_void_p), ("k_cache_index", c_void_p),
+        ("k_scale_cache_index", c_void_p), ("q_quant", c_void_p), ("q_scale", c_void_p), ("k_cache", c_void_p),
+        ("k_scale_cache", c_void_p), ("weights", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("status", c_void_p), ("cache_rows", c_i64), ("k_block_stride", c_i64), ("k_scale_block_stride", c_i64),
+        ("t", c_i32), ("h", c_i32), ("q_lora", c_i32), ("heads", c_i32), ("block_size", c_i32), ("format", c_i32),
+        ("eps", C.c_float),
+    ]
+
+
 class IndexerArgs(C.Structure):
     _fields_ = [
         ("idx_query", c_void_p), ("idx_query_scale", c_void_p), ("idx_key_cache", c_void_p),
@@ -160,6 +173,9 @@ EXPORTS = {
     "dsv32_mla_indexer_prolog": (c_i32, [C.POINTER(FusedPrologArgs), c_void_p]),
     "dsv32_decode_advance": (c_i32, [C.POINTER(AdvanceArgs), c_void_p]),
     "dsv32_wait_selftest": (c_i32, [c_void_p, c_i64, c_void_p]),
+    "dsv32_pg_indexer_prolog": (c_i32, [C.POINTER(PgPrologArgs), c_void_p]),
+    "dsv32_pg_indexer_prolog_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
+    "dsv32_hif8_convert": (c_i32, [c_i32, c_void_p, c_void_p, c_i64, c_void_p]),
 }
 
 ABI_VERSION = 2

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libdsv32_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
-SOURCES = ["api.cu", "topk.cu", "indexer_tc.cu", "sfa_tc.cu", "sfa_combine.cu", "prolog.cu", "prolog_tc.cu", "mla_prolog.cu", "mla_prolog_tc.cu",
+SOURCES = ["api.cu", "topk.cu", "indexer_tc.cu", "sfa_tc.cu", "sfa_combine.cu", "prolog.cu", "prolog_tc.cu", "mla_prolog.cu", "mla_prolog_tc.cu", "pg_prolog.cu",
            "mla_prolog_v4.cu", "hc_pre.cu", "compressor.cu", "decode_advance.cu", "noalloc.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -390,6 +390,82 @@ int dsv32_indexer_prolog_v4(const Dsv32PrologV4Args* a, void* cuda_stream) {
   return launch_prolog_v4(p, a->h, w_scale, static_cast<cudaStream_t>(cuda_stream));
 }
 
+size_t dsv32_pg_indexer_prolog_workspace_bytes(int32_t t, int32_t h, int32_t q_lora, int32_t heads) {
+  return pg_prolog_workspace_bytes(t, h, q_lora, heads);
+}
+
+int dsv32_pg_indexer_prolog(const Dsv32PgPrologArgs* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "pg prolog: args is NULL");
+  REQUIRE(a->t >= 0, "pg prolog: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  REQUIRE(a->format == DSV32_PG_FORMAT_MXFP8 || a->format == DSV32_PG_FORMAT_HIF8, "pg prolog: unknown format %d", a->format);
+  REQUIRE(a->h >= 512 && a->h % 512 == 0, "pg prolog: h=%d must be a positive multiple of 512", a->h);
+  REQUIRE(a->q_lora >= 256 && a->q_lora % 256 == 0, "pg prolog: q_lora=%d must be a positive multiple of 256", a->q_lora);
+  REQUIRE(a->heads >= 1 && a->heads <= 128, "pg prolog: heads=%d must be in [1, 128]", a->heads);
+  REQUIRE(a->block_size >= 1 && a->cache_rows >= 0 && a->cache_rows % a->block_size == 0,
+          "pg prolog: cache_rows=%lld must be a whole number of pages of %d rows", static_cast<long long>(a->cache_rows),
+          a->block_size);
+  REQUIRE(a->k_block_stride >= static_cast<int64_t>(a->block_size) * 128 &&
+              a->k_scale_block_stride >= static_cast<int64_t>(a->block_size) * 4 && a->k_scale_block_stride % 4 == 0,
+          "pg prolog: page strides %lld / %lld are smaller than a page (or the scale stride is not a multiple of 4)",
+          static_cast<long long>(a->k_block_stride), static_cast<long long>(a->k_scale_block_stride));
+  REQUIRE(a->x && a->q_norm && a->q_norm_scale && a->w_qb && a->w_qb_scale && a->wk && a->w_proj && a->gamma_k &&
+              a->cos_idx_rope && a->sin_idx_rope && a->hadamard_q && a->hadamard_k && a->k_cache_index &&
+              a->k_scale_cache_index && a->q_quant && a->q_scale && a->k_cache && a->k_scale_cache && a->weights,
+          "pg prolog: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->x) % 16 == 0 && reinterpret_cast<uintptr_t>(a->q_norm) % 8 == 0 &&
+              reinterpret_cast<uintptr_t>(a->w_qb) % 8 == 0 && reinterpret_cast<uintptr_t>(a->k_scale_cache) % 4 == 0,
+          "pg prolog: x must be 16-byte aligned, q_norm / w_qb 8-byte aligned, k_scale_cache 4-byte aligned");
+  const size_t need = pg_prolog_workspace_bytes(a->t, a->h, a->q_lora, a->heads);
+  if (a->workspace == nullptr || a->workspace_bytes < need || reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) {
+    set_error("pg prolog: workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
+  PgPrologParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.q_norm = a->q_norm;
+  p.w_qb = a->w_qb;
+  if (a->format == DSV32_PG_FORMAT_MXFP8) {
+    p.q_norm_scale_e8 = static_cast<const uint8_t*>(a->q_norm_scale);
+    p.w_qb_scale_e8 = static_cast<const uint8_t*>(a->w_qb_scale);
+  } else {
+    p.q_norm_scale_f32 = static_cast<const float*>(a->q_norm_scale);
+    p.w_qb_scale_f32 = static_cast<const float*>(a->w_qb_scale);
+  }
+  p.wk = static_cast<const __nv_bfloat16*>(a->wk);
+  p.w_proj = static_cast<const __nv_bfloat16*>(a->w_proj);
+  p.gamma_k = static_cast<const __nv_bfloat16*>(a->gamma_k);
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos_idx_rope);
+  p.sin = static_cast<const __nv_bfloat16*>(a->sin_idx_rope);
+  p.hadamard_q = static_cast<const __nv_bfloat16*>(a->hadamard_q);
+  p.hadamard_k = static_cast<const __nv_bfloat16*>(a->hadamard_k);
+  p.k_cache_index = reinterpret_cast<const long long*>(a->k_cache_index);
+  p.k_scale_cache_index = reinterpret_cast<const long long*>(a->k_scale_cache_index);
+  p.q_out = a->q_quant;
+  p.q_scale_out = a->q_scale;
+  p.k_cache = a->k_cache;
+  p.k_scale_cache = a->k_scale_cache;
+  p.weights_out = static_cast<__nv_bfloat16*>(a->weights);
+  p.status = a->status;
+  p.cache_rows = a->cache_rows;
+  p.k_block_stride = a->k_block_stride;
+  p.k_scale_block_stride = a->k_scale_block_stride;
+  p.t = a->t; p.h = a->h; p.q_lora = a->q_lora; p.heads = a->heads; p.n = a->heads * 128;
+  p.block_size = a->block_size; p.format = a->format;
+  p.eps = a->eps;
+  p.heads_rsqrt = static_cast<float>(1.0 / sqrt(static_cast<double>(a->heads)));
+  return launch_pg_prolog(p, a->workspace, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int dsv32_hif8_convert(int32_t direction, const void* in, void* out, int64_t n, void* cuda_stream) {
+  REQUIRE(direction == 0 || direction == 1, "hif8 convert: direction %d is neither 0 (encode) nor 1 (decode)", direction);
+  REQUIRE(n >= 0, "hif8 convert: bad n=%lld", static_cast<long long>(n));
+  if (n == 0) return DSV32_OK;
+  REQUIRE(in != nullptr && out != nullptr, "hif8 convert: NULL pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(direction == 0 ? in : out) % 4 == 0, "hif8 convert: the fp32 array must be 4-byte aligned");
+  return launch_hif8_convert(direction, in, out, n, static_cast<cudaStream_t>(cuda_stream));
+}
+
 size_t dsv32_prolog_workspace_bytes(int32_t t) { return t > 0 ? align_up(prolog_workspace_bytes(t), 256) : 0; }
 
 int dsv32_indexer_prolog(const Dsv32PrologArgs* a, void* cuda_stream) {

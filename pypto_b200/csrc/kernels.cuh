@@ -158,7 +158,42 @@ struct MlaParams {
   float eps_cq, eps_ckv;
 };
 int launch_mla_prolog(const MlaParams& p, cudaStream_t stream);
+// bf16 tcgen05 GEMM as a building block (mla_prolog_tc.cu): fp32 partial sums, one [t, ldc] slab per reduction split
+int launch_bf16_gemm_partial(const __nv_bfloat16* a, int t, int k, const __nv_bfloat16* b, int b_cols, int n_tiles,
+                             int splits, float* partial, int ldc, uint32_t* status, cudaStream_t stream);
 size_t mla_prolog_workspace_bytes(int t);
+
+// Page-grouped indexer prolog with 8-bit float formats (pg_prolog.cu)
+struct PgPrologParams {
+  const __nv_bfloat16* x;              // [t, h]
+  const uint8_t* q_norm;               // [t, q_lora] codes
+  const uint8_t* q_norm_scale_e8;      // MXFP8: E8M0 [t, q_lora / 32]
+  const float* q_norm_scale_f32;       // HiF8: [t]
+  const uint8_t* w_qb;                 // [q_lora, n] codes
+  const uint8_t* w_qb_scale_e8;        // MXFP8: E8M0 [q_lora / 64, n, 2]
+  const float* w_qb_scale_f32;         // HiF8: [n]
+  const __nv_bfloat16* wk;             // [h, 128]
+  const __nv_bfloat16* w_proj;         // [h, heads]
+  const __nv_bfloat16* gamma_k;        // [128]
+  const __nv_bfloat16* cos;            // [t, 64]
+  const __nv_bfloat16* sin;
+  const __nv_bfloat16* hadamard_q;     // [128, 128]
+  const __nv_bfloat16* hadamard_k;
+  const long long* k_cache_index;      // [t]
+  const long long* k_scale_cache_index;
+  uint8_t* q_out;                      // [t, heads, 128] codes
+  float* q_scale_out;                  // [t, heads]
+  uint8_t* k_cache;                    // page p, slot s, dim d at p * k_block_stride + s * 128 + d
+  float* k_scale_cache;                // page p, slot s at byte p * k_scale_block_stride + 4 s
+  __nv_bfloat16* weights_out;          // [t, heads]
+  uint32_t* status;
+  long long cache_rows, k_block_stride, k_scale_block_stride;
+  int t, h, q_lora, heads, n, block_size, format;
+  float eps, heads_rsqrt;
+};
+int launch_pg_prolog(const PgPrologParams& p, void* workspace, cudaStream_t stream);
+size_t pg_prolog_workspace_bytes(int t, int h, int q_lora, int heads);
+int launch_hif8_convert(int direction, const void* in, void* out, long long n, cudaStream_t stream);
 
 struct MlaV4StageParams {
   // quant != 0: the quantised operator (fp32 / int32 GEMM results, int8 qr); 0: the bf16 operator (bf16 throughout)

@@ -35,6 +35,9 @@ struct MlaGemmParams {
   __nv_bfloat16* q_nope;           // kUk out: [t, 128, 512]
   uint32_t* status;
   int t;
+  // kXproj: reduction chunks (of 64) per CTA, row stride of a partial slab in floats, and the first column tile
+  // that reads the second weight matrix
+  int k_chunks, ldc, tile_switch;
 };
 
 template <int kKind>
@@ -83,8 +86,8 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
   // reduction chunks of this CTA
   int c_begin = 0, nchunks = Sh::kChunksTotal;
   if constexpr (kKind == kXproj) {
-    c_begin = split * (Sh::kChunksTotal / kMlaXSplits);
-    nchunks = Sh::kChunksTotal / kMlaXSplits;
+    c_begin = split * p.k_chunks;
+    nchunks = p.k_chunks;
   }
 
   if (warp == 0) {
@@ -124,8 +127,8 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
           tma_load_2d(st, &a_map, k0 * 2, t0, &full_bar[s]);
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            if (tile < kMlaXTilesQ) tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, tile * 256 + j * 128, k0, &full_bar[s]);
-            else tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map1, (tile - kMlaXTilesQ) * 256 + j * 128, k0, &full_bar[s]);
+            if (tile < p.tile_switch) tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, tile * 256 + j * 128, k0, &full_bar[s]);
+            else tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map1, (tile - p.tile_switch) * 256 + j * 128, k0, &full_bar[s]);
           }
         } else if constexpr (kKind == kQb) {
           tma_load_2d(st, &a_map, k0, t0, &full_bar[s]);
@@ -184,7 +187,7 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
     if (__all_sync(0xffffffffu, mbar_wait(d_bar, 0, p.status, 62))) {
       tc_fence_after();
       if constexpr (kKind == kXproj) {
-        float* prow = p.partial + (static_cast<size_t>(split) * p.t + tk) * kMlaXCols + tile * 128;
+        float* prow = p.partial + (static_cast<size_t>(split) * p.t + tk) * p.ldc + tile * 128;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
@@ -361,6 +364,9 @@ int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
   gp.q_nope = p.q_nope;
   gp.status = p.status;
   gp.t = p.t;
+  gp.k_chunks = GemmShape<kXproj>::kChunksTotal / kMlaXSplits;
+  gp.ldc = kMlaXCols;
+  gp.tile_switch = kMlaXTilesQ;
 
   rc = launch_gemm<kXproj>(x_map, wdq_map, wkv_map, gp, dim3(kMlaXTiles, kMlaXSplits, tiles), stream,
                            "mla_gemm_tc_kernel (x projections)");
@@ -389,6 +395,31 @@ int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
   if (rc != DSV32_OK) return rc;
   return launch_gemm<kUk>(ni_map, wuk_map, wuk_map, gp, dim3(kMlaHeads, 1, tiles), stream,
                           "mla_gemm_tc_kernel (q_nope . w_uk)");
+}
+
+// The same bf16 kernel as a building block: fp32 partial sums, one [t, ldc] slab per reduction split, of
+// A[t, k] (row-major) x B[k, b_cols] (row-major) for column tiles 0 .. n_tiles-1 of 128.  k must be a multiple of
+// 64 * splits; both matrices 16-byte aligned with rows that are multiples of 16 bytes.
+int launch_bf16_gemm_partial(const __nv_bfloat16* a, int t, int k, const __nv_bfloat16* b, int b_cols, int n_tiles,
+                             int splits, float* partial, int ldc, uint32_t* status, cudaStream_t stream) {
+  if (t <= 0) return DSV32_OK;
+  if (k <= 0 || splits <= 0 || k % (64 * splits) != 0 || ldc < n_tiles * 128) {
+    set_error("bf16 gemm: k=%d must be a multiple of 64 x %d splits and ldc=%d must hold %d column tiles", k, splits, ldc, n_tiles);
+    return DSV32_ERR_INVALID_ARG;
+  }
+  CUtensorMap a_map, b_map;
+  int rc = make_tensor_map_2d_u8(&a_map, a, t, static_cast<uint64_t>(k) * 2, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&b_map, b, k, static_cast<uint64_t>(b_cols) * 2, 64, 128);
+  if (rc != DSV32_OK) return rc;
+  MlaGemmParams gp{};
+  gp.partial = partial;
+  gp.status = status;
+  gp.t = t;
+  gp.k_chunks = k / 64 / splits;
+  gp.ldc = ldc;
+  gp.tile_switch = n_tiles;   // every tile reads the one weight matrix
+  return launch_gemm<kXproj>(a_map, b_map, b_map, gp, dim3(n_tiles, splits, (t + 127) / 128), stream,
+                             "mla_gemm_tc_kernel (bf16 partial sums)");
 }
 
 }  // namespace dsv32

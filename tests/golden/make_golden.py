@@ -35,6 +35,8 @@ Outputs (small .npz files; bf16/fp16 tensors stored as int16 bit patterns):
                      (gen_hc_pre, models/deepseek_v4/test_hc_pre.py)
   compressor_small.npz  outputs and touched state rows of the DeepSeek-V4 compressor golden (golden_compress,
                      models/deepseek_v4/test_compressor.py) for three cases: ratio 128, ratio 4, ratio 4 + hadamard
+  pg_prolog_mxfp8_small.npz  seed + input digests + outputs of the page-grouped MXFP8 indexer prolog golden
+                     (indexer_prolog, python/tests/st/operator/pg/test_pg_lightning_indexer_prolog_quant_mxfp8.py)
   kat.json           the two interpreter known-answer tests, restated as data
 
 Nothing at test time reads the reference: the tests only read these files.
@@ -476,6 +478,47 @@ def make_compressor():
     np.savez_compressed(os.path.join(HERE, "compressor_small.npz"), **saved)
 
 
+def make_pg_prolog_mxfp8():
+    pg_dir = os.path.join(REF, "python", "tests", "st", "operator", "pg")
+    sys.path.insert(0, pg_dir)
+    had_npu = hasattr(torch.Tensor, "npu")
+    if not had_npu:
+        torch.Tensor.npu = lambda self, *a, **k: self   # the generator parks two tensors on the device
+    try:
+        with _TolerateNpuDispatchKey():
+            import test_pg_lightning_indexer_prolog_quant_mxfp8 as ref  # noqa: reference module
+        seed, b, s1, s2 = 11, 2, 2, 256
+        torch.manual_seed(seed)
+        dims = ref.gen_dims({"b": b, "s1": s1, "s2": s2})
+        inputs = ref.gen_inputs(dims, torch.bfloat16)
+        out = ref.indexer_prolog(inputs, dims, "cpu")
+    finally:
+        sys.path.remove(pg_dir)
+        if not had_npu:
+            del torch.Tensor.npu
+    t = b * s1
+
+    def raw(v):
+        v = v.contiguous()
+        if v.dtype in (torch.float8_e4m3fn, torch.float8_e8m0fnu):
+            return v.view(torch.uint8)
+        if v.dtype in (torch.bfloat16, torch.float16):
+            return v.view(torch.int16)
+        return v
+
+    digests = {k: hashlib.sha256(raw(v).numpy().tobytes()).hexdigest() for k, v in inputs.items()}
+    index = inputs["idx_k_cache_index"].reshape(-1)
+    k_rows = out["idx_k_cache_out"].reshape(-1, 128)[index]          # fp32 values of the rows the operator wrote
+    k_scales = out["idx_k_scale_cache_out"].reshape(-1)[index]
+    np.savez_compressed(
+        os.path.join(HERE, "pg_prolog_mxfp8_small.npz"),
+        seed=seed, b=b, s1=s1, s2=s2, digests=json.dumps(digests),
+        q=out["query"].reshape(t, 24, 128).view(torch.uint8).numpy(), q_scale=out["query_scale"].reshape(t, 24, 1).numpy(),
+        k=k_rows.to(torch.float8_e4m3fn).view(torch.uint8).numpy(), k_scale=k_scales.numpy(),
+        weights=out["weights"].reshape(t, 24).numpy(), cache_index=index.numpy())
+    print("pg_prolog_mxfp8_small: q", tuple(out["query"].shape))
+
+
 def make_kat():
     kat = {
         "topk_ties": {  # test_interp_calc_matmul_sort.cpp:510-524
@@ -507,3 +550,4 @@ if __name__ == "__main__":
     make_mla_v4_bf16()
     make_hc_pre()
     make_compressor()
+    make_pg_prolog_mxfp8()

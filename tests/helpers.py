@@ -516,3 +516,118 @@ def mla_reference_inputs(seed, b, s1, s2):
                 gamma_cq=gamma_cq, gamma_ckv=gamma_ckv, cos=cos.reshape(t, rope), sin=sin.reshape(t, rope),
                 cache_index=cache_index.reshape(t), kv_cache=kv_q.reshape(block_num, bs, 1, lora), kr_cache=kr_cache,
                 ks_cache=kv_s.reshape(block_num, bs, 1, 4), block_table=block_table)
+
+
+# --------------------------------------------------------------------------
+# page-grouped 8-bit-float indexer prologs (python/tests/st/operator/pg/ in the reference)
+# --------------------------------------------------------------------------
+PG_H, PG_QLORA, PG_HEADS, PG_D, PG_ROPE, PG_BS = 2560, 1024, 24, 128, 64, 128
+PG_GROUP = 41    # caches of this many row widths share one page of the page-grouped buffer
+
+
+def load_pg_prolog_mxfp8_golden():
+    z = np.load(os.path.join(GOLDEN, "pg_prolog_mxfp8_small.npz"))
+    return dict(seed=int(z["seed"]), b=int(z["b"]), s1=int(z["s1"]), s2=int(z["s2"]), digests=json.loads(str(z["digests"])),
+                q=torch.from_numpy(z["q"]), q_scale=torch.from_numpy(z["q_scale"]), k=torch.from_numpy(z["k"]),
+                k_scale=torch.from_numpy(z["k_scale"]), weights=torch.from_numpy(z["weights"]),
+                cache_index=torch.from_numpy(z["cache_index"]))
+
+
+def pg_prolog_reference_inputs(seed, b, s1, s2):
+    """Same RNG call order as the reference generator (test_pg_lightning_indexer_prolog_quant_mxfp8.py:160-222), so the
+    same seed reproduces the tensors whose digests are stored in pg_prolog_mxfp8_small.npz.  The key cache and its
+    scale cache are strided views into one page-grouped byte buffer, as the reference builds them."""
+    torch.manual_seed(seed)
+    bf, f8, e8 = torch.bfloat16, torch.float8_e4m3fn, torch.float8_e8m0fnu
+    h, qr, d, n, rd, bs = PG_H, PG_QLORA, PG_D, PG_HEADS, PG_ROPE, PG_BS
+    x = torch.empty((b, s1, h), dtype=bf).uniform_(-1, 1)
+    q_norm = torch.empty((b, s1, qr), dtype=torch.float32).uniform_(-10, 10).to(f8)
+    q_norm_scale = torch.empty((b, s1, qr // 32), dtype=torch.float32).uniform_(0, 1).to(e8)
+    w_qb = torch.empty((qr, n * d), dtype=torch.float32).uniform_(-10, 10).to(f8)
+    w_qb_scale = torch.empty((qr // 64, n * d, 2), dtype=torch.float32).uniform_(0, 1).to(e8)
+    wk = torch.empty((h, d), dtype=bf).uniform_(-1, 1)
+    w_proj = torch.empty((h, n), dtype=bf).uniform_(-1, 1)
+    gamma = torch.ones((d,), dtype=bf)
+    ang = torch.rand(b, s1, rd, dtype=torch.float32) * 2 * torch.pi
+    cos, sin = torch.cos(ang).to(bf), torch.sin(ang).to(bf)
+    hq = torch.empty((d, d), dtype=bf).uniform_(-1, 1)
+    hk = torch.empty((d, d), dtype=bf).uniform_(-1, 1)
+    k_bsnd = torch.empty((b, s2, 1, d), dtype=torch.float32).uniform_(-10, 10).to(f8)
+    ks_bsnd = torch.empty((b, s2, 1, 1), dtype=torch.float32).uniform_(-1, 1)
+    nblk_each = math.ceil(s2 / bs)
+    block_num = nblk_each * b
+    perm = torch.arange(0, block_num, 1)
+    perm = perm[torch.randperm(perm.size(0))].to(torch.int32)
+    block_table = perm.reshape(b, nblk_each).clone()
+    cache_index = torch.empty((b, s1), dtype=torch.int64)
+    for i in range(b):
+        for j in range(s1):
+            pos = s2 - s1 + j
+            cache_index[i, j] = int(block_table[i, pos // bs]) * bs + pos % bs
+    pages = torch.randint(0, 256, (block_num, bs * d * PG_GROUP), dtype=torch.uint8)
+    k_cache = pages.view(f8)[:, bs * d:2 * bs * d].view(block_num, bs, 1, d)
+    off = 2 * bs * d // 4
+    k_scale_cache = pages.view(torch.float32)[:, off:off + bs].view(block_num, bs, 1, 1)
+    for i in range(b):
+        for j in range(nblk_each):
+            k_cache[block_table[i, j]] = k_bsnd[i, j * bs:(j + 1) * bs]
+            k_scale_cache[block_table[i, j]] = ks_bsnd[i, j * bs:(j + 1) * bs]
+    return {
+        "token_x": x, "q_norm": q_norm, "q_norm_scale": q_norm_scale, "w_idx_qb": w_qb, "w_idx_qb_scale": w_qb_scale,
+        "w_idx_k": wk, "w_idx_proj": w_proj, "rms_norm_gamma": gamma, "cos_idx_rope": cos, "sin_idx_rope": sin,
+        "hadamard_q": hq, "hadamard_k": hk, "idx_k_cache": k_cache, "idx_k_scale_cache": k_scale_cache,
+        "idx_k_cache_index": cache_index, "idx_block_table": block_table, "act_seq": torch.tensor([s2] * b),
+        "pages": pages,
+    }
+
+
+def pg_digest(v: torch.Tensor) -> str:
+    v = v.contiguous()
+    if v.dtype in (torch.float8_e4m3fn, torch.float8_e8m0fnu):
+        v = v.view(torch.uint8)
+    elif v.dtype in (torch.bfloat16, torch.float16):
+        v = v.view(torch.int16)
+    return hashlib.sha256(v.numpy().tobytes()).hexdigest()
+
+
+def gen_pg_prolog_inputs(seed, t, fmt, nblocks=4):
+    """Seeded inputs of the page-grouped prolog in either format, as the operator's 2-D arguments (CPU tensors).
+    fmt "mxfp8": float8_e4m3fn codes with E8M0 scales per 32 reduction elements; fmt "hif8": uint8 HiF8 codes with
+    an fp32 scale per token / per output column.  The caches are strided views into a page-grouped byte buffer."""
+    from oracle import pg_prolog_oracle as pgo
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    h, qr, d, n, rd, bs = PG_H, PG_QLORA, PG_D, PG_HEADS, PG_ROPE, PG_BS
+    u = lambda shape, a, lo=None: torch.empty(shape, dtype=torch.float32).uniform_(-a if lo is None else lo, a, generator=g)  # noqa: E731
+    x = u((t, h), 1.0).to(bf)
+    if fmt == "mxfp8":
+        q_norm = u((t, qr), 10.0).to(torch.float8_e4m3fn)
+        q_norm_scale = u((t, qr // 32), 1.0, 0.0).to(torch.float8_e8m0fnu)
+        w_qb = u((qr, n * d), 10.0).to(torch.float8_e4m3fn)
+        w_qb_scale = u((qr // 64, n * d, 2), 1.0, 0.0).to(torch.float8_e8m0fnu)
+    else:
+        q_norm = pgo.hif8_encode(u((t, qr), 10.0))
+        q_norm_scale = u((t, 1), 1.0, 0.05)
+        w_qb = pgo.hif8_encode(u((qr, n * d), 10.0))
+        w_qb_scale = u((1, n * d), 1.0, 0.05)
+    wk = u((h, d), 1.0).to(bf)
+    w_proj = u((h, n), 1.0).to(bf)
+    gamma = u((1, d), 1.5, 0.5).to(bf)
+    ang = torch.rand((t, rd), generator=g) * 2 * torch.pi
+    cos, sin = torch.cos(ang).to(bf), torch.sin(ang).to(bf)
+    hq, hk = u((d, d), 1.0).to(bf), u((d, d), 1.0).to(bf)
+    pages = torch.randint(0, 256, (nblocks, bs * d * PG_GROUP), dtype=torch.uint8, generator=g)
+    cache_index = torch.randperm(nblocks * bs, generator=g)[:t].to(torch.int64).reshape(t, 1)
+    return dict(x=x, q_norm=q_norm, q_norm_scale=q_norm_scale, w_qb=w_qb, w_qb_scale=w_qb_scale, wk=wk, w_proj=w_proj,
+                gamma_k=gamma, cos=cos, sin=sin, hadamard_q=hq, hadamard_k=hk, pages=pages, cache_index=cache_index)
+
+
+def pg_cache_views(pages: torch.Tensor, fmt: str):
+    """(key cache [blocks, 128, 1, 128], key scale cache [blocks, 128, 1, 1] fp32) as strided views into `pages`."""
+    bs, d = PG_BS, PG_D
+    blocks = pages.shape[0]
+    kc = pages.view(torch.float8_e4m3fn) if fmt == "mxfp8" else pages
+    k_cache = kc[:, bs * d:2 * bs * d].view(blocks, bs, 1, d)
+    off = 2 * bs * d // 4
+    k_scale_cache = pages.view(torch.float32)[:, off:off + bs].view(blocks, bs, 1, 1)
+    return k_cache, k_scale_cache
