@@ -337,6 +337,37 @@ typedef struct {
 int dsv32_pg_indexer_prolog(const Dsv32PgPrologArgs* args, void* cuda_stream);
 size_t dsv32_pg_indexer_prolog_workspace_bytes(int32_t t, int32_t h, int32_t q_lora, int32_t heads);
 
+/* ---------------------------------------------------------------------------------------
+ * Matrix products on this library's tcgen05 kernel, for the projections of the DeepSeek-V4 operators
+ * whose host code lives in Python (models/deepseek_v4/mla_prolog_quant_v4_impl.py:438-520, mla_prolog_v4_impl.py,
+ * compressor_impl.py:421-923: their `pypto.matmul` calls).
+ *   dsv32_gemm_bf16: C[t, n] = A[t, k] x B, bf16 operands, fp32 accumulation; B is [k, n] row-major
+ *     (b_layout 0) or [n, k] row-major (b_layout 1: a weight held one row per output column); C is fp32
+ *     (c_dtype 0) or bf16 (c_dtype 1, one rounding of the fp32 sum).  k a multiple of 64, n of 8.
+ *   dsv32_gemm_i8: int32 C[t, n] = int8 A[t, k] x int8 B[k, n]; k a multiple of 128, n of 256.
+ * All pointers 16-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* a;                    /* bf16 [t, k]                                  */
+  const void* b;                    /* bf16 [k, n] or [n, k] (b_layout)             */
+  void* c;                          /* out fp32 or bf16 [t, n] (c_dtype)            */
+  void* workspace;                  /* >= dsv32_gemm_bf16_workspace_bytes(t, k, n), 256-byte aligned */
+  size_t workspace_bytes;
+  uint32_t* status;
+  int32_t t, k, n, b_layout, c_dtype;
+} Dsv32GemmBf16Args;
+int dsv32_gemm_bf16(const Dsv32GemmBf16Args* args, void* cuda_stream);
+size_t dsv32_gemm_bf16_workspace_bytes(int32_t t, int32_t k, int32_t n);
+
+typedef struct {
+  const int8_t* a;                  /* int8 [t, k]                                  */
+  const int8_t* b;                  /* int8 [k, n]                                  */
+  int32_t* c;                       /* out int32 [t, n]                             */
+  uint32_t* status;
+  int32_t t, k, n;
+} Dsv32GemmI8Args;
+int dsv32_gemm_i8(const Dsv32GemmI8Args* args, void* cuda_stream);
+
 /* Array conversions of the HiF8 format (device pointers; n elements):
  * direction 0: fp32 -> codes (nearest value, ties away from zero, saturating at 2^15), 1: codes -> fp32. */
 int dsv32_hif8_convert(int32_t direction, const void* in, void* out, int64_t n, void* cuda_stream);

@@ -96,6 +96,18 @@ class PgPrologArgs(C.Structure):
     ]
 
 
+class GemmBf16Args(C.Structure):
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("c", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("status", c_void_p), ("t", c_i32), ("k", c_i32), ("n", c_i32), ("b_layout", c_i32), ("c_dtype", c_i32),
+    ]
+
+
+class GemmI8Args(C.Structure):
+    _fields_ = [("a", c_void_p), ("b", c_void_p), ("c", c_void_p), ("status", c_void_p), ("t", c_i32), ("k", c_i32),
+                ("n", c_i32)]
+
+
 class IndexerArgs(C.Structure):
     _fields_ = [
         ("idx_query", c_void_p), ("idx_query_scale", c_void_p), ("idx_key_cache", c_void_p),
@@ -176,6 +188,9 @@ EXPORTS = {
     "dsv32_pg_indexer_prolog": (c_i32, [C.POINTER(PgPrologArgs), c_void_p]),
     "dsv32_pg_indexer_prolog_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
     "dsv32_hif8_convert": (c_i32, [c_i32, c_void_p, c_void_p, c_i64, c_void_p]),
+    "dsv32_gemm_bf16": (c_i32, [C.POINTER(GemmBf16Args), c_void_p]),
+    "dsv32_gemm_bf16_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32]),
+    "dsv32_gemm_i8": (c_i32, [C.POINTER(GemmI8Args), c_void_p]),
 }
 
 ABI_VERSION = 2

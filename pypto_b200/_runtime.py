@@ -42,11 +42,56 @@ def same_device(*tensors):
     return dev
 
 
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """bf16 [m, k] x bf16 [k, n] -> fp32 (or bf16) [m, n] on this library's tcgen05 kernel: the products of bf16
+    numbers are exact in fp32 and the accumulation is fp32, so this is the fp32 product of the widened operands up to
+    the order of the summation.  `b` may be a contiguous [k, n] matrix or the transposed view of a contiguous [n, k]
+    one (a weight held one row per output column); k must be a multiple of 64, n of 8."""
+    check_tensor(a, "gemm a", torch.bfloat16, ndim=2)
+    if not isinstance(b, torch.Tensor) or b.dtype != torch.bfloat16 or b.dim() != 2 or b.shape[0] != a.shape[1]:
+        raise ValueError(f"gemm b: expected a bf16 matrix with {a.shape[1]} rows, got {getattr(b, 'shape', None)}")
+    if b.is_contiguous():
+        layout = 0
+    elif b.t().is_contiguous():
+        layout = 1
+    else:
+        raise ValueError("gemm b: expected a contiguous matrix or the transposed view of one")
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"gemm: out_dtype {out_dtype} is neither float32 nor bfloat16")
+    m, k, n = int(a.shape[0]), int(a.shape[1]), int(b.shape[1])
+    dev = same_device(a, b)
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    if m == 0:
+        return out
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws_bytes = lib.dsv32_gemm_bf16_workspace_bytes(m, k, n)
+        ws = workspace(max(int(ws_bytes), 256), dev)
+        args = _lib.GemmBf16Args(ptr(a), ptr(b), ptr(out), ptr(ws), int(ws_bytes), ptr(status_word(dev)), m, k, n, layout,
+                                 1 if out_dtype == torch.bfloat16 else 0)
+        _lib.check(lib.dsv32_gemm_bf16(C.byref(args), stream_ptr(dev)), "gemm_bf16")
+    return out
+
+
 def gemm_bf16_fp32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """bf16 [m, k] x bf16 [k, n] -> fp32 [m, n] on the tensor cores (library GEMM): the products of bf16 numbers
-    are exact in fp32 and the accumulation is fp32, so this is the fp32 product of the widened operands up to
-    the order of the summation, without materialising fp32 copies of the weights.  `b` may be a transposed view."""
-    return torch.mm(a, b, out_dtype=torch.float32)
+    """bf16 x bf16 -> fp32 (see gemm_bf16)."""
+    return gemm_bf16(a, b, torch.float32)
+
+
+def gemm_i8(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """int8 [m, k] x int8 [k, n] -> int32 [m, n], exact, on this library's tcgen05 kernel (k a multiple of 128, n of 256)."""
+    check_tensor(a, "gemm a", torch.int8, ndim=2)
+    check_tensor(b, "gemm b", torch.int8, (a.shape[1], None))
+    m, k, n = int(a.shape[0]), int(a.shape[1]), int(b.shape[1])
+    dev = same_device(a, b)
+    out = torch.empty((m, n), dtype=torch.int32, device=dev)
+    if m == 0:
+        return out
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        args = _lib.GemmI8Args(ptr(a), ptr(b), ptr(out), ptr(status_word(dev)), m, k, n)
+        _lib.check(lib.dsv32_gemm_i8(C.byref(args), stream_ptr(dev)), "gemm_i8")
+    return out
 
 
 _SIDE_STREAMS = {}

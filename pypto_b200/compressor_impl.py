@@ -7,8 +7,9 @@ cache row: per token kv = x @ wkv.T and score = x @ wgate.T + ape[pos % ratio] a
 when a window is complete its kv rows are summed with softmax(score rows) weights per column (ratio 4 mixes the
 first halves of the previous window with the second halves of the current one), RMS-normalised, given the
 interleaved rotary embedding on the last 64 dims and, with `rotate`, multiplied by a hadamard matrix.
-The two projections and the hadamard product are library GEMMs (cuBLAS through torch; bf16 operands with fp32
-accumulation and fp32 results, i.e. the reference golden's fp32 product up to summation order); the state update and the compression are one CUDA kernel.  `kv_state` and `score_state` are
+The two projections and the hadamard product run on this library's tcgen05 GEMM kernel (dsv32_gemm_bf16; bf16 operands
+with fp32 accumulation, i.e. the reference golden's fp32 product up to summation order; the weights are read as they
+are held, one row per output column); the state update and the compression are one CUDA kernel.  `kv_state` and `score_state` are
 updated in place and returned with the new rows, as the reference does.  Work is only enqueued on the current stream.
 """
 from __future__ import annotations
@@ -71,7 +72,7 @@ def npu_compressor(x, kv_state, score_state, kv_block_table, score_block_table, 
                                 score_block_table.shape[1], EPS)
         rt.check(lib.dsv32_compressor_update(C.byref(a), rt.stream_ptr(dev)), "compressor")
         if rotate:
-            out = torch.matmul(out, hadamard)                  # rows of requests that did not compress stay zero
+            out = rt.gemm_bf16(out, hadamard, torch.bfloat16)  # rows of requests that did not compress stay zero
     return out, kv_state, score_state
 
 

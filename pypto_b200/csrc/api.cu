@@ -457,6 +457,41 @@ int dsv32_pg_indexer_prolog(const Dsv32PgPrologArgs* a, void* cuda_stream) {
   return launch_pg_prolog(p, a->workspace, static_cast<cudaStream_t>(cuda_stream));
 }
 
+size_t dsv32_gemm_bf16_workspace_bytes(int32_t t, int32_t k, int32_t n) { return bf16_gemm_workspace_bytes(t, k, n); }
+
+int dsv32_gemm_bf16(const Dsv32GemmBf16Args* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "gemm bf16: args is NULL");
+  REQUIRE(a->t >= 0, "gemm bf16: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  REQUIRE(a->k >= 64 && a->k % 64 == 0, "gemm bf16: k=%d must be a positive multiple of 64", a->k);
+  REQUIRE(a->n >= 8 && a->n % 8 == 0, "gemm bf16: n=%d must be a positive multiple of 8", a->n);
+  REQUIRE((a->b_layout == 0 || a->b_layout == 1) && (a->c_dtype == 0 || a->c_dtype == 1),
+          "gemm bf16: b_layout=%d / c_dtype=%d must be 0 or 1", a->b_layout, a->c_dtype);
+  REQUIRE(a->a && a->b && a->c, "gemm bf16: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->a) % 16 == 0 && reinterpret_cast<uintptr_t>(a->b) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->c) % 16 == 0,
+          "gemm bf16: a / b / c must be 16-byte aligned");
+  const size_t need = bf16_gemm_workspace_bytes(a->t, a->k, a->n);
+  if (a->workspace == nullptr || a->workspace_bytes < need || reinterpret_cast<uintptr_t>(a->workspace) % 256 != 0) {
+    set_error("gemm bf16: workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return DSV32_ERR_WORKSPACE;
+  }
+  return launch_bf16_gemm(static_cast<const __nv_bfloat16*>(a->a), a->t, a->k, static_cast<const __nv_bfloat16*>(a->b), a->n,
+                          a->b_layout == 1, a->c, a->c_dtype == 1, a->workspace, a->status,
+                          static_cast<cudaStream_t>(cuda_stream));
+}
+
+int dsv32_gemm_i8(const Dsv32GemmI8Args* a, void* cuda_stream) {
+  REQUIRE(a != nullptr, "gemm int8: args is NULL");
+  REQUIRE(a->t >= 0, "gemm int8: bad t=%d", a->t);
+  if (a->t == 0) return DSV32_OK;
+  REQUIRE(a->a && a->b && a->c, "gemm int8: NULL tensor pointer");
+  REQUIRE(reinterpret_cast<uintptr_t>(a->a) % 16 == 0 && reinterpret_cast<uintptr_t>(a->b) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(a->c) % 16 == 0,
+          "gemm int8: a / b / c must be 16-byte aligned");
+  return launch_i8_gemm(a->a, a->t, a->k, a->b, a->n, a->c, a->status, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int dsv32_hif8_convert(int32_t direction, const void* in, void* out, int64_t n, void* cuda_stream) {
   REQUIRE(direction == 0 || direction == 1, "hif8 convert: direction %d is neither 0 (encode) nor 1 (decode)", direction);
   REQUIRE(n >= 0, "hif8 convert: bad n=%lld", static_cast<long long>(n));

@@ -160,7 +160,13 @@ struct MlaParams {
 int launch_mla_prolog(const MlaParams& p, cudaStream_t stream);
 // bf16 tcgen05 GEMM as a building block (mla_prolog_tc.cu): fp32 partial sums, one [t, ldc] slab per reduction split
 int launch_bf16_gemm_partial(const __nv_bfloat16* a, int t, int k, const __nv_bfloat16* b, int b_cols, int n_tiles,
-                             int splits, float* partial, int ldc, uint32_t* status, cudaStream_t stream);
+                             int splits, float* partial, int ldc, uint32_t* status, cudaStream_t stream,
+                             bool b_kmajor = false);
+// C[t, n] (fp32 or bf16) = A[t, k] x B (bf16; B as [k, n], or with b_kmajor as [n, k]) through partial sums in `workspace`
+int launch_bf16_gemm(const __nv_bfloat16* a, int t, int k, const __nv_bfloat16* b, int n, bool b_kmajor, void* out,
+                     bool out_bf16, void* workspace, uint32_t* status, cudaStream_t stream);
+size_t bf16_gemm_workspace_bytes(int t, int k, int n);
+int launch_i8_gemm(const int8_t* a, int t, int k, const int8_t* b, int n, int32_t* c, uint32_t* status, cudaStream_t stream);
 size_t mla_prolog_workspace_bytes(int t);
 
 // Page-grouped indexer prolog with 8-bit float formats (pg_prolog.cu)

@@ -22,7 +22,7 @@ namespace dsv32 {
 constexpr int kGemmThreads = 192;   // warp 0: TMA producer, warp 1: MMA issuer + tensor-memory owner, 2..5: epilogue
 constexpr int kMlaH = 7168, kMlaQLora = 1536, kMlaHeads = 128, kMlaNope = 128, kMlaRope = 64, kMlaLora = 512;
 
-enum { kXproj = 0, kQb = 1, kUk = 2 };
+enum { kXproj = 0, kQb = 1, kUk = 2, kI8 = 3 };
 
 struct MlaGemmParams {
   float* partial;                  // kXproj out: [kMlaXSplits][t][kMlaXCols]
@@ -38,11 +38,13 @@ struct MlaGemmParams {
   // kXproj: reduction chunks (of 64) per CTA, row stride of a partial slab in floats, and the first column tile
   // that reads the second weight matrix
   int k_chunks, ldc, tile_switch;
+  int b_kmajor;                    // kXproj: the weights are held as [n, k] (each row one output column) instead of [k, n]
+  int32_t* c_i32;                  // kI8 out: [t, ldc] int32 (ldc = n, a multiple of 256); k_chunks = k / 128
 };
 
 template <int kKind>
 struct GemmShape {
-  static constexpr bool kInt8 = kKind == kQb;
+  static constexpr bool kInt8 = kKind == kQb || kKind == kI8;
   // 128-byte column chunks of B per stage: 128 / 256 / 512 columns per CTA.  Few, wide CTAs with deep rings: what
   // bounds these kernels is the bytes of weights one SM keeps in flight, not the number of CTAs.
   static constexpr int kNChunks = kKind == kUk ? 8 : 2;
@@ -52,7 +54,7 @@ struct GemmShape {
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBChunk = kKRows * 128;
   static constexpr int kStageBytes = kABytes + kNChunks * kBChunk;    // 32 / 48 / 80 KB
-  static constexpr int kStages = kKind == kXproj ? 6 : (kKind == kQb ? 4 : 2);
+  static constexpr int kStages = kKind == kXproj ? 6 : (kInt8 ? 4 : 2);
   static constexpr int kChunksTotal = kKind == kXproj ? kMlaH / 64 : (kKind == kQb ? kMlaQLora / 128 : kMlaNope / 64);
   static constexpr int kOffWs = kStages * kStageBytes;                // kQb: 256 column scales
   static constexpr int kOffBars = kOffWs + 1024;
@@ -87,6 +89,8 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
   int c_begin = 0, nchunks = Sh::kChunksTotal;
   if constexpr (kKind == kXproj) {
     c_begin = split * p.k_chunks;
+    nchunks = p.k_chunks;
+  } else if constexpr (kKind == kI8) {
     nchunks = p.k_chunks;
   }
 
@@ -125,12 +129,16 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
         const int k0 = (c_begin + c) * Sh::kKRows;   // first reduction element of the chunk
         if constexpr (kKind == kXproj) {
           tma_load_2d(st, &a_map, k0 * 2, t0, &full_bar[s]);
+          if (p.b_kmajor) {   // 128 weight rows (output columns) x 64 reduction elements: one 16 KB box, laid out like A
+            tma_load_2d(st + Sh::kABytes, &b_map0, k0 * 2, tile * 128, &full_bar[s]);
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             if (tile < p.tile_switch) tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map0, tile * 256 + j * 128, k0, &full_bar[s]);
             else tma_load_2d(st + Sh::kABytes + j * Sh::kBChunk, &b_map1, (tile - p.tile_switch) * 256 + j * 128, k0, &full_bar[s]);
           }
-        } else if constexpr (kKind == kQb) {
+        } else if constexpr (Sh::kInt8) {
           tma_load_2d(st, &a_map, k0, t0, &full_bar[s]);
 #pragma unroll
           for (int j = 0; j < 2; ++j)
@@ -146,7 +154,10 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
   } else if (warp == 1) {
     // ---- MMA issuer: the whole warp runs the loop (uniform operands), lane 0 issues ---------------------------
     const bool leader = lane == 0;
-    constexpr uint32_t idesc = Sh::kInt8 ? umma_idesc_i8(128, Sh::kMmaN, true) : umma_idesc_bf16(128, Sh::kMmaN, false, true);
+    constexpr uint32_t idesc_mn = Sh::kInt8 ? umma_idesc_i8(128, Sh::kMmaN, true) : umma_idesc_bf16(128, Sh::kMmaN, false, true);
+    constexpr uint32_t idesc_k = umma_idesc_bf16(128, Sh::kMmaN, false, false);
+    const bool b_kmajor = kKind == kXproj && p.b_kmajor != 0;
+    const uint32_t idesc = b_kmajor ? idesc_k : idesc_mn;
     const uint32_t tbase = __shfl_sync(0xffffffffu, tmem_base, 0);
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
@@ -161,8 +172,9 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
         const uint32_t acc = (c > 0 || ks > 0) ? 1u : 0u;
 #pragma unroll
         for (int h = 0; h < Sh::kN / Sh::kMmaN; ++h) {  // 512 columns: two instructions of 256
-          const uint64_t bd = umma_smem_desc_sw128(b_s + h * (Sh::kMmaN / (Sh::kInt8 ? 128 : 64)) * Sh::kBChunk +
-                                                       ks * (Sh::kInt8 ? 4096 : 2048), Sh::kBChunk, 1024);
+          const uint64_t bd = b_kmajor ? umma_smem_desc_sw128(b_s + ks * 32, 16, 1024)
+                                       : umma_smem_desc_sw128(b_s + h * (Sh::kMmaN / (Sh::kInt8 ? 128 : 64)) * Sh::kBChunk +
+                                                                  ks * (Sh::kInt8 ? 4096 : 2048), Sh::kBChunk, 1024);
           if constexpr (Sh::kInt8) {
             asm volatile(
                 "{\n\t.reg .pred pa, pl;\n\tsetp.ne.b32 pa, %4, 0;\n\tsetp.ne.b32 pl, %5, 0;\n\t"
@@ -199,6 +211,19 @@ mla_gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_const
               *reinterpret_cast<float4*>(prow + c * 32 + j) =
                   make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
                               __uint_as_float(r[j + 3]));
+          }
+        }
+      } else if constexpr (kKind == kI8) {
+        int32_t* crow = p.c_i32 + static_cast<size_t>(tk) * p.ldc + tile * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint4*>(crow + c * 32 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
           }
         }
       } else if constexpr (kKind == kQb) {
@@ -398,10 +423,11 @@ int launch_mla_prolog(const MlaParams& p, cudaStream_t stream) {
 }
 
 // The same bf16 kernel as a building block: fp32 partial sums, one [t, ldc] slab per reduction split, of
-// A[t, k] (row-major) x B[k, b_cols] (row-major) for column tiles 0 .. n_tiles-1 of 128.  k must be a multiple of
-// 64 * splits; both matrices 16-byte aligned with rows that are multiples of 16 bytes.
+// A[t, k] (row-major) x B for column tiles 0 .. n_tiles-1 of 128, where B is [k, b_cols] row-major, or with
+// b_kmajor [b_cols, k] row-major (one row per output column; rows past b_cols read as zero).  k must be a multiple
+// of 64 * splits; both matrices 16-byte aligned with rows that are multiples of 16 bytes.
 int launch_bf16_gemm_partial(const __nv_bfloat16* a, int t, int k, const __nv_bfloat16* b, int b_cols, int n_tiles,
-                             int splits, float* partial, int ldc, uint32_t* status, cudaStream_t stream) {
+                             int splits, float* partial, int ldc, uint32_t* status, cudaStream_t stream, bool b_kmajor) {
   if (t <= 0) return DSV32_OK;
   if (k <= 0 || splits <= 0 || k % (64 * splits) != 0 || ldc < n_tiles * 128) {
     set_error("bf16 gemm: k=%d must be a multiple of 64 x %d splits and ldc=%d must hold %d column tiles", k, splits, ldc, n_tiles);
@@ -409,7 +435,10 @@ int launch_bf16_gemm_partial(const __nv_bfloat16* a, int t, int k, const __nv_bf
   }
   CUtensorMap a_map, b_map;
   int rc = make_tensor_map_2d_u8(&a_map, a, t, static_cast<uint64_t>(k) * 2, 128, 128);
-  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&b_map, b, k, static_cast<uint64_t>(b_cols) * 2, 64, 128);
+  if (rc == DSV32_OK) {
+    if (b_kmajor) rc = make_tensor_map_2d_u8(&b_map, b, b_cols, static_cast<uint64_t>(k) * 2, 128, 128);
+    else rc = make_tensor_map_2d_u8(&b_map, b, k, static_cast<uint64_t>(b_cols) * 2, 64, 128);
+  }
   if (rc != DSV32_OK) return rc;
   MlaGemmParams gp{};
   gp.partial = partial;
@@ -418,8 +447,71 @@ int launch_bf16_gemm_partial(const __nv_bfloat16* a, int t, int k, const __nv_bf
   gp.k_chunks = k / 64 / splits;
   gp.ldc = ldc;
   gp.tile_switch = n_tiles;   // every tile reads the one weight matrix
+  gp.b_kmajor = b_kmajor ? 1 : 0;
   return launch_gemm<kXproj>(a_map, b_map, b_map, gp, dim3(n_tiles, splits, (t + 127) / 128), stream,
                              "mla_gemm_tc_kernel (bf16 partial sums)");
+}
+
+// int32 C[t, n] = int8 A[t, k] (row-major) x int8 B[k, n] (row-major): k a multiple of 128, n of 256.
+int launch_i8_gemm(const int8_t* a, int t, int k, const int8_t* b, int n, int32_t* c, uint32_t* status, cudaStream_t stream) {
+  if (t <= 0) return DSV32_OK;
+  if (k <= 0 || k % 128 != 0 || n <= 0 || n % 256 != 0) {
+    set_error("int8 gemm: k=%d must be a positive multiple of 128 and n=%d of 256", k, n);
+    return DSV32_ERR_INVALID_ARG;
+  }
+  CUtensorMap a_map, b_map;
+  int rc = make_tensor_map_2d_u8(&a_map, a, t, k, 128, 128);
+  if (rc == DSV32_OK) rc = make_tensor_map_2d_u8(&b_map, b, k, n, 128, 128);
+  if (rc != DSV32_OK) return rc;
+  MlaGemmParams gp{};
+  gp.status = status;
+  gp.t = t;
+  gp.k_chunks = k / 128;
+  gp.ldc = n;
+  gp.c_i32 = c;
+  return launch_gemm<kI8>(a_map, b_map, b_map, gp, dim3(n / 256, 1, (t + 127) / 128), stream, "mla_gemm_tc_kernel (int8)");
+}
+
+// out[t, n] (fp32, or bf16 with one rounding) = sum over the reduction splits, in order, of the fp32 slabs [t, ldp]
+__global__ void __launch_bounds__(256) gemm_reduce_kernel(const float* partial, int splits, int t, int ldp, int n, void* out,
+                                                          int out_bf16) {
+  const long long total = static_cast<long long>(t) * n;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
+    const long long row = i / n, col = i % n;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[(static_cast<size_t>(s) * t + row) * ldp + col];
+    if (out_bf16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(acc);
+    else static_cast<float*>(out)[i] = acc;
+  }
+}
+
+static int gemm_splits(int t, int k, int n) {
+  const int chunks = k / 64, ctas = ((n + 127) / 128) * ((t + 127) / 128);
+  int best = 1;
+  for (int s = 1; s <= 16; ++s)
+    if (chunks % s == 0 && ctas * s <= 296) best = s;   // at most two CTAs' worth of work per SM
+  return best;
+}
+
+size_t bf16_gemm_workspace_bytes(int t, int k, int n) {
+  if (t <= 0 || k <= 0 || n <= 0 || k % 64 != 0) return 0;
+  const size_t ldp = static_cast<size_t>((n + 127) / 128) * 128;
+  return (static_cast<size_t>(gemm_splits(t, k, n)) * t * ldp * sizeof(float) + 255) / 256 * 256;
+}
+
+int launch_bf16_gemm(const __nv_bfloat16* a, int t, int k, const __nv_bfloat16* b, int n, bool b_kmajor, void* out,
+                     bool out_bf16, void* workspace, uint32_t* status, cudaStream_t stream) {
+  if (t <= 0) return DSV32_OK;
+  const int splits = gemm_splits(t, k, n), n_tiles = (n + 127) / 128, ldp = n_tiles * 128;
+  float* partial = static_cast<float*>(workspace);
+  int rc = launch_bf16_gemm_partial(a, t, k, b, n, n_tiles, splits, partial, ldp, status, stream, b_kmajor);
+  if (rc != DSV32_OK) return rc;
+  const long long total = static_cast<long long>(t) * n;
+  const long long blocks = (total + 255) / 256;
+  gemm_reduce_kernel<<<static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(partial, splits, t, ldp, n, out,
+                                                                                                out_bf16 ? 1 : 0);
+  count_launch();
+  return check_launch("gemm_reduce_kernel");
 }
 
 }  // namespace dsv32

@@ -6,9 +6,10 @@ mla_prolog_v4_in :567-629, mla_prolog_quant_pypto :655-658; compute mla_prolog_v
   q            = bf16(RMSNorm_per_head(int32(qr @ wq_b) * qr_scale * wq_b_scale)), heads of 512 dims, interleaved
                  rotary embedding on the last 64 dims of each head                (the query of the V4 attention)
   kv           = bf16(RMSNorm(x @ wkv) * gamma_ckv), rotary embedding on its last 64 dims   (the new cache row)
-The three projections are library GEMMs (cuBLAS through torch: bf16 operands with fp32 accumulation and fp32 results, which is
-the reference golden's fp32 product of the widened operands up to summation order; int8 with int32 accumulation); everything between them is one fused CUDA kernel per stage.  Weights are
-plain row-major [K, N].  Work is enqueued on the current CUDA stream and, for the
+The three projections run on this library's tcgen05 GEMM kernel (dsv32_gemm_bf16: bf16 operands, fp32 accumulation and
+fp32 results, which is the reference golden's fp32 product of the widened operands up to summation order;
+dsv32_gemm_i8: int8 with exact int32 accumulation); everything between them is one fused CUDA kernel per stage.
+Weights are plain row-major [K, N].  Work is enqueued on the current CUDA stream and, for the
 independent kv branch, on a second stream of the device that is forked from and joined back into it by events
 (also when the q branch raises).
 """
@@ -52,15 +53,6 @@ class MlaPrologV4Configs:
     chunk_size: int = 2
 
 
-
-def _int8_gemm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """int8 [m,k] x int8 [k,n] -> int32 [m', n] with m' >= m (the library kernel wants more than 16 rows)."""
-    m = a.shape[0]
-    if m <= 16:
-        pad = torch.zeros((32, a.shape[1]), dtype=torch.int8, device=a.device)
-        pad[:m] = a
-        a = pad
-    return torch._int_mm(a, b)
 
 def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_sin, wq_b_scale, q_out, kv_out, qr_out,
                   qr_scale_out, attrs=None, configs=None, tile_configs=None):
@@ -111,7 +103,7 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
             q_a = rt.gemm_bf16_fp32(token_x, wq_a)                                   # [t, 1024] fp32
             a.q_a = rt.ptr(q_a)
             rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 0, stream), "mla_prolog_v4 (q norm + quant)")
-            q_b = _int8_gemm(qr_out, wq_b)                                    # [>= t, heads * 512] int32
+            q_b = rt.gemm_i8(qr_out, wq_b)                                       # [t, heads * 512] int32, exact
             a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]
             rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 1, stream), "mla_prolog_v4 (q dequant + norm + rope)")
         finally:

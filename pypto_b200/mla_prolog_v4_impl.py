@@ -5,7 +5,8 @@ mla_prolog_v4_in :415-455, mla_prolog_pypto :479-480; compute mla_prolog_v4_comp
   qr = bf16(RMSNorm(bf16(x @ wq_a)) * gamma_cq)
   q  = bf16(RMSNorm_per_head(bf16(qr @ wq_b))), heads of 512 dims, interleaved rotary embedding on the last 64
   kv = bf16(RMSNorm(bf16(x @ wkv)) * gamma_ckv), rotary embedding on its last 64 dims
-The three projections are library bf16 GEMMs (cuBLAS through torch); the stages between them are the kernels of
+The three projections run on this library's tcgen05 GEMM kernel (dsv32_gemm_bf16, fp32 accumulation, one rounding to
+bf16); the stages between them are the kernels of
 the quantised operator (mla_prolog_quant_v4_impl) instantiated without the quantisation.  Work is enqueued on the
 current CUDA stream and, for the independent kv branch, on a second stream of the device that is forked from and
 joined back into it by events (also when the q branch raises).
@@ -77,15 +78,15 @@ def mla_prolog_v4(token_x, wq_a, wq_b, wkv, gamma_cq, gamma_ckv, rope_cos, rope_
         # the kv branch (one GEMM + one stage kernel) is independent of the q branch: it runs on a second stream
         fork = rt.side_stream(dev)
         with fork:
-            kv_a = torch.matmul(token_x, wkv)                             # [t, 512] bf16
+            kv_a = rt.gemm_bf16(token_x, wkv, torch.bfloat16)             # [t, 512] bf16
             a.kv_a = rt.ptr(kv_a)
             rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 2, rt.stream_ptr(dev)), "mla_prolog_v4 (kv norm + rope)")
         try:   # whatever happens on this branch, the caller's stream must wait for the side branch
             stream = rt.stream_ptr(dev)
-            q_a = torch.matmul(token_x, wq_a)                                 # [t, 1024] bf16
+            q_a = rt.gemm_bf16(token_x, wq_a, torch.bfloat16)                 # [t, 1024] bf16
             a.q_a = rt.ptr(q_a)
             rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 0, stream), "mla_prolog_v4 (q norm)")
-            q_b = torch.matmul(qr_out, wq_b)                                  # [t, heads * 512] bf16
+            q_b = rt.gemm_bf16(qr_out, wq_b, torch.bfloat16)                  # [t, heads * 512] bf16
             a.q_b, a.q_b_ld = rt.ptr(q_b), q_b.shape[1]
             rt.check(lib.dsv32_mla_prolog_v4_stage(C.byref(a), 1, stream), "mla_prolog_v4 (q norm + rope)")
         finally:
