@@ -461,7 +461,7 @@ int dsv32_decode_advance(const Dsv32AdvanceArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused element-wise stages of the DeepSeek-V4 MLA prolog (quant), between its three
- * library GEMMs.  Replaces the vector work of mla_prolog_v4 / mla_prolog_v4_in
+ * projections (dsv32_gemm_bf16 / dsv32_gemm_i8).  Replaces the vector work of mla_prolog_v4 / mla_prolog_v4_in
  * (models/deepseek_v4/mla_prolog_quant_v4_impl.py:406-517 / 567-629):
  *   stage 0: q_a = x.wq_a (fp32) -> RMSNorm * gamma_cq -> per-token int8 quant -> qr, qr_scale
  *   stage 1: q_b = qr.wq_b (int32) -> * qr_scale * wq_b_scale -> per-head RMSNorm (no weight)
