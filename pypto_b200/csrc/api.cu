@@ -396,7 +396,7 @@ size_t dsv32_pg_indexer_prolog_workspace_bytes(int32_t t, int32_t h, int32_t q_l
 
 int dsv32_pg_indexer_prolog(const Dsv32PgPrologArgs* a, void* cuda_stream) {
   REQUIRE(a != nullptr, "pg prolog: args is NULL");
-  REQUIRE(a->t >= 0, "pg prolog: bad t=%d", a->t);
+  REQUIRE(a->t >= 0 && a->t <= (1 << 22), "pg prolog: t=%d must be in [0, 2^22]", a->t);
   if (a->t == 0) return DSV32_OK;
   REQUIRE(a->format == DSV32_PG_FORMAT_MXFP8 || a->format == DSV32_PG_FORMAT_HIF8, "pg prolog: unknown format %d", a->format);
   REQUIRE(a->h >= 512 && a->h % 512 == 0, "pg prolog: h=%d must be a positive multiple of 512", a->h);

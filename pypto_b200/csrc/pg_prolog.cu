@@ -191,7 +191,7 @@ __device__ __forceinline__ uint32_t pg_rope_hadamard_quant(float v, const __nv_b
 __global__ void __launch_bounds__(kPgDim) pg_q_finish_kernel(PgPrologParams p, const float* partial, int splits) {
   __shared__ float row_s[kPgDim];
   __shared__ float red_s[4];
-  const int head = blockIdx.x, tok = blockIdx.y, j = threadIdx.x;
+  const int head = blockIdx.x % p.heads, tok = blockIdx.x / p.heads, j = threadIdx.x;   // t * heads CTAs in x: no 65,535 limit
   const int col = head * kPgDim + j;
   float acc = 0.f;
   for (int s = 0; s < splits; ++s) acc += partial[(static_cast<size_t>(s) * p.t + tok) * p.n + col];
@@ -298,7 +298,7 @@ int launch_pg_prolog(const PgPrologParams& p, void* workspace, cudaStream_t stre
   if (rc != DSV32_OK) return rc;
   rc = launch_bf16_gemm_partial(p.x, p.t, p.h, xw_bf, kPgXwCols, kPgXwCols / 128, xs, part_x, kPgXwCols, p.status, stream);
   if (rc != DSV32_OK) return rc;
-  pg_q_finish_kernel<<<dim3(p.heads, p.t), kPgDim, 0, stream>>>(p, part_q, qs);
+  pg_q_finish_kernel<<<p.heads * p.t, kPgDim, 0, stream>>>(p, part_q, qs);
   count_launch();
   rc = check_launch("pg_q_finish_kernel");
   if (rc != DSV32_OK) return rc;
