@@ -1,5 +1,7 @@
-// Row-wise top-k by block-wide radix select (one CTA per row), followed by a bitonic sort of the
-// selected entries so that rows come out by descending score, equal scores by ascending id.
+// Row-wise top-k by block-wide radix select (one CTA per row), followed by an ordering of the selected entries
+// so that rows come out by descending score, equal scores by ascending id: a counting sort on the top eleven bits
+// of the span the selected scores actually cover, then each entry's rank inside its (small) bucket -- or, when
+// the scores crowd into few buckets (plateaus of equal scores), a bitonic sort.
 //
 // Selection key: 64-bit composite  (sortable(score) << 32) | (0xFFFFFFFF - id).
 // Fast path (position ids): two scans of the row.  Scan 1 histograms the top 12 key bits; scan 2 sends
@@ -18,7 +20,10 @@ constexpr int kTopkThreads = 1024;
 constexpr int kTopkMaxK = 2048;
 constexpr int kHistBins = 4096;
 constexpr int kCandCap = 4096;
+constexpr int kSortBuckets = 2048;    // buckets of the counting sort over the span of the selected scores
+constexpr int kSortGroupCap = 96;     // largest bucket that is ordered by ranking; beyond it the bitonic sort takes over
 constexpr size_t kTopkSmemBytes = kHistBins * 4 + kTopkMaxK * 8 + kCandCap * 8;
+static_assert(2 * kSortBuckets * 4 <= kHistBins * 4 && 2 * kTopkMaxK <= kCandCap, "the counting sort reuses these areas");
 
 __device__ __forceinline__ int row_count(const TopkParams& p, int row, int& col0) {
   if (p.counts != nullptr) {
@@ -132,7 +137,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   uint64_t* cand = sel + kTopkMaxK;
   __shared__ uint32_t warp_tot[32];
   __shared__ uint32_t s_tmp[4];
-  __shared__ uint32_t s_nsel, s_ncand;
+  __shared__ uint32_t s_nsel, s_ncand, s_kmin, s_kmax, s_maxgroup;
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -147,6 +152,9 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   if (tid == 0) {
     s_nsel = 0;
     s_ncand = 0;
+    s_kmin = 0xFFFFFFFFu;
+    s_kmax = 0u;
+    s_maxgroup = 0u;
   }
   SelectState st{0, 0, static_cast<uint32_t>(min(p.k, n)), false};
   auto from_global = [&](int j, uint64_t& c) -> bool {
@@ -282,8 +290,71 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   }
   __syncthreads();
   const int nsel = min(static_cast<int>(s_nsel), min(p.k, kTopkMaxK));
+  // ---- counting sort on the span of the selected scores, then the rank inside each bucket -----------------------
+  // bucket = (largest key - key) >> shift with the shift that maps the span onto kSortBuckets buckets: bucket 0
+  // holds the largest scores.  Entries land bucket by bucket in arrival order (`grp`), then every entry counts the
+  // larger keys of its bucket (keys are distinct: they carry the id) and takes that slot (`ordered`).
+  uint32_t* bcount = hist;                  // entries per bucket, consumed as fill counters
+  uint32_t* bstart = hist + kSortBuckets;   // first slot of every bucket
+  uint64_t* grp = cand;                     // the candidate list is done with
+  uint64_t* ordered_s = cand + kTopkMaxK;
+  const uint64_t* ordered = sel;
+  bool ranked = false;
+  if (nsel >= 64) {
+    uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
+    for (int i = tid; i < nsel; i += kTopkThreads) {
+      const uint32_t k32 = static_cast<uint32_t>(sel[i] >> 32);
+      kmin = min(kmin, k32);
+      kmax = max(kmax, k32);
+    }
+    kmin = __reduce_min_sync(0xffffffffu, kmin);
+    kmax = __reduce_max_sync(0xffffffffu, kmax);
+    if ((tid & 31) == 0 && kmin <= kmax) {
+      atomicMin(&s_kmin, kmin);
+      atomicMax(&s_kmax, kmax);
+    }
+    for (int i = tid; i < 2 * kSortBuckets; i += kTopkThreads) hist[i] = 0;
+    __syncthreads();
+    kmin = s_kmin;
+    kmax = s_kmax;
+    const uint32_t span = kmax - kmin;
+    const int shift = span < static_cast<uint32_t>(kSortBuckets) ? 0 : (32 - __clz(span)) - 11;   // span >> shift < 2048
+    for (int i = tid; i < nsel; i += kTopkThreads)
+      atomicAdd(&bcount[(kmax - static_cast<uint32_t>(sel[i] >> 32)) >> shift], 1u);
+    __syncthreads();
+    {  // exclusive scan over the buckets, two per thread; the largest bucket decides whether ranking is cheap
+      const uint32_t c0 = bcount[2 * tid], c1 = bcount[2 * tid + 1];
+      uint32_t total;
+      const uint32_t ex = block_exclusive_scan(c0 + c1, warp_tot, total);
+      bstart[2 * tid] = ex;
+      bstart[2 * tid + 1] = ex + c0;
+      const uint32_t mx = __reduce_max_sync(0xffffffffu, max(c0, c1));
+      if ((tid & 31) == 0) atomicMax(&s_maxgroup, mx);
+    }
+    __syncthreads();
+    ranked = s_maxgroup <= static_cast<uint32_t>(kSortGroupCap);
+    if (ranked) {
+      for (int i = tid; i < nsel; i += kTopkThreads) {
+        const uint64_t c = sel[i];
+        const uint32_t b = (kmax - static_cast<uint32_t>(c >> 32)) >> shift;
+        grp[bstart[b] + (atomicSub(&bcount[b], 1u) - 1u)] = c;
+      }
+      __syncthreads();
+      for (int i = tid; i < nsel; i += kTopkThreads) {
+        const uint64_t c = grp[i];
+        const uint32_t b = (kmax - static_cast<uint32_t>(c >> 32)) >> shift;
+        const uint32_t start = bstart[b];
+        const uint32_t end = b + 1 < static_cast<uint32_t>(kSortBuckets) ? bstart[b + 1] : static_cast<uint32_t>(nsel);
+        uint32_t rank = 0;
+        for (uint32_t j = start; j < end; ++j) rank += grp[j] > c ? 1u : 0u;
+        ordered_s[start + rank] = c;
+      }
+      ordered = ordered_s;
+    }
+  }
   int npad = 2;
   while (npad < nsel) npad <<= 1;
+  if (!ranked) {
   for (int i = tid; i < npad; i += kTopkThreads)
     if (i >= nsel) sel[i] = 0ull;
   // ---- bitonic sort, descending ------------------------------------------------------------------------------
@@ -354,10 +425,11 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
       }
     }
   }
+  }  // !ranked
   __syncthreads();
   for (int i = tid; i < p.k; i += kTopkThreads) {
     if (i < nsel) {
-      const uint64_t c = sel[i];
+      const uint64_t c = ordered[i];
       orow[i] = static_cast<int32_t>(0xFFFFFFFFu - static_cast<uint32_t>(c));
       if (osrow) osrow[i] = key_to_float(static_cast<uint32_t>(c >> 32));
     } else {

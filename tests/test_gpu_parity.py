@@ -63,6 +63,31 @@ def test_topk_random_rows_exact_order(n, k):
         assert torch.equal(os_[r, :ref.numel()], sc[r, ref])
 
 
+@pytest.mark.parametrize("n,k", [(65536, 2048), (9000, 2048), (65536, 100)])
+def test_topk_exact_order_across_score_distributions(n, k):
+    """The output order comes from placing the winners by the top 12 key bits and ranking inside a bucket, with the
+    bitonic sort as the fall-back for crowded buckets: rows whose winners spread over many octaves (hundreds of small
+    buckets), over both signs, over one narrow bucket (the fall-back), a row with a plateau of equal scores across
+    the threshold, and one with infinities."""
+    g = torch.Generator().manual_seed(n * 3 + k)
+    sc = torch.empty(6, n)
+    sc[0] = torch.exp(torch.randn(n, generator=g) * 4)                       # many octaves
+    sc[1] = torch.randn(n, generator=g) * torch.exp(torch.randn(n, generator=g) * 3)   # both signs, wide
+    sc[2] = 1.0 + torch.rand(n, generator=g) * 0.01                          # one bucket
+    sc[3] = torch.randn(n, generator=g)
+    sc[3, torch.randperm(n, generator=g)[:min(3 * k, n // 2)]] = 0.75          # plateau around the threshold
+    sc[4] = torch.randn(n, generator=g)
+    sc[4, :7] = float("inf")
+    sc[4, 7:19] = float("-inf")
+    sc[5] = -torch.exp(torch.randn(n, generator=g) * 4)                      # all negative, many octaves
+    counts = torch.full((6,), n, dtype=torch.int32)
+    oi, os_ = _run_topk(sc, counts, k)
+    for r in range(6):
+        ref = orc.topk_indices_ref(sc[r], min(k, n))
+        assert oi[r, :ref.numel()].tolist() == ref.tolist(), (r,)
+        assert torch.equal(os_[r, :ref.numel()], sc[r, ref])
+
+
 def test_topk_explicit_ids_merge_rule():
     g = torch.Generator().manual_seed(9)
     n, k = 4096, 512
