@@ -12,17 +12,34 @@
 // in global memory.  Semantics: pypto.topk as used at
 // models/deepseek_v32_exp/lightning_indexer_quant_impl.py:179-216 with the tie rule of
 // framework/src/interface/interpreter/calculator/calc_torch.cpp:2481-2495.
+//
+// Rows are few in decode (batch x query positions), so a row may be split over the CTAs of a thread-block cluster:
+// every CTA scans its slice of the row (both scans).  After scan 1 each CTA adds the occupied bins of its slice
+// histogram into a merged histogram in every CTA's shared memory, so that all of them find the threshold bucket
+// without a further exchange; after scan 2 each CTA appends its slice lists to those of the cluster's first CTA,
+// which finishes the row alone.  Two cluster barriers lie on the path (a third, at the start, is waited for only
+// after scan 1).
+#include <cooperative_groups.h>
+
 #include "kernels.cuh"
 
 namespace dsv32 {
+
+namespace cg = cooperative_groups;
 
 constexpr int kTopkThreads = 1024;
 constexpr int kTopkMaxK = 2048;
 constexpr int kHistBins = 4096;
 constexpr int kCandCap = 4096;
+constexpr int kSplitMinFloat4 = 12288;  // shortest row (in float4) that is split over a cluster
 constexpr int kSortBuckets = 2048;    // buckets of the counting sort over the span of the selected scores
 constexpr int kSortGroupCap = 96;     // largest bucket that is ordered by ranking; beyond it the bitonic sort takes over
-constexpr size_t kTopkSmemBytes = kHistBins * 4 + kTopkMaxK * 8 + kCandCap * 8;
+constexpr size_t kTopkSmemBytes = kHistBins * 4 + kTopkMaxK * 8 + kCandCap * 8;   // histogram, output list, candidate list
+// A cluster launch adds the merged histogram, and asks for more than half of an SM's shared memory, so that every
+// CTA has an SM to itself: two CTAs that share one run their scans at half the speed each, and the split gains
+// nothing.  The plain launch keeps the small request: what it leaves is L1, where scan 2 finds part of the row.
+constexpr size_t kTopkClusterSmemBytes = 120 * 1024;
+static_assert(kTopkClusterSmemBytes >= kTopkSmemBytes + kHistBins * 4, "room for the merged histogram");
 static_assert(2 * kSortBuckets * 4 <= kHistBins * 4 && 2 * kTopkMaxK <= kCandCap, "the counting sort reuses these areas");
 
 __device__ __forceinline__ int row_count(const TopkParams& p, int row, int& col0) {
@@ -130,16 +147,75 @@ __device__ __forceinline__ void radix_passes(SelectState& st, int first_pass, in
   }
 }
 
-__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p) {
+// Scan 2 over the float4 range [j, hi4) of a row, U float4 per thread and step, for the warps that lie inside the
+// range as a whole; returns the first index this thread has not covered.  An entry is kept when its key is not
+// below `bin_lo`: with flip = 0x80000000 for a threshold among the non-negative scores and 0xFFFFFFFF otherwise
+// that is (bits ^ flip) >= bin_lo, two instructions, and most entries end there.  The kept ones (a few per cent)
+// are then taken one per lane and round: the warp counts winners and threshold-bucket entries by ballot, reserves
+// their slots with one atomic per list and stores them.
+template <int U>
+__device__ __forceinline__ int scan2_chunks(int j, int hi4, const float4* srow4, const float* srow, uint32_t flip,
+                                            uint32_t bin_lo, uint32_t win_lo, bool top_bin, uint32_t idb,
+                                            uint64_t* sel, uint64_t* cand, uint32_t* n_sel, uint32_t* n_cand) {
+  constexpr uint32_t kFull = 0xFFFFFFFFu;
+  const int lane = threadIdx.x & 31;
+  const uint32_t lanes_below = (1u << lane) - 1u;
+  for (; j - lane + 31 + (U - 1) * kTopkThreads < hi4; j += U * kTopkThreads) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = *reinterpret_cast<const uint4*>(srow4 + j + u * kTopkThreads);
+    uint32_t km = 0;   // bit 4u+c: component c of float4 u is kept
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      km |= ((v[u].x ^ flip) >= bin_lo ? 1u : 0u) << (4 * u);
+      km |= ((v[u].y ^ flip) >= bin_lo ? 1u : 0u) << (4 * u + 1);
+      km |= ((v[u].z ^ flip) >= bin_lo ? 1u : 0u) << (4 * u + 2);
+      km |= ((v[u].w ^ flip) >= bin_lo ? 1u : 0u) << (4 * u + 3);
+    }
+    while (__any_sync(kFull, km != 0)) {
+      const bool act = km != 0;
+      bool win = false;
+      uint64_t c = 0;
+      if (act) {
+        const int e = __ffs(km) - 1;
+        km &= km - 1u;
+        const int col = 4 * (j + (e >> 2) * kTopkThreads) + (e & 3);
+        const uint32_t k32 = float_to_key(srow[col]);   // read again (cache hit) rather than indexed out of registers
+        c = (static_cast<uint64_t>(k32) << 32) | static_cast<uint64_t>(0xFFFFFFFFu - (idb + col));
+        win = !top_bin && k32 >= win_lo;
+      }
+      const uint32_t bw = __ballot_sync(kFull, act && win), bt = __ballot_sync(kFull, act && !win);
+      uint32_t base_w = 0, base_t = 0;
+      if (lane == 0) {
+        if (bw) base_w = atomicAdd(n_sel, static_cast<uint32_t>(__popc(bw)));
+        if (bt) base_t = atomicAdd(n_cand, static_cast<uint32_t>(__popc(bt)));
+      }
+      base_w = __shfl_sync(kFull, base_w, 0);
+      base_t = __shfl_sync(kFull, base_t, 0);
+      if (act) {
+        if (win) sel[base_w + __popc(bw & lanes_below)] = c;
+        else cand[base_t + __popc(bt & lanes_below)] = c;
+      }
+    }
+  }
+  return j;
+}
+
+__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p, int csize) {
   extern __shared__ __align__(16) unsigned char topk_smem[];
   uint32_t* hist = reinterpret_cast<uint32_t*>(topk_smem);
   uint64_t* sel = reinterpret_cast<uint64_t*>(topk_smem + kHistBins * 4);
   uint64_t* cand = sel + kTopkMaxK;
+  uint32_t* merged = reinterpret_cast<uint32_t*>(cand + kCandCap);   // the row's histogram when the row is split
   __shared__ uint32_t warp_tot[32];
   __shared__ uint32_t s_tmp[4];
   __shared__ uint32_t s_nsel, s_ncand, s_kmin, s_kmax, s_maxgroup;
+  __shared__ uint32_t s_base[2];    // where this CTA's slice lists go in the first CTA's lists
 
-  const int row = blockIdx.x;
+  // csize CTAs (one cluster; 1 = no cluster, and then no cluster call is made) share a row
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = csize > 1 ? static_cast<int>(cluster.block_rank()) : 0;
+  const int row = blockIdx.x / csize;
   const int tid = threadIdx.x;
   int col0;
   const int n = row_count(p, row, col0);
@@ -169,16 +245,27 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
   };
 
   bool emitted = false;
+  const bool vec = (reinterpret_cast<uintptr_t>(srow) & 15) == 0;
+  const int n4 = vec ? (n >> 2) : 0;
+  // a short row is left to the first CTA (the barriers would cost more than the scans); all CTAs of the cluster decide alike
+  const bool split = csize > 1 && irow == nullptr && n4 >= kSplitMinFloat4;
+  if (!split && crank != 0) return;
   if (n > 0 && irow == nullptr) {
     // ---- fast path: scan 1 = histogram of the top 12 key bits (vectorised when the row is 16-byte aligned) ----
     for (int i = tid; i < kHistBins; i += kTopkThreads) hist[i] = 0;
+    if (split)
+      for (int i = tid; i < kHistBins; i += kTopkThreads) merged[i] = 0;
     __syncthreads();
-    const bool vec = (reinterpret_cast<uintptr_t>(srow) & 15) == 0;
-    const int n4 = vec ? (n >> 2) : 0;
+    if (split) cluster.barrier_arrive();   // "my merged histogram is cleared"; waited for after scan 1
     const float4* srow4 = reinterpret_cast<const float4*>(srow);
+    int lo4 = 0, hi4 = n4;   // this CTA's slice, in float4
+    if (split) {
+      lo4 = static_cast<int>(static_cast<long long>(n4) * crank / csize);
+      hi4 = static_cast<int>(static_cast<long long>(n4) * (crank + 1) / csize);
+    }
     {
-      int j = tid;
-      for (; j + 3 * kTopkThreads < n4; j += 4 * kTopkThreads) {  // four independent loads in flight per thread
+      int j = lo4 + tid;
+      for (; j + 3 * kTopkThreads < hi4; j += 4 * kTopkThreads) {  // four independent loads in flight per thread
         float4 v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) v[u] = srow4[j + u * kTopkThreads];
@@ -190,7 +277,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
           atomicAdd(&hist[float_to_key(v[u].w) >> 20], 1u);
         }
       }
-      for (; j < n4; j += kTopkThreads) {
+      for (; j < hi4; j += kTopkThreads) {
         const float4 v = srow4[j];
         atomicAdd(&hist[float_to_key(v.x) >> 20], 1u);
         atomicAdd(&hist[float_to_key(v.y) >> 20], 1u);
@@ -198,13 +285,33 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
         atomicAdd(&hist[float_to_key(v.w) >> 20], 1u);
       }
     }
-    for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) atomicAdd(&hist[float_to_key(srow[j]) >> 20], 1u);
+    if (crank == 0)
+      for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) atomicAdd(&hist[float_to_key(srow[j]) >> 20], 1u);
     __syncthreads();
+    const uint32_t* row_hist = hist;
+    if (split) {
+      cluster.barrier_wait();   // every CTA's merged histogram is cleared
+      const uint4 mine = reinterpret_cast<const uint4*>(hist)[tid];   // 1024 threads x 4 bins
+      const uint32_t cnt[4] = {mine.x, mine.y, mine.z, mine.w};
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        if (cnt[b] != 0)
+          for (int q = 0; q < csize; ++q) atomicAdd(cluster.map_shared_rank(merged, q) + 4 * tid + b, cnt[b]);
+      cluster.sync();           // all slices are in every merged histogram
+      row_hist = merged;
+    }
+    // mode 0: the first digit settles the row (emission below); 1: scan 2; 2: the threshold bucket does not fit the
+    // candidate list (digit loop over global memory).  The CTAs of a split row all work this out, from equal data.
     uint32_t total;
-    narrow(st, hist, warp_tot, s_tmp, 52, 0xFFFu, total);
-    if (!st.done && s_tmp[2] <= static_cast<uint32_t>(kCandCap)) {
+    narrow(st, row_hist, warp_tot, s_tmp, 52, 0xFFFu, total);
+    const uint32_t mode = st.done ? 0u : (s_tmp[2] <= static_cast<uint32_t>(kCandCap) ? 1u : 2u);
+    const uint32_t bin = static_cast<uint32_t>(st.prefix >> 52);
+    if (mode != 1u && crank != 0) return;   // the first CTA finishes such a row alone; no cluster call follows
+    if (mode == 1u) {
       // ---- scan 2: winners go to the output list, the threshold bucket to the candidate list ---------------
-      const uint32_t bin = static_cast<uint32_t>(st.prefix >> 52);
+      const uint32_t bin_lo = bin << 20, win_lo = (bin + 1u) << 20;   // smallest keys of the threshold bucket / of the next
+      const bool top_bin = bin == 0xFFFu;                              // no bucket above the topmost one
+      const uint32_t flip = (bin_lo & 0x80000000u) ? 0x80000000u : 0xFFFFFFFFu;
       auto place = [&](float s, int j) {
         const uint32_t k32 = float_to_key(s);
         const uint32_t b = k32 >> 20;
@@ -214,42 +321,10 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
         else cand[atomicAdd(&s_ncand, 1u)] = c;
       };
       {
-        int j = tid;
-        for (; j + 3 * kTopkThreads < n4; j += 4 * kTopkThreads) {
-          // sixteen entries per thread: count first, reserve the slots of both lists with one atomic each,
-          // then store -- instead of one divergent atomic per entry
-          float4 v[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) v[u] = srow4[j + u * kTopkThreads];
-          uint32_t nw = 0, nt = 0;
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t b = float_to_key(f[q]) >> 20;
-              nw += (b > bin) ? 1u : 0u;
-              nt += (b == bin) ? 1u : 0u;
-            }
-          }
-          if ((nw | nt) == 0) continue;
-          uint32_t pw = nw ? atomicAdd(&s_nsel, nw) : 0u;
-          uint32_t pt = nt ? atomicAdd(&s_ncand, nt) : 0u;
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t k32 = float_to_key(f[q]);
-              const uint32_t b = k32 >> 20;
-              const uint64_t c = (static_cast<uint64_t>(k32) << 32) |
-                                 static_cast<uint64_t>(0xFFFFFFFFu - (idb + 4 * (j + u * kTopkThreads) + q));
-              if (b > bin) sel[pw++] = c;
-              else if (b == bin) cand[pt++] = c;
-            }
-          }
-        }
-        for (; j < n4; j += kTopkThreads) {
+        int j = lo4 + tid;
+        j = scan2_chunks<4>(j, hi4, srow4, srow, flip, bin_lo, win_lo, top_bin, idb, sel, cand, &s_nsel, &s_ncand);
+        j = scan2_chunks<1>(j, hi4, srow4, srow, flip, bin_lo, win_lo, top_bin, idb, sel, cand, &s_nsel, &s_ncand);
+        for (; j < hi4; j += kTopkThreads) {   // the warp that straddles the end of the slice
           const float4 v = srow4[j];
           place(v.x, 4 * j);
           place(v.y, 4 * j + 1);
@@ -257,8 +332,25 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
           place(v.w, 4 * j + 3);
         }
       }
-      for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) place(srow[j], j);
+      if (crank == 0)
+        for (int j = n4 * 4 + tid; j < n; j += kTopkThreads) place(srow[j], j);
       __syncthreads();
+      if (split) {
+        if (crank != 0) {   // append this slice's lists to the first CTA's
+          const uint32_t nw = s_nsel, nt = s_ncand;
+          if (tid == 0) {
+            s_base[0] = nw ? atomicAdd(cluster.map_shared_rank(&s_nsel, 0), nw) : 0u;
+            s_base[1] = nt ? atomicAdd(cluster.map_shared_rank(&s_ncand, 0), nt) : 0u;
+          }
+          __syncthreads();
+          uint64_t* sel0 = cluster.map_shared_rank(sel, 0) + s_base[0];
+          uint64_t* cand0 = cluster.map_shared_rank(cand, 0) + s_base[1];
+          for (uint32_t i = tid; i < nw; i += kTopkThreads) sel0[i] = sel[i];
+          for (uint32_t i = tid; i < nt; i += kTopkThreads) cand0[i] = cand[i];
+        }
+        cluster.sync();   // the first CTA holds all lists; the others are done
+        if (crank != 0) return;
+      }
       const int ncand = static_cast<int>(s_ncand);
       auto from_cand = [&](int j, uint64_t& c) -> bool {
         c = cand[j];
@@ -270,7 +362,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
         if ((c & st.mask) >= st.prefix) sel[atomicAdd(&s_nsel, 1u)] = c;
       }
       emitted = true;
-    } else if (!st.done) {
+    } else if (mode == 2u) {
       radix_passes(st, 1, n, from_global, hist, warp_tot, s_tmp);  // bucket too large for the candidate list
     }
   } else if (n > 0) {
@@ -441,8 +533,54 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p)
 
 int launch_topk(const TopkParams& p, int rows, cudaStream_t stream) {
   if (rows <= 0) return DSV32_OK;
-  cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTopkSmemBytes);
-  topk_select_kernel<<<rows, kTopkThreads, kTopkSmemBytes, stream>>>(p);
+  cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTopkClusterSmemBytes);
+  // A cluster per row while rows are few: the largest of 8/4/2 CTAs for which the device can hold all rows'
+  // clusters at once (a CTA fills an SM, and a cluster has to find its SMs within one GPC).  Rows with explicit
+  // ids, and short rows, are not split.
+  static int room[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // room[c]: clusters of c CTAs the device holds at once; 0 = not asked yet
+  int csize = 1;
+  const int longest = p.counts != nullptr ? p.ld : min(p.ld, p.key_end) - p.key_begin;   // no row has more entries
+  if (p.ids == nullptr && longest / 4 >= kSplitMinFloat4)
+    for (int c = 8; c > 1; c >>= 1) {
+      if (room[c] == 0) {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(c);
+        probe.blockDim = dim3(kTopkThreads);
+        probe.dynamicSmemBytes = kTopkClusterSmemBytes;
+        cudaLaunchAttribute pattr;
+        pattr.id = cudaLaunchAttributeClusterDimension;
+        pattr.val.clusterDim.x = c;
+        pattr.val.clusterDim.y = 1;
+        pattr.val.clusterDim.z = 1;
+        probe.attrs = &pattr;
+        probe.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, topk_select_kernel, &probe);
+        if (e != cudaSuccess) cudaGetLastError();
+        room[c] = (e == cudaSuccess && clusters > 0) ? clusters : -1;
+      }
+      if (rows <= room[c]) {
+        csize = c;
+        break;
+      }
+    }
+  if (csize == 1) {
+    topk_select_kernel<<<rows, kTopkThreads, kTopkSmemBytes, stream>>>(p, 1);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * csize);
+    cfg.blockDim = dim3(kTopkThreads);
+    cfg.dynamicSmemBytes = kTopkClusterSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = csize;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, topk_select_kernel, p, csize);
+  }
   count_launch();
   return check_launch("topk_select_kernel");
 }

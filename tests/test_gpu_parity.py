@@ -88,6 +88,32 @@ def test_topk_exact_order_across_score_distributions(n, k):
         assert torch.equal(os_[r, :ref.numel()], sc[r, ref])
 
 
+@pytest.mark.parametrize("rows,ld", [(2, 65536), (20, 65536), (40, 65536), (5, 65537), (3, 131072 + 36)])
+def test_topk_rows_split_over_a_cluster(rows, ld):
+    """While rows are few and long, a row is scanned by the 8, 4 or 2 CTAs of a cluster (fewer CTAs as rows grow).
+    One launch mixes rows that are split with rows that are not: a short one, an empty one, rows whose start is
+    not 16-byte aligned (odd row pitch), a row of one narrow bucket (the threshold bucket overflows the candidate
+    list and the first CTA finishes alone) and a plateau across the threshold."""
+    k = 2048
+    g = torch.Generator().manual_seed(rows * 7 + ld)
+    sc = torch.randn(rows, ld, generator=g)
+    counts = torch.full((rows,), ld, dtype=torch.int32)
+    counts[0] = ld - 5
+    if rows > 2:
+        counts[1] = 3000                                             # short: left to the first CTA
+        sc[2] = 2.0 + torch.rand(ld, generator=g) * 0.001            # one bucket
+    if rows > 4:
+        counts[3] = 0
+        sc[4, torch.randperm(ld, generator=g)[:3 * k]] = 1.25          # plateau around the threshold
+    oi, os_ = _run_topk(sc, counts, k)
+    for r in range(rows):
+        c = int(counts[r])
+        ref = orc.topk_indices_ref(sc[r, :c], min(k, c))
+        assert oi[r, :ref.numel()].tolist() == ref.tolist(), (r,)
+        assert (oi[r, ref.numel():] == -1).all()
+        assert torch.equal(os_[r, :ref.numel()], sc[r, ref])
+
+
 def test_topk_explicit_ids_merge_rule():
     g = torch.Generator().manual_seed(9)
     n, k = 4096, 512
