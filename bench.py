@@ -10,8 +10,8 @@ config 2 (default)  full decode chain, batch 64, context 64K, 2 query tokens per
                     one rank per GPU, no collective on the data path) the 64 requests are SPLIT over the ranks
                     ("strong"); the figure with 64 requests on every rank is printed beside it as "weak".
 config 3            one request, 128K keys, a 4096-token query chunk: the index-key range is sharded over the ranks,
-                    per-rank top-2048 candidates are all-gathered (NCCL) and re-selected, attention runs on the rank
-                    that owns each query slice.
+                    every rank sends each peer its top-2048 candidates for that peer's query slice (one NCCL all-to-all), the
+                    candidates are re-selected, attention runs on the rank that owns each query slice.
 config 4            ragged production decode, batch 256, context lengths log-uniform in [1K, 128K] (10 % below 2048),
                     requests assigned to ranks by longest-processing-time-first on their cost.
 One step = one pass of the chain over the batch.  The metric is decode tokens/s (whole job, all ranks).  Every
@@ -216,8 +216,9 @@ def workload_config(args, world):
         return {"workload": f"config 3: one request, {args.ctx} keys, {args.s1}-token query chunk, 128 heads, top-k {TOPK}: "
                             f"lightning indexer over a sharded key range + candidate merge + SFA",
                 "ctx": args.ctx, "s1": args.s1, "topk": TOPK, "global_batch": 1,
-                "parallelism": f"index-key range sharded over {world} GPU(s); one all-gather of (score, index) "
-                               f"candidates; attention on the rank that owns each query slice",
+                "parallelism": f"index-key range sharded over {world} GPU(s); one all-to-all of (score, index) "
+                               f"candidates (each rank receives those of its own query slice); attention on the "
+                               f"rank that owns each query slice",
                 "l2_policy": "L2 flushed between steps (a 256 MB buffer is overwritten)"}
     name = "config 2: full decode chain" if args.config == 2 else \
         "config 4: ragged decode chain (ctx log-uniform 1K..128K, 10 % below 2048, LPT assignment)"
@@ -613,8 +614,9 @@ def run_config3(args, rank, world, local_rank):
     begin, end = sharding.key_range_for_rank(L, rank, world)
     res = torch.empty((s1, 1, TOPK), dtype=torch.int32, device=dev)
     sc = torch.empty((s1, TOPK), dtype=torch.float32, device=dev)
-    packed = torch.empty((2, s1, TOPK), dtype=torch.int32, device=dev)
-    gathered = torch.empty((world, 2, s1, TOPK), dtype=torch.int32, device=dev) if world > 1 else None
+    per = math.ceil(s1 / world)
+    a2a_send = torch.empty((world, 2, per, TOPK), dtype=torch.int32, device=dev) if world > 1 else None
+    a2a_recv = torch.empty_like(a2a_send) if world > 1 else None
     counts = torch.full((n_own,), world * TOPK, dtype=torch.int32, device=dev)
     merged = torch.empty((n_own, TOPK), dtype=torch.int32, device=dev)
     merged_sc = torch.empty((n_own, TOPK), dtype=torch.float32, device=dev)
@@ -632,13 +634,9 @@ def run_config3(args, rank, world, local_rank):
                             d["block_table"], res, TOPK, topk_scores=sc, key_begin=begin, key_end=end)
         e[1].record()
         if world > 1:
-            packed[0].copy_(sc.view(torch.int32))
-            packed[1].copy_(res.reshape(s1, TOPK))
-            dist.all_gather_into_tensor(gathered, packed)
+            # candidates of this rank's own query slice from every rank, one row per token: [n_own, world * topk]
+            cs, ci = sharding.exchange_own_slice(sc, res.reshape(s1, TOPK), send=a2a_send, recv=a2a_recv)
             e[2].record()
-            # candidates of this rank's own query slice, one row per token: [n_own, world * topk]
-            cs = gathered[:, 0, t0:t1].permute(1, 0, 2).reshape(n_own, world * TOPK).view(torch.float32)
-            ci = gathered[:, 1, t0:t1].permute(1, 0, 2).reshape(n_own, world * TOPK)
             if n_own:
                 topk_select(cs.contiguous(), counts, TOPK, ids=ci.contiguous(), out_idx=merged, out_scores=merged_sc)
             sel = merged
@@ -677,7 +675,7 @@ def run_config3(args, rank, world, local_rank):
         peaks = load_peaks()
         ms_step = stats["median"]
         value = s1 / (ms_step * 1e-3)
-        sent = 2 * s1 * TOPK * 4
+        sent = 2 * per * TOPK * 4 * (world - 1)   # bytes this rank sends to its peers (and receives from them)
         k_valid = [min(TOPK, max(L - s1 + 1 + i, 0)) for i in range(t0, t1)]
         sfa_flops = sum(sfa_flops_per_token(k) for k in k_valid)
         t_sfa = phase["sfa"] * 1e-3
@@ -689,15 +687,15 @@ def run_config3(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
             "ms_per_step": ms_step, "ms_per_step_spread": stats, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
-            "phases_ms": {"indexer_topk_local": phase["indexer"], "all_gather": phase["gather"],
+            "phases_ms": {"indexer_topk_local": phase["indexer"], "all_to_all": phase["gather"],
                           "merge_topk": phase["merge"], "sfa_own_slice": phase["sfa"],
-                          "all_gather_share": phase["gather"] / ms_step},
+                          "all_to_all_share": phase["gather"] / ms_step},
             "nvlink": None if world == 1 else {
-                "bytes_sent_per_rank": sent, "bytes_received_per_rank": sent * (world - 1),
-                "achieved_gbs_per_direction": sent * (world - 1) / (phase["gather"] * 1e-3) / 1e9,
+                "bytes_sent_per_rank": sent, "bytes_received_per_rank": sent,
+                "achieved_gbs_per_direction": sent / (phase["gather"] * 1e-3) / 1e9,
                 "peak_gbs_per_direction": NVLINK_PEER_GBS,
-                "frac": sent * (world - 1) / (phase["gather"] * 1e-3) / 1e9 / NVLINK_PEER_GBS,
-                "note": "the all-gather phase also holds two small packing copies"},
+                "frac": sent / (phase["gather"] * 1e-3) / 1e9 / NVLINK_PEER_GBS,
+                "note": "the all-to-all phase also holds the packing copies into the send buffer"},
             "roofline": {"kernel": "sfa_tc_kernel", "bound": "tensor", "achieved": sfa_flops / t_sfa / 1e12 if t_sfa > 0 else None,
                          "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": sfa_flops / t_sfa / 1e12 / peaks["bf16_tflops_sustained"] if t_sfa > 0 else None,

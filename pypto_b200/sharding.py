@@ -3,10 +3,14 @@
 * Decode batches shard by request with no collective: `split_even` / `lpt_assign` decide which rank owns
   which request (each rank keeps its requests' cache pages in its own pool).
 * A single long request shards the index-key RANGE: every rank scores all query tokens against its block
-  range, emits a local top-k with scores, the candidates are all-gathered and every rank re-selects the
-  global top-k (exact: the global top-k is a subset of the union of the local top-ks; ties go to the lower
-  global index).  The reference indexer is single-device (lightning_indexer_quant_impl.py:31-32), so this
-  has no reference counterpart; its result equals the unsharded operator's.
+  range, emits a local top-k with scores, and the global top-k is re-selected from the ranks' candidates
+  (exact: the global top-k is a subset of the union of the local top-ks; ties go to the lower global
+  index).  The attention of the request's query tokens is sharded by token slice, so a rank only needs the
+  candidates of ITS slice: one all-to-all (`exchange_own_slice`: every rank sends each peer the candidates
+  of that peer's tokens, 1/world of what an all-gather would move per link); `sharded_indexer_topk` keeps the
+  all-gather form for callers that want the selection of every token on every rank.  The reference indexer
+  is single-device (lightning_indexer_quant_impl.py:31-32), so this has no reference counterpart; its result
+  equals the unsharded operator's.
 """
 from __future__ import annotations
 
@@ -109,4 +113,60 @@ def sharded_indexer_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scal
     dist.all_gather(gathered, packed, group=group)
     cand_sc = torch.cat([g[0].view(torch.float32) for g in gathered], dim=1)
     cand_id = torch.cat([g[1] for g in gathered], dim=1)
+    return merge_fn(cand_sc, cand_id, selected_count)
+
+
+def exchange_own_slice(scores: torch.Tensor, idx: torch.Tensor, group=None, send=None, recv=None):
+    """All-to-all of local top-k candidates: `scores` fp32 / `idx` int32 [n_tokens, k] of ALL query tokens over this
+    rank's key range go out so that every rank ends up with the candidates of its own token slice
+    (`token_slice_for_rank`) from every rank.  Returns (cand_scores fp32, cand_ids int32), each [n_own, world * k],
+    rank-major along the second axis.  Token slices are padded to a common length on the wire (pad ids are -1, which
+    the merge ignores).  `send` / `recv` are optional reusable int32 buffers [world, 2, per, k]."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    n_tokens, k = idx.shape
+    per = math.ceil(n_tokens / world)
+    t0, t1 = token_slice_for_rank(n_tokens, rank, world)
+    if send is None:
+        send = torch.empty((world, 2, per, k), dtype=torch.int32, device=idx.device)
+    if recv is None:
+        recv = torch.empty_like(send)
+    full = (n_tokens // per) if per else 0          # peers whose slice is complete
+    if full:
+        send[:full, 0].copy_(scores[:full * per].view(torch.int32).view(full, per, k))
+        send[:full, 1].copy_(idx[:full * per].view(full, per, k))
+    if full < world:                                # a ragged last slice, and empty ones after it
+        rem = n_tokens - full * per
+        send[full:, 1].fill_(-1)
+        send[full:, 0].zero_()
+        if rem:
+            send[full, 0, :rem].copy_(scores[full * per:].view(torch.int32))
+            send[full, 1, :rem].copy_(idx[full * per:])
+    dist.all_to_all_single(recv.view(-1), send.view(-1), group=group)
+    n_own = t1 - t0
+    cand_sc = recv[:, 0, :n_own].permute(1, 0, 2).reshape(n_own, world * k).view(torch.float32)
+    cand_id = recv[:, 1, :n_own].permute(1, 0, 2).reshape(n_own, world * k)
+    return cand_sc, cand_id
+
+
+def sharded_indexer_topk_own_slice(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
+                                   block_table, selected_count: int = 2048, group=None,
+                                   local_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None):
+    """Key-range-sharded lightning indexer for a request whose attention is sharded by query-token slice: every rank
+    passes the same query-side tensors and a cache that holds (at least) its own block range, and gets the global
+    top-k [n_own, selected_count] int32 of ITS token slice (`token_slice_for_rank`), equal to the rows the
+    unsharded operator computes for those tokens."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    local_fn = local_fn or _cuda_local_topk
+    merge_fn = merge_fn or _cuda_merge
+    max_ctx = block_table.shape[1] * 128
+    begin, end = key_range_for_rank(max_ctx, rank, world)
+    idx, sc = local_fn(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key, block_table,
+                       selected_count, begin, end)
+    if world == 1:
+        return idx
+    cand_sc, cand_id = exchange_own_slice(sc, idx.to(torch.int32), group=group)
+    if cand_sc.shape[0] == 0:
+        return cand_id[:, :selected_count]
     return merge_fn(cand_sc, cand_id, selected_count)

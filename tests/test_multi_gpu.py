@@ -38,6 +38,10 @@ def _long_request(rank, world):
     d = synth.make_long_request(L, s1, 31, dev, token_slice=(t0, t1))
     idx = sharding.sharded_indexer_topk(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"],
                                         d["act_seq"], d["block_table"], k)
+    # the all-to-all form gives this rank the same rows for its own token slice
+    own = sharding.sharded_indexer_topk_own_slice(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"],
+                                                  d["act_seq"], d["block_table"], k)
+    assert torch.equal(own, idx[t0:t1])
     out = torch.empty((1, t1 - t0, 128, 512), dtype=torch.bfloat16, device=dev)
     act_slice = torch.tensor([L - s1 + t1], dtype=torch.int32, device=dev)
     sparse_flash_attention_quant_d(d["q_nope"], d["q_rope"], d["k_nope"], d["k_rope"], d["k_scales"],
