@@ -615,8 +615,24 @@ def run_config3(args, rank, world, local_rank):
     res = torch.empty((s1, 1, TOPK), dtype=torch.int32, device=dev)
     sc = torch.empty((s1, TOPK), dtype=torch.float32, device=dev)
     per = math.ceil(s1 / world)
-    a2a_send = torch.empty((world, 2, per, TOPK), dtype=torch.int32, device=dev) if world > 1 else None
-    a2a_recv = torch.empty_like(a2a_send) if world > 1 else None
+    # candidate exchange: the top-k kernel stores every token's row straight into the owning rank's symmetric-memory
+    # buffer ("peer stores": no collective, a barrier), or one NCCL all-to-all where symmetric memory is unavailable
+    bufs, exchange = None, "none"
+    if world > 1:
+        exchange = "nccl all-to-all"
+        if args.c3_exchange == "peer":
+            try:
+                bufs = sharding.PeerCandidateBuffers(s1, TOPK, dev)
+                exchange = "peer stores from the top-k kernel (symmetric memory), one barrier"
+            except Exception as e:  # noqa: BLE001
+                sys.stderr.write(f"config 3: symmetric memory unavailable ({type(e).__name__}: {e}); using the all-to-all\n")
+        # every rank must take the same path
+        flag = torch.tensor([1 if bufs is not None else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            bufs, exchange = None, "nccl all-to-all"
+    a2a_send = torch.empty((world, 2, per, TOPK), dtype=torch.int32, device=dev) if world > 1 and bufs is None else None
+    a2a_recv = torch.empty_like(a2a_send) if a2a_send is not None else None
     counts = torch.full((n_own,), world * TOPK, dtype=torch.int32, device=dev)
     merged = torch.empty((n_own, TOPK), dtype=torch.int32, device=dev)
     merged_sc = torch.empty((n_own, TOPK), dtype=torch.float32, device=dev)
@@ -630,13 +646,23 @@ def run_config3(args, rank, world, local_rank):
     def step(i, record=True):
         e = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         e[0].record()
-        indexer_scores_topk(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"], d["act_seq"],
-                            d["block_table"], res, TOPK, topk_scores=sc, key_begin=begin, key_end=end)
-        e[1].record()
-        if world > 1:
-            # candidates of this rank's own query slice from every rank, one row per token: [n_own, world * topk]
-            cs, ci = sharding.exchange_own_slice(sc, res.reshape(s1, TOPK), send=a2a_send, recv=a2a_recv)
+        if bufs is not None:
+            bufs.barrier()   # nobody is still merging the previous step's candidates
+            indexer_scores_topk(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"], d["act_seq"],
+                                d["block_table"], None, TOPK, key_begin=begin, key_end=end, scatter=bufs.scatter_arg())
+            e[1].record()
+            bufs.barrier()
             e[2].record()
+            cs, ci = bufs.own()
+        else:
+            indexer_scores_topk(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"], d["act_seq"],
+                                d["block_table"], res, TOPK, topk_scores=sc, key_begin=begin, key_end=end)
+            e[1].record()
+        if world > 1:
+            if bufs is None:
+                # candidates of this rank's own query slice from every rank, one row per token: [n_own, world * topk]
+                cs, ci = sharding.exchange_own_slice(sc, res.reshape(s1, TOPK), send=a2a_send, recv=a2a_recv)
+                e[2].record()
             if n_own:
                 topk_select(cs.contiguous(), counts, TOPK, ids=ci.contiguous(), out_idx=merged, out_scores=merged_sc)
             sel = merged
@@ -687,15 +713,17 @@ def run_config3(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
             "ms_per_step": ms_step, "ms_per_step_spread": stats, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
-            "phases_ms": {"indexer_topk_local": phase["indexer"], "all_to_all": phase["gather"],
+            "phases_ms": {"indexer_topk_local": phase["indexer"], "exchange": phase["gather"],
                           "merge_topk": phase["merge"], "sfa_own_slice": phase["sfa"],
-                          "all_to_all_share": phase["gather"] / ms_step},
+                          "exchange_share": phase["gather"] / ms_step, "exchange_form": exchange},
             "nvlink": None if world == 1 else {
                 "bytes_sent_per_rank": sent, "bytes_received_per_rank": sent,
                 "achieved_gbs_per_direction": sent / (phase["gather"] * 1e-3) / 1e9,
                 "peak_gbs_per_direction": NVLINK_PEER_GBS,
                 "frac": sent / (phase["gather"] * 1e-3) / 1e9 / NVLINK_PEER_GBS,
-                "note": "the all-to-all phase also holds the packing copies into the send buffer"},
+                "note": ("with peer stores the bytes cross NVLink inside the top-k kernel of the indexer phase; the exchange "
+                         "phase is the barrier alone, so achieved / frac are not a link bandwidth") if bufs is not None else
+                        "the all-to-all phase also holds the packing copies into the send buffer"},
             "roofline": {"kernel": "sfa_tc_kernel", "bound": "tensor", "achieved": sfa_flops / t_sfa / 1e12 if t_sfa > 0 else None,
                          "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": sfa_flops / t_sfa / 1e12 / peaks["bf16_tflops_sustained"] if t_sfa > 0 else None,
@@ -915,6 +943,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-timed-ms", type=float, default=500.0, help="keep timing rounds of --steps until this much "
                     "timed region has accumulated (profiling runs pass 0: three rounds)")
+    ap.add_argument("--c3-exchange", default="peer", choices=["peer", "a2a"],
+                    help="config 3: how the ranks' top-k candidates reach the rank that owns a token")
     ap.add_argument("--kv-splits", type=int, default=0, help="fix the key splits of the attention kernel (0: automatic)")
     args = ap.parse_args()
     defaults = {2: (64, 65536, 2), 3: (1, 131072, 4096), 4: (256, None, 2)}[args.config]

@@ -178,6 +178,31 @@ size_t dsv32_indexer_workspace_bytes(int32_t b, int32_t s1, int32_t max_blocks, 
 int dsv32_indexer_topk(const Dsv32IndexerArgs* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The same operator as one stage of a key-range-sharded indexer over several GPUs of a node
+ * (no counterpart in the reference, whose indexer is single-device:
+ * lightning_indexer_quant_impl.py:31-32).  One request (b = 1) whose s1 query tokens are
+ * owned by ranks in consecutive slices of tokens_per_rank tokens: every rank scores all
+ * tokens against its own key range (key_begin / key_end) and the top-k kernel stores a
+ * token's row -- indices and scores -- straight into the buffers of the rank that owns the
+ * token: idx_ptrs[owner] int32 / score_ptrs[owner] fp32, each
+ * [tokens_per_rank, world, selected_count], at [token - owner * tokens_per_rank][rank].
+ * The pointers of the other ranks are peer-mapped device addresses (symmetric memory or
+ * CUDA IPC); the stores are plain st.global, carried by NVLink.  Nothing is exchanged
+ * afterwards: once every rank's call has completed (a barrier across the ranks, stream-
+ * ordered after this call), each rank holds world * selected_count candidates per own token
+ * and re-selects with dsv32_topk_select (explicit ids).  args.topk_res / topk_scores are
+ * ignored.  At most 8 ranks.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t world, rank, tokens_per_rank;
+  int32_t reserved;
+  void* idx_ptrs[8];     /* int32 [tokens_per_rank, world, selected_count] on rank r */
+  void* score_ptrs[8];   /* fp32  [tokens_per_rank, world, selected_count] on rank r */
+} Dsv32TopkScatter;
+
+int dsv32_indexer_topk_scatter(const Dsv32IndexerArgs* args, const Dsv32TopkScatter* scatter, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------
  * The same operator for callers that must not allocate device memory (no counterpart in the
  * reference, whose launcher always allocates its workspace through a callback).  The fp32
  * score rows -- the operator's only scratch -- are kept in a fixed array inside the library

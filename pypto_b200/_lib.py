@@ -108,6 +108,11 @@ class GemmI8Args(C.Structure):
                 ("n", c_i32)]
 
 
+class TopkScatter(C.Structure):
+    _fields_ = [("world", c_i32), ("rank", c_i32), ("tokens_per_rank", c_i32), ("reserved", c_i32),
+                ("idx_ptrs", c_void_p * 8), ("score_ptrs", c_void_p * 8)]
+
+
 class IndexerArgs(C.Structure):
     _fields_ = [
         ("idx_query", c_void_p), ("idx_query_scale", c_void_p), ("idx_key_cache", c_void_p),
@@ -171,6 +176,7 @@ EXPORTS = {
     "dsv32_indexer_workspace_bytes": (c_size_t, [c_i32, c_i32, c_i32, c_i32]),
     "dsv32_indexer_topk": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
     "dsv32_indexer_topk_noalloc": (c_i32, [C.POINTER(IndexerArgs), c_void_p]),
+    "dsv32_indexer_topk_scatter": (c_i32, [C.POINTER(IndexerArgs), C.POINTER(TopkScatter), c_void_p]),
     "dsv32_topk_select": (c_i32, [C.POINTER(TopkArgs), c_void_p]),
     "dsv32_indexer_prolog_v4": (c_i32, [C.POINTER(PrologV4Args), c_void_p]),
     "dsv32_prolog_v4_workspace_bytes": (c_size_t, [c_i32, c_i32]),

@@ -265,7 +265,27 @@ size_t dsv32_indexer_workspace_bytes(int32_t b, int32_t s1, int32_t max_blocks, 
   return align_up(static_cast<size_t>(b) * s1 * max_blocks * block_size * sizeof(float), 256);
 }
 
-int dsv32_indexer_topk(const Dsv32IndexerArgs* a, void* cuda_stream) {
+static int indexer_topk_run(const Dsv32IndexerArgs* a, const Dsv32TopkScatter* sc, void* cuda_stream);
+
+int dsv32_indexer_topk(const Dsv32IndexerArgs* a, void* cuda_stream) { return indexer_topk_run(a, nullptr, cuda_stream); }
+
+int dsv32_indexer_topk_scatter(const Dsv32IndexerArgs* a, const Dsv32TopkScatter* sc, void* cuda_stream) {
+  REQUIRE(a != nullptr && sc != nullptr, "indexer scatter: args is NULL");
+  REQUIRE(a->b == 1, "indexer scatter: one request (b=%d)", a->b);
+  REQUIRE(sc->world >= 1 && sc->world <= 8 && sc->rank >= 0 && sc->rank < sc->world,
+          "indexer scatter: bad world=%d rank=%d (at most 8 ranks)", sc->world, sc->rank);
+  REQUIRE(sc->tokens_per_rank >= 1 && static_cast<long long>(sc->tokens_per_rank) * sc->world >= a->s1,
+          "indexer scatter: tokens_per_rank=%d x world=%d does not cover s1=%d", sc->tokens_per_rank, sc->world, a->s1);
+  REQUIRE(a->selected_count >= 1 && a->selected_count <= 2048, "indexer scatter: selected_count=%d must be in [1, 2048]",
+          a->selected_count);
+  for (int r = 0; r < sc->world; ++r)
+    REQUIRE(sc->idx_ptrs[r] != nullptr && sc->score_ptrs[r] != nullptr &&
+                reinterpret_cast<uintptr_t>(sc->idx_ptrs[r]) % 16 == 0 && reinterpret_cast<uintptr_t>(sc->score_ptrs[r]) % 16 == 0,
+            "indexer scatter: NULL or unaligned buffer of rank %d", r);
+  return indexer_topk_run(a, sc, cuda_stream);
+}
+
+static int indexer_topk_run(const Dsv32IndexerArgs* a, const Dsv32TopkScatter* sc, void* cuda_stream) {
   REQUIRE(a != nullptr, "indexer: args is NULL");
   REQUIRE(a->b >= 0 && a->s1 >= 1, "indexer: bad b=%d s1=%d", a->b, a->s1);
   if (a->b == 0) return DSV32_OK;
@@ -310,8 +330,17 @@ int dsv32_indexer_topk(const Dsv32IndexerArgs* a, void* cuda_stream) {
   p.key_begin = a->key_begin;
   p.key_end = a->key_end;
   int rc = launch_indexer_scores_tc(p, st);
-  if (rc != DSV32_OK || a->topk_res == nullptr) return rc;
+  if (rc != DSV32_OK || (a->topk_res == nullptr && sc == nullptr)) return rc;
   TopkParams tp{};
+  if (sc != nullptr) {
+    tp.scatter_world = sc->world;
+    tp.scatter_rank = sc->rank;
+    tp.scatter_per = sc->tokens_per_rank;
+    for (int r = 0; r < sc->world; ++r) {
+      tp.scatter_idx[r] = static_cast<int32_t*>(sc->idx_ptrs[r]);
+      tp.scatter_sc[r] = static_cast<float*>(sc->score_ptrs[r]);
+    }
+  }
   tp.scores = scores;
   tp.ids = nullptr;
   tp.counts = nullptr;

@@ -13,6 +13,12 @@ struct TopkParams {
   float* out_scores;
   int s1, key_begin, key_end;
   int ld, k, id_base;
+  // Key-range-sharded indexer of one long request (scatter_world > 0): row = query token; the row's results do not go
+  // to out_idx / out_scores but into the buffers of the rank that owns the token (tokens_per_rank consecutive tokens
+  // each), at [token - first token of the owner][this rank][k] -- plain stores, over NVLink for the other ranks.
+  int scatter_world, scatter_rank, scatter_per;
+  int32_t* scatter_idx[8];
+  float* scatter_sc[8];
 };
 int launch_topk(const TopkParams& p, int rows, cudaStream_t stream);
 

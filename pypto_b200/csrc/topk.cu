@@ -224,6 +224,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(TopkParams p,
   const uint32_t idb = static_cast<uint32_t>(col0 + p.id_base);
   int32_t* orow = p.out_idx + static_cast<size_t>(row) * p.k;
   float* osrow = p.out_scores ? p.out_scores + static_cast<size_t>(row) * p.k : nullptr;
+  if (p.scatter_world > 0) {   // the row goes to the rank that owns this token
+    const int owner = row / p.scatter_per;
+    const size_t at = (static_cast<size_t>(row - owner * p.scatter_per) * p.scatter_world + p.scatter_rank) * p.k;
+    orow = p.scatter_idx[owner] + at;
+    osrow = p.scatter_sc[owner] + at;
+  }
 
   if (tid == 0) {
     s_nsel = 0;

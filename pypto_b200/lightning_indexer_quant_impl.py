@@ -33,10 +33,12 @@ class LightningIndexerConfigs:
 
 def indexer_scores_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
                         block_table, topk_res=None, selected_count=2048, *, topk_scores=None, scores_out=None,
-                        dots_out=None, key_begin=0, key_end=INT32_MAX):
+                        dots_out=None, key_begin=0, key_end=INT32_MAX, scatter=None):
     """Scores + top-k with the optional extra outputs of the C ABI (see include/dsv32_b200.h):
     `topk_scores` (scores of the selected keys), `scores_out` (full fp32 score rows), `dots_out`
-    (raw int32 dot products, verification only) and a logical key range for key-range sharding."""
+    (raw int32 dot products, verification only) and a logical key range for key-range sharding.
+    `scatter` = (world, rank, tokens_per_rank, idx_ptrs, score_ptrs): the rows go to the owning ranks' peer-mapped
+    candidate buffers instead of topk_res (dsv32_indexer_topk_scatter)."""
     rt.require_cuda()
     rt.check_tensor(idx_query, "idx_query", torch.int8, (None, 64, 128))
     t = idx_query.shape[0]
@@ -85,7 +87,16 @@ def indexer_scores_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale
             rt.ptr(idx_weight), rt.ptr(act_seq_key), rt.ptr(block_table), rt.ptr(topk_res), rt.ptr(topk_scores),
             rt.ptr(scores_out), rt.ptr(dots_out), rt.ptr(ws), int(ws_bytes), rt.ptr(rt.status_word(dev)), nblk, b, s1,
             128, max_blocks, int(selected_count), ld, int(key_begin), int(min(key_end, INT32_MAX)))
-        rt.check(lib.dsv32_indexer_topk(C.byref(a), rt.stream_ptr(dev)), "lightning_indexer_decode")
+        if scatter is not None:
+            world, rank, per, idx_ptrs, score_ptrs = scatter
+            sca = _lib.TopkScatter(int(world), int(rank), int(per), 0)
+            for r in range(int(world)):
+                sca.idx_ptrs[r] = int(idx_ptrs[r])
+                sca.score_ptrs[r] = int(score_ptrs[r])
+            rt.check(lib.dsv32_indexer_topk_scatter(C.byref(a), C.byref(sca), rt.stream_ptr(dev)),
+                     "lightning_indexer_decode (scatter)")
+        else:
+            rt.check(lib.dsv32_indexer_topk(C.byref(a), rt.stream_ptr(dev)), "lightning_indexer_decode")
     return None
 
 

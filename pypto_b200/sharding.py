@@ -170,3 +170,59 @@ def sharded_indexer_topk_own_slice(idx_query, idx_query_scale, idx_key_cache, id
     if cand_sc.shape[0] == 0:
         return cand_id[:, :selected_count]
     return merge_fn(cand_sc, cand_id, selected_count)
+
+
+class PeerCandidateBuffers:
+    """Candidate buffers of a key-range-sharded indexer that the other ranks of the node write into directly: on every
+    rank an int32 and an fp32 array [tokens_per_rank, world, k] in symmetric memory (`torch.distributed._symmetric_memory`:
+    the same allocation on every rank, each mapped into every other rank's address space).  The top-k kernel of rank s
+    stores the row of token t at [t - owner * tokens_per_rank][s] of the owner's arrays (dsv32_indexer_topk_scatter), so
+    after `barrier()` each rank holds world * k candidates for each of its own tokens, already in the layout the merge
+    reads.  NCCL-free on the data path: plain stores over NVLink."""
+
+    def __init__(self, n_tokens: int, k: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerCandidateBuffers: at most 8 ranks (one node)")
+        self.k = k
+        self.per = math.ceil(n_tokens / self.world)
+        self.t0, self.t1 = token_slice_for_rank(n_tokens, self.rank, self.world)
+        shape = (self.per, self.world * k)
+        self.ids = symm_mem.empty(shape, dtype=torch.int32, device=device)
+        self.scores = symm_mem.empty(shape, dtype=torch.float32, device=device)
+        self._h_ids = symm_mem.rendezvous(self.ids, group)
+        self._h_sc = symm_mem.rendezvous(self.scores, group)
+        self.idx_ptrs = [int(p) for p in self._h_ids.buffer_ptrs]
+        self.score_ptrs = [int(p) for p in self._h_sc.buffer_ptrs]
+
+    def scatter_arg(self):
+        return (self.world, self.rank, self.per, self.idx_ptrs, self.score_ptrs)
+
+    def barrier(self):
+        """Every rank's stores have landed once every rank has passed this point in stream order."""
+        self._h_ids.barrier()
+
+    def own(self):
+        """(cand_scores, cand_ids) [n_own, world * k] of this rank's tokens (views of the symmetric arrays)."""
+        n = self.t1 - self.t0
+        return self.scores[:n], self.ids[:n]
+
+
+def sharded_indexer_topk_peer_stores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
+                                     block_table, buffers: PeerCandidateBuffers, selected_count: int = 2048):
+    """`sharded_indexer_topk_own_slice` without a collective: the top-k kernel of every rank writes its candidates
+    straight into the owning ranks' buffers (`buffers`, made once), a barrier follows, and the own slice is merged."""
+    from .lightning_indexer_quant_impl import indexer_scores_topk
+    max_ctx = block_table.shape[1] * 128
+    begin, end = key_range_for_rank(max_ctx, buffers.rank, buffers.world)
+    buffers.barrier()   # nobody is still merging the previous step's candidates
+    indexer_scores_topk(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key, block_table,
+                        None, selected_count, key_begin=begin, key_end=end, scatter=buffers.scatter_arg())
+    buffers.barrier()
+    cand_sc, cand_id = buffers.own()
+    if cand_sc.shape[0] == 0:
+        return cand_id[:, :selected_count]
+    return _cuda_merge(cand_sc, cand_id, selected_count)

@@ -42,6 +42,19 @@ def _long_request(rank, world):
     own = sharding.sharded_indexer_topk_own_slice(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"], d["weights"],
                                                   d["act_seq"], d["block_table"], k)
     assert torch.equal(own, idx[t0:t1])
+    # ... and so does the collective-free form, in which the top-k kernel stores every token's row straight into
+    # the owning rank's symmetric-memory buffer (twice: the buffers are reused from step to step)
+    try:
+        bufs = sharding.PeerCandidateBuffers(s1, k, dev)
+    except Exception as e:  # noqa: BLE001 -- symmetric memory is not available everywhere (needs peer mapping support)
+        print(f"[multi-gpu] symmetric memory unavailable, peer-store form not run: {type(e).__name__}: {e}")
+        bufs = None
+    if bufs is not None:
+        for _ in range(2):
+            peer = sharding.sharded_indexer_topk_peer_stores(d["q_int8"], d["q_scale"], d["idx_k"], d["idx_k_scale"],
+                                                             d["weights"], d["act_seq"], d["block_table"], bufs, k)
+            assert torch.equal(peer, idx[t0:t1])
+        pypto_b200.check_status(dev)
     out = torch.empty((1, t1 - t0, 128, 512), dtype=torch.bfloat16, device=dev)
     act_slice = torch.tensor([L - s1 + t1], dtype=torch.int32, device=dev)
     sparse_flash_attention_quant_d(d["q_nope"], d["q_rope"], d["k_nope"], d["k_rope"], d["k_scales"],
