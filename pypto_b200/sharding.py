@@ -15,6 +15,7 @@
 from __future__ import annotations
 
 import math
+import os
 from typing import Callable, List, Optional, Sequence
 
 import torch
@@ -181,6 +182,9 @@ class PeerCandidateBuffers:
     reads.  NCCL-free on the data path: plain stores over NVLink."""
 
     def __init__(self, n_tokens: int, k: int, device, group=None):
+        # Only peer pointers are needed here (plain stores, no multimem): ask torch not to bind the buffers to an NVLink
+        # multicast object, which would tie every rank's GPU to the fate of the others.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(group)
