@@ -59,6 +59,24 @@ def test_host_side_rejections(lib):
     t = _lib.TopkArgs()
     t.rows, t.ld, t.k = 1, 8, 4096
     assert lib.dsv32_topk_select(C.byref(t), None) == -1
+    # the sharded form of the indexer: one request, at most eight ranks, a buffer pair for every rank
+    sc = _lib.TopkScatter()
+    i2 = _lib.IndexerArgs()
+    i2.b, i2.s1, i2.block_size, i2.max_blocks, i2.selected_count = 2, 4, 128, 1, 2048
+    sc.world, sc.rank, sc.tokens_per_rank = 2, 0, 2
+    assert lib.dsv32_indexer_topk_scatter(C.byref(i2), C.byref(sc), None) == -1
+    assert b"one request" in lib.dsv32_last_error()
+    i2.b = 1
+    sc.world = 9
+    assert lib.dsv32_indexer_topk_scatter(C.byref(i2), C.byref(sc), None) == -1
+    assert b"at most 8" in lib.dsv32_last_error()
+    sc.world, sc.tokens_per_rank = 2, 1
+    assert lib.dsv32_indexer_topk_scatter(C.byref(i2), C.byref(sc), None) == -1
+    assert b"does not cover" in lib.dsv32_last_error()
+    sc.tokens_per_rank = 2
+    assert lib.dsv32_indexer_topk_scatter(C.byref(i2), C.byref(sc), None) == -1
+    assert b"buffer of rank 0" in lib.dsv32_last_error()
+    assert lib.dsv32_indexer_topk_scatter(C.byref(i2), None, None) == -1
     p = _lib.PrologArgs()
     p.t = -1
     assert lib.dsv32_indexer_prolog(C.byref(p), None) == -1
