@@ -104,17 +104,18 @@ def _worker(rank, world, port, mode, ret):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
     try:
-        d = helpers.gen_indexer_inputs(21, [6000], s1=3 if mode == "own" else 2)
+        d = helpers.gen_indexer_inputs(21, [6000], s1={"own": 3, "own1": 1}.get(mode, 2))
         if mode == "die" and rank == 1:
             raise RuntimeError("rank 1 fails before the collective")
-        if mode == "own":   # three tokens over two ranks: slices of two and one token, the second padded on the wire
+        if mode in ("own", "own1"):   # three tokens over two ranks: slices of two and one token, the second padded on the
+            # wire; one token: the second rank owns nothing and gets an empty result
             out = sharding.sharded_indexer_topk_own_slice(d["query"], d["q_scale"], d["key"], d["k_scale"], d["weights"],
                                                           d["act_seq"], d["block_table"], 2048, local_fn=_oracle_local,
                                                           merge_fn=orc.merge_topk_candidates)
             ref = orc.lightning_indexer(d["query"], d["q_scale"], d["key"], d["k_scale"], d["weights"], d["act_seq"],
                                         d["block_table"], 2048)
-            t0, t1 = sharding.token_slice_for_rank(3, rank, world)
-            ret[rank] = "ok" if torch.equal(out, ref[t0:t1, 0]) else "mismatch"
+            t0, t1 = sharding.token_slice_for_rank(ref.shape[0], rank, world)
+            ret[rank] = "ok" if (out.shape[0] == t1 - t0 and torch.equal(out, ref[t0:t1, 0])) else "mismatch"
             return
         out = sharding.sharded_indexer_topk(d["query"], d["q_scale"], d["key"], d["k_scale"], d["weights"], d["act_seq"],
                                             d["block_table"], 2048, local_fn=_oracle_local,
@@ -151,6 +152,10 @@ def test_key_range_sharded_indexer_equals_unsharded_world2():
 def test_own_slice_exchange_equals_unsharded_rows_world2():
     """The all-to-all form: every rank gets the global top-k of its own token slice only."""
     assert _run("own") == {0: "ok", 1: "ok"}
+
+
+def test_own_slice_exchange_with_a_rank_that_owns_no_token_world2():
+    assert _run("own1") == {0: "ok", 1: "ok"}
 
 
 def test_rank_failure_surfaces_as_error_on_the_healthy_rank():
